@@ -1,0 +1,418 @@
+"""fomoe_b200 -- fomoe's routed-expert FFN decode path, native on B200.
+
+This package is a thin ctypes mirror of ``include/fomoe_b200.h``; all work happens in
+``libfomoe_b200.so`` (hand-written CUDA for sm_100a behind a C host library).  There is no
+Python or CPU implementation of the path: if the shared library is missing or no CUDA
+device is present, construction fails loudly.
+
+The three classes follow the three groups of the C ABI:
+
+* :class:`GpuOperator`   -- the reference's ``gpu.h`` surface (``gpu_init`` / ``gpu_expert_ffn``)
+* :class:`ExpertEngine`  -- CUDA twin of the reference's ``cpu_expert.h`` engine
+* :class:`MoeDecoder`    -- resident expert table + on-device routing + decode stack
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfomoe_b200.so")
+
+TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K = 12, 13, 14
+STREAM_ROUTER, STREAM_RESID, STREAM_NORMW, STREAM_HIDDEN = 3, 4, 5, 6
+M_GATE, M_UP, M_DOWN = 0, 1, 2
+ROUTER_STD, RESID_STD, NORMW_MEAN, NORMW_STD = 0.02, 1.0, 1.0, 0.1
+BLOCK_BYTES = {TYPE_Q4_K: 144, TYPE_Q6_K: 210}
+
+_f32p = C.POINTER(C.c_float)
+_i32p = C.POINTER(C.c_int)
+
+
+class Config(C.Structure):
+    _fields_ = [("device", C.c_int), ("n_layers", C.c_int), ("n_embd", C.c_int), ("n_inter", C.c_int),
+                ("n_experts", C.c_int), ("top_k", C.c_int), ("has_shared", C.c_int), ("gate_type", C.c_int),
+                ("down_types", _i32p), ("tp_rank", C.c_int), ("tp_size", C.c_int), ("rms_eps", C.c_float),
+                ("car_threshold", C.c_float), ("car_dampen", C.c_int), ("max_tokens", C.c_int)]
+
+
+class Work(C.Structure):
+    _fields_ = [("expert_data", C.c_void_p), ("score", C.c_float), ("gate_type", C.c_int), ("up_type", C.c_int),
+                ("down_type", C.c_int), ("expert_gate_size", C.c_uint64), ("expert_up_size", C.c_uint64)]
+
+
+# name -> (restype, argtypes); every symbol include/fomoe_b200.h declares
+_SIGS = {
+    "gpu_init": (C.c_void_p, []),
+    "gpu_free": (None, [C.c_void_p]),
+    "gpu_register_buffers": (None, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_uint64]),
+    "gpu_unregister_buffers": (None, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int]),
+    "gpu_upload_model": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "gpu_set_ram_cache_mb": (None, [C.c_void_p, C.c_int]),
+    "gpu_set_vram_cache_mb": (None, [C.c_void_p, C.c_int]),
+    "gpu_forward": (C.c_void_p, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "gpu_reset_state": (None, [C.c_void_p]),
+    "gpu_seed_vram_cache": (C.c_int, [C.c_void_p, C.c_void_p, C.c_char_p]),
+    "gpu_enable_expert_freq": (None, [C.c_void_p]),
+    "gpu_get_expert_freq": (C.c_void_p, [C.c_void_p]),
+    "gpu_get_expert_dims": (None, [C.c_void_p, _i32p, _i32p]),
+    "gpu_get_pingpong_relay_stats": (None, [C.c_void_p] + [C.POINTER(C.c_uint64)] * 5),
+    "gpu_expert_ffn": (C.c_int, [C.c_void_p, _f32p, C.POINTER(C.c_void_p), _f32p, C.c_int, C.c_int, C.c_int,
+                                 C.c_uint64, C.c_uint64, C.c_uint64, C.c_int, C.c_int, C.c_int, _f32p]),
+    "b200_expert_create": (C.c_void_p, [C.c_int, C.c_int]),
+    "b200_expert_free": (None, [C.c_void_p]),
+    "b200_expert_reset": (None, [C.c_void_p]),
+    "b200_expert_ffn": (None, [C.c_void_p, C.c_void_p, _f32p, C.c_float, C.c_int, C.c_int, C.c_int, C.c_uint64,
+                               C.c_uint64]),
+    "b200_expert_submit_async": (None, [C.c_void_p, _f32p, C.POINTER(Work), C.c_int]),
+    "b200_expert_wait": (None, [C.c_void_p]),
+    "b200_expert_result": (_f32p, [C.c_void_p]),
+    "b200_expert_get_timing": (None, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_double), _i32p]),
+    "fomoe_b200_create": (C.c_void_p, [C.POINTER(Config)]),
+    "fomoe_b200_destroy": (None, [C.c_void_p]),
+    "fomoe_b200_last_error": (C.c_char_p, [C.c_void_p]),
+    "fomoe_b200_status": (C.c_int, [C.c_void_p]),
+    "fomoe_b200_record_bytes": (C.c_uint64, [C.c_void_p, C.c_int]),
+    "fomoe_b200_table_bytes": (C.c_uint64, [C.c_void_p]),
+    "fomoe_b200_table_generate": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "fomoe_b200_table_upload": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "fomoe_b200_table_export": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "fomoe_b200_table_dequant": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, _f32p]),
+    "fomoe_b200_router_upload": (C.c_int, [C.c_void_p, C.c_int, _f32p]),
+    "fomoe_b200_glue_upload": (C.c_int, [C.c_void_p, C.c_int, _f32p, _f32p]),
+    "fomoe_b200_set_resident_mask": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "fomoe_b200_set_car": (C.c_int, [C.c_void_p, C.c_float, C.c_int]),
+    "fomoe_b200_moe_layer": (C.c_int, [C.c_void_p, C.c_int, _f32p, _f32p, _i32p, _f32p, _i32p, _f32p]),
+    "fomoe_b200_moe_layer_routed": (C.c_int, [C.c_void_p, C.c_int, _f32p, _i32p, _f32p, C.c_int, _f32p]),
+    "fomoe_b200_stack_run": (C.c_int, [C.c_void_p, _f32p, C.c_int, C.c_int, _f32p]),
+    "fomoe_b200_tokens_upload": (C.c_int, [C.c_void_p, C.c_int, C.c_int, _f32p]),
+    "fomoe_b200_tokens_run": (C.c_int, [C.c_void_p, C.c_int, C.c_int, _f32p]),
+    "fomoe_b200_tokens_download": (C.c_int, [C.c_void_p, C.c_int, C.c_int, _f32p]),
+    "fomoe_b200_decode_token": (C.c_int, [C.c_void_p, _f32p, _f32p]),
+    "fomoe_b200_tokens_profile": (C.c_int, [C.c_void_p, C.c_int, C.c_int, _f32p, _i32p]),
+    "fomoe_b200_get_routing": (C.c_int, [C.c_void_p, C.c_int, _i32p, _f32p, _i32p]),
+    "fomoe_b200_substitutions": (C.c_uint64, [C.c_void_p]),
+    "fomoe_b200_kernel_launches": (C.c_uint64, [C.c_void_p]),
+    "fomoe_b200_set_graphs": (C.c_int, [C.c_void_p, C.c_int]),
+    "fomoe_b200_peek": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_uint64]),
+    "fomoe_b200_matvec": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p, _f32p]),
+    "fomoe_b200_quantize_q8k": (C.c_int, [C.c_void_p, _f32p, C.c_int, C.c_void_p]),
+    "fomoe_b200_synth_matrix": (None, [C.c_uint64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "fomoe_b200_synth_f32": (None, [C.c_uint64, C.c_int, C.c_int, C.c_float, C.c_float, C.c_uint64, _f32p]),
+}
+
+_lib = None
+
+
+def lib():
+    """Load libfomoe_b200.so (built by ``__graft_entry__.build()`` / ``make -C fomoe_b200/csrc``)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `make -C fomoe_b200/csrc` "
+                              "(there is no fallback implementation)")
+        l = C.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGS.items():
+            f = getattr(l, name)
+            f.restype = res
+            f.argtypes = args
+        _lib = l
+    return _lib
+
+
+def exported_symbols():
+    return sorted(_SIGS)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _fp(a):
+    return a.ctypes.data_as(_f32p)
+
+
+def _ip(a):
+    return a.ctypes.data_as(_i32p)
+
+
+def matrix_bytes(qtype, rows, cols):
+    return rows * (cols // 256) * BLOCK_BYTES[qtype]
+
+
+def synth_matrix(seed, layer, expert, matrix, qtype, rows, cols):
+    """Host-side synthetic generator: ggml-ordered bytes of one expert matrix."""
+    out = np.empty(matrix_bytes(qtype, rows, cols), dtype=np.uint8)
+    lib().fomoe_b200_synth_matrix(seed, layer, expert, matrix, qtype, rows, cols, out.ctypes.data)
+    return out
+
+
+def synth_f32(seed, layer, stream_id, mean, std, n):
+    out = np.empty(n, dtype=np.float32)
+    lib().fomoe_b200_synth_f32(seed, layer, stream_id, mean, std, n, _fp(out))
+    return out
+
+
+class MoeDecoder:
+    """Resident expert table + router/CAR + SwiGLU experts + decode stack on one GPU (one TP rank)."""
+
+    def __init__(self, n_layers, n_embd=4096, n_inter=1024, n_experts=512, top_k=10, has_shared=True,
+                 down_types=None, device=0, tp_rank=0, tp_size=1, rms_eps=1e-6, car_threshold=1.0,
+                 car_dampen=False, max_tokens=1):
+        self._l = lib()
+        self.n_layers, self.n_embd, self.n_inter = n_layers, n_embd, n_inter
+        self.n_experts, self.top_k, self.has_shared = n_experts, top_k, bool(has_shared)
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        self.down_types = list(down_types) if down_types is not None else [TYPE_Q6_K] * n_layers
+        self._dt = (C.c_int * n_layers)(*self.down_types)
+        cfg = Config(device, n_layers, n_embd, n_inter, n_experts, top_k, int(bool(has_shared)), TYPE_Q4_K,
+                     C.cast(self._dt, _i32p), tp_rank, tp_size, rms_eps, car_threshold, int(bool(car_dampen)),
+                     max_tokens)
+        self._h = self._l.fomoe_b200_create(C.byref(cfg))
+        if not self._h:
+            raise RuntimeError("fomoe_b200_create failed (no CUDA device, unsupported shape or out of memory)")
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._l.fomoe_b200_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def _ck(self, rc, what):
+        if rc != 0:
+            raise RuntimeError(f"{what}: {self._l.fomoe_b200_last_error(self._h).decode()}")
+
+    # ---- table
+    def record_bytes(self, layer):
+        return int(self._l.fomoe_b200_record_bytes(self._h, layer))
+
+    def table_bytes(self):
+        return int(self._l.fomoe_b200_table_bytes(self._h))
+
+    def generate(self, seed):
+        self._ck(self._l.fomoe_b200_table_generate(self._h, seed), "table_generate")
+
+    def upload_expert(self, layer, expert, record):
+        r = np.ascontiguousarray(record).view(np.uint8).reshape(-1)
+        assert r.size == self.record_bytes(layer), (r.size, self.record_bytes(layer))
+        self._ck(self._l.fomoe_b200_table_upload(self._h, layer, expert, r.ctypes.data), "table_upload")
+
+    def _shard_shape(self, layer, matrix):
+        if matrix == M_DOWN:
+            return self.down_types[layer], self.n_embd, self.n_inter // self.tp_size
+        return TYPE_Q4_K, self.n_inter // self.tp_size, self.n_embd
+
+    def export_shard(self, layer, expert, matrix):
+        """This rank's shard of one matrix, ggml block order, row-major over (rows, column blocks)."""
+        t, rows, cols = self._shard_shape(layer, matrix)
+        out = np.empty(matrix_bytes(t, rows, cols), dtype=np.uint8)
+        self._ck(self._l.fomoe_b200_table_export(self._h, layer, expert, matrix, out.ctypes.data), "table_export")
+        return out
+
+    def dequant_shard(self, layer, expert, matrix):
+        t, rows, cols = self._shard_shape(layer, matrix)
+        out = np.empty((rows, cols), dtype=np.float32)
+        self._ck(self._l.fomoe_b200_table_dequant(self._h, layer, expert, matrix, _fp(out)), "table_dequant")
+        return out
+
+    def upload_router(self, layer, w):
+        w = _f32(w)
+        assert w.shape == (self.n_experts, self.n_embd)
+        self._ck(self._l.fomoe_b200_router_upload(self._h, layer, _fp(w)), "router_upload")
+
+    def upload_glue(self, layer, resid=None, normw=None):
+        r = _f32(resid) if resid is not None else None
+        w = _f32(normw) if normw is not None else None
+        self._ck(self._l.fomoe_b200_glue_upload(self._h, layer, _fp(r) if r is not None else None,
+                                                _fp(w) if w is not None else None), "glue_upload")
+
+    def set_resident_mask(self, layer, mask):
+        if mask is None:
+            self._ck(self._l.fomoe_b200_set_resident_mask(self._h, layer, None), "set_resident_mask")
+            return
+        m = np.zeros(16, dtype=np.uint32)
+        mm = np.ascontiguousarray(mask, dtype=np.uint32)
+        m[:mm.size] = mm
+        self._ck(self._l.fomoe_b200_set_resident_mask(self._h, layer, m.ctypes.data), "set_resident_mask")
+
+    def set_car(self, threshold, dampen):
+        self._ck(self._l.fomoe_b200_set_car(self._h, threshold, int(bool(dampen))), "set_car")
+
+    # ---- compute
+    def moe_layer(self, layer, h):
+        """-> dict(out, ids, scores, ids_orig, all_scores)."""
+        h = _f32(h)
+        out = np.empty(self.n_embd, dtype=np.float32)
+        ids = np.empty(self.top_k, dtype=np.int32)
+        ids0 = np.empty(self.top_k, dtype=np.int32)
+        sc = np.empty(self.top_k, dtype=np.float32)
+        alls = np.empty(self.n_experts, dtype=np.float32)
+        self._ck(self._l.fomoe_b200_moe_layer(self._h, layer, _fp(h), _fp(out), _ip(ids), _fp(sc), _ip(ids0),
+                                              _fp(alls)), "moe_layer")
+        return dict(out=out, ids=ids, scores=sc, ids_orig=ids0, all_scores=alls)
+
+    def moe_layer_routed(self, layer, h, ids, scores):
+        h, scores = _f32(h), _f32(scores)
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        out = np.empty(self.n_embd, dtype=np.float32)
+        self._ck(self._l.fomoe_b200_moe_layer_routed(self._h, layer, _fp(h), _ip(ids), _fp(scores), ids.size,
+                                                     _fp(out)), "moe_layer_routed")
+        return out
+
+    def stack_run(self, x, l0=0, l1=None):
+        x = _f32(x)
+        out = np.empty_like(x)
+        self._ck(self._l.fomoe_b200_stack_run(self._h, _fp(x), l0, self.n_layers if l1 is None else l1, _fp(out)),
+                 "stack_run")
+        return out
+
+    def tokens_upload(self, first, x):
+        x = _f32(x).reshape(-1, self.n_embd)
+        self._ck(self._l.fomoe_b200_tokens_upload(self._h, first, x.shape[0], _fp(x)), "tokens_upload")
+
+    def tokens_run(self, first, count):
+        """Runs `count` resident tokens through every layer; returns CUDA-event milliseconds."""
+        ms = C.c_float(0.0)
+        self._ck(self._l.fomoe_b200_tokens_run(self._h, first, count, C.byref(ms)), "tokens_run")
+        return float(ms.value)
+
+    def decode_token(self, x):
+        """One token host -> host through every layer (H2D, graph launch, D2H, synchronise)."""
+        x = _f32(x)
+        out = np.empty_like(x)
+        self._ck(self._l.fomoe_b200_decode_token(self._h, _fp(x), _fp(out)), "decode_token")
+        return out
+
+    def tokens_profile(self, first, count):
+        """Plain launches with CUDA events around every kernel -> (ms, launches) per phase."""
+        ms = np.zeros(5, dtype=np.float32)
+        n = np.zeros(4, dtype=np.int32)
+        self._ck(self._l.fomoe_b200_tokens_profile(self._h, first, count, _fp(ms), _ip(n)), "tokens_profile")
+        names = ("prologue", "router", "gate_up", "down")
+        return {k: (float(ms[i]), int(n[i])) for i, k in enumerate(names)}, float(ms[4])
+
+    def tokens_download(self, first, count):
+        out = np.empty((count, self.n_embd), dtype=np.float32)
+        self._ck(self._l.fomoe_b200_tokens_download(self._h, first, count, _fp(out)), "tokens_download")
+        return out
+
+    def get_routing(self, layer):
+        ids = np.empty(self.top_k, dtype=np.int32)
+        ids0 = np.empty(self.top_k, dtype=np.int32)
+        sc = np.empty(self.top_k, dtype=np.float32)
+        self._ck(self._l.fomoe_b200_get_routing(self._h, layer, _ip(ids), _fp(sc), _ip(ids0)), "get_routing")
+        return ids, sc, ids0
+
+    def status(self):
+        return int(self._l.fomoe_b200_status(self._h))
+
+    def substitutions(self):
+        return int(self._l.fomoe_b200_substitutions(self._h))
+
+    def kernel_launches(self):
+        return int(self._l.fomoe_b200_kernel_launches(self._h))
+
+    def set_graphs(self, enable):
+        self._ck(self._l.fomoe_b200_set_graphs(self._h, int(bool(enable))), "set_graphs")
+
+    def peek(self, what, n_slots=None):
+        """Intermediates of the most recent layer call: 'act', 'q8a', 'q8h', 'dots', 'h'."""
+        ns = self.top_k + int(self.has_shared) if n_slots is None else n_slots
+        il = self.n_inter // self.tp_size
+        sel, dtype, shape = {"act": (0, np.float32, (ns, il)), "q8a": (1, np.uint8, (ns, il // 256, 304)),
+                             "q8h": (2, np.uint8, (self.n_embd // 256, 304)),
+                             "dots": (3, np.float32, (ns, self.n_embd)), "h": (4, np.float32, (self.n_embd,))}[what]
+        out = np.empty(shape, dtype=dtype)
+        self._ck(self._l.fomoe_b200_peek(self._h, sel, out.ctypes.data, out.nbytes), "peek")
+        return out
+
+    # ---- micro helpers
+    def matvec(self, qtype, w_ggml, rows, cols, x):
+        w = np.ascontiguousarray(w_ggml).view(np.uint8).reshape(-1)
+        assert w.size == matrix_bytes(qtype, rows, cols)
+        x = _f32(x)
+        y = np.empty(rows, dtype=np.float32)
+        self._ck(self._l.fomoe_b200_matvec(self._h, qtype, w.ctypes.data, rows, cols, _fp(x), _fp(y)), "matvec")
+        return y
+
+    def quantize_q8k(self, x):
+        x = _f32(x)
+        out = np.empty((x.size // 256) * 292, dtype=np.uint8)
+        self._ck(self._l.fomoe_b200_quantize_q8k(self._h, _fp(x), x.size, out.ctypes.data), "quantize_q8k")
+        return out
+
+
+class GpuOperator:
+    """The reference's gpu.h operator surface (gpu_init / gpu_expert_ffn / gpu_free)."""
+
+    def __init__(self):
+        self._l = lib()
+        self._h = self._l.gpu_init()
+        if not self._h:
+            raise RuntimeError("gpu_init failed: no CUDA device")
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._l.gpu_free(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def expert_ffn(self, h, expert_buffers, scores, n_embd, inter, gate_size, up_size, stride, gate_type, up_type,
+                   down_type):
+        """Returns (rc, ffn_out); rc == -1 means "fall back to the CPU path" as in the reference."""
+        h, scores = _f32(h), _f32(scores)
+        keep = [np.ascontiguousarray(e).view(np.uint8).reshape(-1) for e in expert_buffers]
+        ptrs = (C.c_void_p * len(keep))(*[e.ctypes.data for e in keep])
+        out = np.zeros(n_embd, dtype=np.float32)
+        rc = self._l.gpu_expert_ffn(self._h, _fp(h), ptrs, _fp(scores), len(keep), n_embd, inter, gate_size, up_size,
+                                    stride, gate_type, up_type, down_type, _fp(out))
+        return rc, out
+
+
+class ExpertEngine:
+    """CUDA twin of the reference's cpu_expert.h engine (create/reset/ffn/submit_async/wait/result)."""
+
+    def __init__(self, n_embd, inter):
+        self._l = lib()
+        self.n_embd, self.inter = n_embd, inter
+        self._h = self._l.b200_expert_create(n_embd, inter)
+        if not self._h:
+            raise RuntimeError("b200_expert_create failed: no CUDA device or unsupported shape")
+        self._keep = []
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._l.b200_expert_free(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def reset(self):
+        self._l.b200_expert_reset(self._h)
+
+    def ffn(self, expert, x, score, gate_type, up_type, down_type, gate_size, up_size):
+        e = np.ascontiguousarray(expert).view(np.uint8).reshape(-1)
+        x = _f32(x)
+        self._l.b200_expert_ffn(self._h, e.ctypes.data, _fp(x), score, gate_type, up_type, down_type, gate_size,
+                                up_size)
+
+    def submit_async(self, x, experts, scores, gate_type, up_type, down_type, gate_size, up_size):
+        self._keep = [np.ascontiguousarray(e).view(np.uint8).reshape(-1) for e in experts] + [_f32(x)]
+        w = (Work * len(experts))()
+        for i, e in enumerate(self._keep[:-1]):
+            w[i] = Work(e.ctypes.data, float(scores[i]), gate_type, up_type, down_type, gate_size, up_size)
+        self._l.b200_expert_submit_async(self._h, _fp(self._keep[-1]), w, len(experts))
+
+    def wait(self):
+        self._l.b200_expert_wait(self._h)
+
+    def result(self):
+        p = self._l.b200_expert_result(self._h)
+        return np.ctypeslib.as_array(p, shape=(self.n_embd,)).copy()
+
+    def timing(self):
+        a, b, n = C.c_double(0), C.c_double(0), C.c_int(0)
+        self._l.b200_expert_get_timing(self._h, C.byref(a), C.byref(b), C.byref(n))
+        return a.value, b.value, n.value

@@ -1,0 +1,154 @@
+/*
+ * dots.cuh -- per-lane integer dot products of one quantised weight block (already in
+ * registers) with one Q8_K activation block, plus the warp-level Q8_K quantiser.
+ *
+ * Arithmetic follows the reference's Q8_K-activation path:
+ *   Q4_K: src/quant.c:405-476   sum_j sc_j * dot32(q4_j, q8_j) as int32, times (y.d * d), minus
+ *                               (y.d * dmin) * sum_j m_j * (bsum_2j + bsum_2j+1)
+ *   Q6_K: src/quant.c:478-607   sum_g sc_g * dot16(q6_g, q8_g) as int32, times (y.d * d)
+ *   Q8_K: src/quant.c:343-375   amax, iscale = 127/amax, roundf, clamp, bsums, d = 1/iscale
+ * All integer sums are exact, so dp4a may associate them freely; only the fp32 sum over
+ * blocks differs in order from the CPU.
+ */
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "launch.h"
+
+#define FB_Q8_U4 19 /* uint4 per fb_q8_entry_t */
+
+__device__ __forceinline__ int fb_dp4a(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
+
+__device__ __forceinline__ uint32_t fb_u4c(const uint4 &v, int i) {
+    return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+}
+
+__device__ __forceinline__ float fb_half_bits_to_float(uint32_t h16) {
+    return __half2float(__ushort_as_half((unsigned short)h16));
+}
+
+/* a: the activation entry (16 uint4 of int8, then 2 uint4 of int16 bsums, then d). */
+__device__ __forceinline__ float fb_dot_q4k(const uint4 &hdr, const uint4 (&qs)[8], const uint4 *a) {
+    const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+    const uint32_t sc_lo = u0 & 0x3f3f3f3fu;
+    const uint32_t sc_hi = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
+    const uint32_t m_lo = u1 & 0x3f3f3f3fu;
+    const uint32_t m_hi = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
+
+    int isum = 0;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        int lo = 0, hi = 0;
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            const uint4 w = qs[2 * c + kk];
+            const uint4 al = a[4 * c + kk];
+            const uint4 ah = a[4 * c + 2 + kk];
+            lo = fb_dp4a(w.x & 0x0f0f0f0fu, al.x, lo);
+            lo = fb_dp4a(w.y & 0x0f0f0f0fu, al.y, lo);
+            lo = fb_dp4a(w.z & 0x0f0f0f0fu, al.z, lo);
+            lo = fb_dp4a(w.w & 0x0f0f0f0fu, al.w, lo);
+            hi = fb_dp4a((w.x >> 4) & 0x0f0f0f0fu, ah.x, hi);
+            hi = fb_dp4a((w.y >> 4) & 0x0f0f0f0fu, ah.y, hi);
+            hi = fb_dp4a((w.z >> 4) & 0x0f0f0f0fu, ah.z, hi);
+            hi = fb_dp4a((w.w >> 4) & 0x0f0f0f0fu, ah.w, hi);
+        }
+        const uint32_t scw = (c < 2) ? sc_lo : sc_hi;
+        const int s0 = (scw >> (16 * (c & 1))) & 0xff, s1 = (scw >> (16 * (c & 1) + 8)) & 0xff;
+        isum += s0 * lo + s1 * hi;
+    }
+    /* mins: bsums are int16 pairs; bs32_j = bsums[2j] + bsums[2j+1] */
+    const uint4 b0 = a[16], b1 = a[17];
+    int msum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const uint32_t pr = fb_u4c(j < 4 ? b0 : b1, j & 3);
+        const int bs = (int)(short)(pr & 0xffff) + (int)(short)(pr >> 16);
+        const uint32_t mw = (j < 4) ? m_lo : m_hi;
+        msum += (int)((mw >> (8 * (j & 3))) & 0xff) * bs;
+    }
+    const float yd = __uint_as_float(a[18].x);
+    const float d = __fmul_rn(yd, fb_half_bits_to_float(hdr.x & 0xffff));
+    const float dmin = __fmul_rn(yd, fb_half_bits_to_float(hdr.x >> 16));
+    return __fmaf_rn(d, (float)isum, -__fmul_rn(dmin, (float)msum));
+}
+
+__device__ __forceinline__ float fb_dot_q6k(const uint4 (&ql)[8], const uint4 (&qh)[4], const uint4 &sc,
+                                            uint32_t d16, const uint4 *a) {
+    int total = 0;
+    const uint4 b0 = a[16], b1 = a[17];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+#pragma unroll
+        for (int tq = 0; tq < 2; tq++) {
+            /* 16 value positions x 4 sub-blocks: words t = 4*tq .. 4*tq+3 */
+            const uint4 A = ql[4 * h + tq], B = ql[4 * h + 2 + tq], H = qh[2 * h + tq];
+            int d0 = 0, d1 = 0, d2 = 0, d3 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t qa = fb_u4c(A, i), qb = fb_u4c(B, i), hh = fb_u4c(H, i);
+                const uint32_t v0 = (qa & 0x0f0f0f0fu) | ((hh << 4) & 0x30303030u);
+                const uint32_t v1 = (qb & 0x0f0f0f0fu) | ((hh << 2) & 0x30303030u);
+                const uint32_t v2 = ((qa >> 4) & 0x0f0f0f0fu) | (hh & 0x30303030u);
+                const uint32_t v3 = ((qb >> 4) & 0x0f0f0f0fu) | ((hh >> 2) & 0x30303030u);
+                d0 = fb_dp4a(v0, fb_u4c(a[8 * h + 0 + tq], i), d0);
+                d1 = fb_dp4a(v1, fb_u4c(a[8 * h + 2 + tq], i), d1);
+                d2 = fb_dp4a(v2, fb_u4c(a[8 * h + 4 + tq], i), d2);
+                d3 = fb_dp4a(v3, fb_u4c(a[8 * h + 6 + tq], i), d3);
+            }
+            /* groups g = 8h + 2i + tq; q6 = v - 32  =>  dot = dsum - 32 * bsum_g */
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int g = 8 * h + 2 * i + tq;
+                const uint32_t pr = fb_u4c(g < 8 ? b0 : b1, (g & 7) >> 1);
+                const int bs = (g & 1) ? (int)(short)(pr >> 16) : (int)(short)(pr & 0xffff);
+                const int scv = (int)(signed char)((fb_u4c(sc, g >> 2) >> (8 * (g & 3))) & 0xff);
+                const int dv = i == 0 ? d0 : i == 1 ? d1 : i == 2 ? d2 : d3;
+                total += scv * (dv - 32 * bs);
+            }
+        }
+    }
+    const float yd = __uint_as_float(a[18].x);
+    const float d = __fmul_rn(yd, fb_half_bits_to_float(d16));
+    return __fmul_rn(d, (float)total);
+}
+
+/* Sum over the `span` consecutive lanes (span a power of two <= 32) that share a row. */
+__device__ __forceinline__ float fb_span_sum(float v, int span) {
+    for (int o = span >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+/* One warp quantises 256 floats (lane holds src[8*lane .. 8*lane+7]) into one entry. */
+__device__ __forceinline__ void fb_warp_quantize(const float (&x)[8], fb_q8_entry_t *dst, int lane) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(x[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    uint32_t w0 = 0, w1 = 0;
+    int bs = 0;
+    float dout = 0.0f;
+    if (amax != 0.0f) {
+        const float iscale = __fdiv_rn(127.0f, amax);
+        int q[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            int v = (int)roundf(__fmul_rn(iscale, x[i]));
+            v = max(-127, min(127, v));
+            q[i] = v;
+            bs += v;
+        }
+        w0 = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+        w1 = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+        dout = __fdiv_rn(1.0f, iscale);
+    }
+    bs += __shfl_xor_sync(0xffffffffu, bs, 1); /* groups of 16 values = lane pairs */
+    reinterpret_cast<uint2 *>(dst->qs)[lane] = make_uint2(w0, w1);
+    if ((lane & 1) == 0) dst->bsums[lane >> 1] = (int16_t)bs;
+    if (lane == 0) {
+        dst->d = dout;
+        dst->pad[0] = dst->pad[1] = dst->pad[2] = 0;
+    }
+}

@@ -1,0 +1,1180 @@
+/*
+ * engine.c -- host side of libfomoe_b200.so, in C like the reference's host code.
+ *
+ * Owns the CUDA context objects, the HBM-resident expert table and the per-token launch
+ * sequence; calls the kernels only through the thin C-ABI of launch.h.  The reference
+ * keeps experts in a VRAM LRU backed by pinned DRAM and NVMe (src/expert_cache.c,
+ * src/expert_store.c, src/nvme_io.c) and returns to the host after the router of every
+ * layer to classify and run car_evaluate (src/gpu_kernels.hip:6984, 7097-7187); here the
+ * whole table is resident and routing stays on the device, so a token is one CUDA graph.
+ */
+#include <cuda_runtime_api.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "../../include/fomoe_b200.h"
+#include "launch.h"
+#include "synth.h"
+
+#define FB_N_SM_DEFAULT 148
+
+typedef struct {
+    uint8_t *table;      /* (n_experts + has_shared) records of rec_bytes */
+    uint64_t rec_bytes;  /* this rank's bytes per record in the device layout */
+    uint64_t down_bytes;
+    int down_type;
+    float *router_w, *resid, *normw;
+    uint32_t *mask; /* device copy of the residency mask */
+    int mask_set;
+} fb_layer_t;
+
+struct fomoe_b200_ctx {
+    fomoe_b200_config_t cfg;
+    int *down_types;
+    int n_sm;
+    cudaStream_t stream;
+    cudaEvent_t ev0, ev1;
+    fb_layer_t *layers;
+    uint64_t table_bytes;
+    /* geometry */
+    int inter_local, gate_bpr, down_bpr, gate_groups, down_groups, n_slots;
+    uint64_t gate_bytes; /* bytes of one gate (or up) shard */
+    /* state */
+    float *x, *h, *moe_out, *logits, *all_scores, *scores, *act, *dots;
+    int *ids, *ids_orig, *status;
+    const uint8_t **slot_rec;
+    fb_q8_entry_t *q8h, *q8a;
+    unsigned *counters, *tok_ctr;
+    uint32_t *freq; /* [n_layers][n_experts] or NULL */
+    float *tok_in, *tok_out;
+    int max_tokens;
+    /* staging */
+    uint8_t *stage;       /* device staging for uploads / exports */
+    uint64_t stage_bytes;
+    float *pin;           /* pinned host scratch, 4 * n_embd floats + routing scratch */
+    /* graphs */
+    int use_graphs;
+    cudaGraphExec_t graph_exec;
+    int graph_nodes;
+    uint64_t launches;
+    int pin_busy; /* an un-synchronised call may still be reading the pinned scratch */
+    /* per-kernel event timing (tokens_profile) */
+    cudaEvent_t *pev;
+    int *pev_phase;
+    int pev_cap, pev_n, profiling;
+    char err[256];
+};
+
+static void set_err(fomoe_b200_ctx_t *c, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(c->err, sizeof(c->err), fmt, ap);
+    va_end(ap);
+    fprintf(stderr, "fomoe_b200: %s\n", c->err);
+}
+
+#define CK(c, call)                                                                      \
+    do {                                                                                 \
+        cudaError_t e_ = (call);                                                         \
+        if (e_ != cudaSuccess) {                                                         \
+            set_err((c), "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+            return -1;                                                                   \
+        }                                                                                \
+    } while (0)
+
+#define CKL(c, call)                                                                     \
+    do {                                                                                 \
+        int e_;                                                                          \
+        if ((c)->profiling) prof_mark((c), #call);                                       \
+        e_ = (call);                                                                     \
+        (c)->launches++;                                                                 \
+        if (e_ != 0) {                                                                   \
+            set_err((c), "%s failed: %s (%s:%d)", #call, cudaGetErrorString((cudaError_t)e_), __FILE__, __LINE__); \
+            return -1;                                                                   \
+        }                                                                                \
+    } while (0)
+
+static void prof_mark(struct fomoe_b200_ctx *c, const char *call);
+
+static int is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+static uint64_t ggml_matrix_bytes(int type, int rows, int cols) {
+    return (uint64_t)rows * (uint64_t)(cols / FB_QK) * fb_block_bytes(type);
+}
+
+static fb_shard_geom_t geom_gate(const fomoe_b200_ctx_t *c) {
+    fb_shard_geom_t g;
+    g.type = c->cfg.gate_type;
+    g.rows_local = c->inter_local;
+    g.bpr_local = g.bpr_full = c->gate_bpr;
+    g.row0 = c->cfg.tp_rank * c->inter_local;
+    g.b0 = 0;
+    return g;
+}
+
+static fb_shard_geom_t geom_down(const fomoe_b200_ctx_t *c, int type) {
+    fb_shard_geom_t g;
+    g.type = type;
+    g.rows_local = c->cfg.n_embd;
+    g.bpr_local = c->down_bpr;
+    g.bpr_full = c->cfg.n_inter / FB_QK;
+    g.row0 = 0;
+    g.b0 = c->cfg.tp_rank * c->down_bpr;
+    return g;
+}
+
+static void drop_graph(fomoe_b200_ctx_t *c) {
+    if (c->graph_exec) {
+        cudaGraphExecDestroy(c->graph_exec);
+        c->graph_exec = NULL;
+    }
+}
+
+/* ------------------------------------------------------------------ create / destroy */
+void fomoe_b200_destroy(fomoe_b200_ctx_t *c) {
+    if (!c) return;
+    cudaSetDevice(c->cfg.device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    drop_graph(c);
+    if (c->layers) {
+        for (int l = 0; l < c->cfg.n_layers; l++) {
+            cudaFree(c->layers[l].table);
+            cudaFree(c->layers[l].router_w);
+            cudaFree(c->layers[l].resid);
+            cudaFree(c->layers[l].normw);
+            cudaFree(c->layers[l].mask);
+        }
+        free(c->layers);
+    }
+    cudaFree(c->x); cudaFree(c->h); cudaFree(c->moe_out); cudaFree(c->logits); cudaFree(c->all_scores);
+    cudaFree(c->scores); cudaFree(c->act); cudaFree(c->dots); cudaFree(c->ids); cudaFree(c->ids_orig);
+    cudaFree(c->status); cudaFree((void *)c->slot_rec); cudaFree(c->q8h); cudaFree(c->q8a);
+    cudaFree(c->counters); cudaFree(c->tok_ctr); cudaFree(c->freq); cudaFree(c->tok_in); cudaFree(c->tok_out);
+    cudaFree(c->stage);
+    if (c->pin) cudaFreeHost(c->pin);
+    for (int i = 0; i < c->pev_cap; i++) cudaEventDestroy(c->pev[i]);
+    free(c->pev);
+    free(c->pev_phase);
+    if (c->ev0) cudaEventDestroy(c->ev0);
+    if (c->ev1) cudaEventDestroy(c->ev1);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    free(c->down_types);
+    free(c);
+}
+
+static int dev_alloc(fomoe_b200_ctx_t *c, void **p, uint64_t bytes) {
+    CK(c, cudaMalloc(p, bytes ? bytes : 16));
+    CK(c, cudaMemset(*p, 0, bytes ? bytes : 16));
+    return 0;
+}
+
+fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
+    if (!cfg) return NULL;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) {
+        fprintf(stderr, "fomoe_b200: no CUDA device (this library has no CPU path)\n");
+        return NULL;
+    }
+    fomoe_b200_ctx_t *c = (fomoe_b200_ctx_t *)calloc(1, sizeof(*c));
+    if (!c) return NULL;
+    c->cfg = *cfg;
+    c->use_graphs = 1;
+    const int N = cfg->tp_size > 0 ? cfg->tp_size : 1;
+    c->cfg.tp_size = N;
+    if (cfg->device < 0 || cfg->device >= ndev || cfg->n_layers < 1 || cfg->n_embd % FB_QK || cfg->n_embd > 8192 ||
+        cfg->n_embd < FB_QK || cfg->n_inter % (FB_QK * N) || cfg->n_inter < FB_QK * N || cfg->n_experts < 1 ||
+        cfg->n_experts > FB_MAX_EXPERTS || cfg->top_k < 1 || cfg->top_k > FB_MAX_TOPK || cfg->top_k > cfg->n_experts ||
+        cfg->gate_type != FB_TYPE_Q4_K || cfg->tp_rank < 0 || cfg->tp_rank >= N) {
+        set_err(c, "unsupported configuration");
+        free(c);
+        return NULL;
+    }
+    c->inter_local = cfg->n_inter / N;
+    c->gate_bpr = cfg->n_embd / FB_QK;
+    c->down_bpr = c->inter_local / FB_QK;
+    if (!is_pow2(c->gate_bpr) || !is_pow2(c->down_bpr) || c->gate_bpr > 32 || c->down_bpr > 32 ||
+        c->inter_local / FB_QK > 32) {
+        set_err(c, "blocks per row must be a power of two <= 32 (n_embd %d, local intermediate %d)", cfg->n_embd,
+                c->inter_local);
+        free(c);
+        return NULL;
+    }
+    c->n_slots = cfg->top_k + (cfg->has_shared ? 1 : 0);
+    c->gate_groups = (int)fb_n_groups((uint64_t)c->inter_local * c->gate_bpr);
+    c->down_groups = (int)fb_n_groups((uint64_t)cfg->n_embd * c->down_bpr);
+    c->gate_bytes = fb_shard_bytes(FB_TYPE_Q4_K, (uint64_t)c->inter_local * c->gate_bpr);
+    c->max_tokens = cfg->max_tokens > 0 ? cfg->max_tokens : 1;
+    c->down_types = (int *)malloc(sizeof(int) * (size_t)cfg->n_layers);
+    for (int l = 0; l < cfg->n_layers; l++) {
+        c->down_types[l] = cfg->down_types ? cfg->down_types[l] : FB_TYPE_Q6_K;
+        if (c->down_types[l] != FB_TYPE_Q4_K && c->down_types[l] != FB_TYPE_Q6_K) {
+            set_err(c, "layer %d: down type %d unsupported", l, c->down_types[l]);
+            free(c->down_types);
+            free(c);
+            return NULL;
+        }
+    }
+    c->cfg.down_types = c->down_types;
+
+    if (cudaSetDevice(cfg->device) != cudaSuccess) goto fail;
+    {
+        struct cudaDeviceProp prop;
+        c->n_sm = (cudaGetDeviceProperties(&prop, cfg->device) == cudaSuccess) ? prop.multiProcessorCount
+                                                                                : FB_N_SM_DEFAULT;
+    }
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) goto fail;
+    if (cudaEventCreate(&c->ev0) != cudaSuccess || cudaEventCreate(&c->ev1) != cudaSuccess) goto fail;
+
+    c->layers = (fb_layer_t *)calloc((size_t)cfg->n_layers, sizeof(fb_layer_t));
+    const int n_recs = cfg->n_experts + (cfg->has_shared ? 1 : 0);
+    uint64_t max_rec_ggml = 0;
+    for (int l = 0; l < cfg->n_layers; l++) {
+        fb_layer_t *L = &c->layers[l];
+        L->down_type = c->down_types[l];
+        L->down_bytes = fb_shard_bytes(L->down_type, (uint64_t)cfg->n_embd * c->down_bpr);
+        L->rec_bytes = 2 * c->gate_bytes + L->down_bytes;
+        const uint64_t tb = L->rec_bytes * (uint64_t)n_recs;
+        if (cudaMalloc((void **)&L->table, tb) != cudaSuccess) {
+            set_err(c, "cudaMalloc of %.2f GB for layer %d's experts failed", tb / 1e9, l);
+            goto fail;
+        }
+        c->table_bytes += tb;
+        if (dev_alloc(c, (void **)&L->router_w, sizeof(float) * (uint64_t)cfg->n_experts * cfg->n_embd)) goto fail;
+        if (dev_alloc(c, (void **)&L->resid, sizeof(float) * cfg->n_embd)) goto fail;
+        if (dev_alloc(c, (void **)&L->normw, sizeof(float) * cfg->n_embd)) goto fail;
+        if (dev_alloc(c, (void **)&L->mask, sizeof(uint32_t) * 16)) goto fail;
+        const uint64_t rg = fomoe_b200_record_bytes(c, l);
+        if (rg > max_rec_ggml) max_rec_ggml = rg;
+    }
+    const int nl = cfg->n_layers, ne = cfg->n_embd;
+    if (dev_alloc(c, (void **)&c->x, sizeof(float) * ne) || dev_alloc(c, (void **)&c->h, sizeof(float) * ne) ||
+        dev_alloc(c, (void **)&c->moe_out, sizeof(float) * ne) ||
+        dev_alloc(c, (void **)&c->logits, sizeof(float) * nl * FB_MAX_EXPERTS) ||
+        dev_alloc(c, (void **)&c->all_scores, sizeof(float) * nl * FB_MAX_EXPERTS) ||
+        dev_alloc(c, (void **)&c->scores, sizeof(float) * nl * FB_MAX_SLOTS) ||
+        dev_alloc(c, (void **)&c->ids, sizeof(int) * nl * FB_MAX_SLOTS) ||
+        dev_alloc(c, (void **)&c->ids_orig, sizeof(int) * nl * FB_MAX_SLOTS) ||
+        dev_alloc(c, (void **)&c->slot_rec, sizeof(void *) * nl * FB_MAX_SLOTS) ||
+        dev_alloc(c, (void **)&c->act, sizeof(float) * FB_MAX_SLOTS * c->inter_local) ||
+        dev_alloc(c, (void **)&c->dots, sizeof(float) * FB_MAX_SLOTS * ne) ||
+        dev_alloc(c, (void **)&c->q8h, sizeof(fb_q8_entry_t) * (ne / FB_QK)) ||
+        dev_alloc(c, (void **)&c->q8a, sizeof(fb_q8_entry_t) * FB_MAX_SLOTS * (c->inter_local / FB_QK)) ||
+        dev_alloc(c, (void **)&c->counters, sizeof(unsigned) * (FB_CNT_WIN + FB_MAX_SLOTS * 32 + c->down_groups)) ||
+        dev_alloc(c, (void **)&c->status, sizeof(int)) || dev_alloc(c, (void **)&c->tok_ctr, sizeof(unsigned)) ||
+        dev_alloc(c, (void **)&c->tok_in, sizeof(float) * (uint64_t)c->max_tokens * ne) ||
+        dev_alloc(c, (void **)&c->tok_out, sizeof(float) * (uint64_t)c->max_tokens * ne))
+        goto fail;
+    c->stage_bytes = max_rec_ggml > sizeof(float) * (uint64_t)ne * 1024 ? max_rec_ggml : sizeof(float) * (uint64_t)ne * 1024;
+    if (cudaMalloc((void **)&c->stage, c->stage_bytes) != cudaSuccess) goto fail;
+    if (cudaHostAlloc((void **)&c->pin, sizeof(float) * (4 * (size_t)ne + 4 * FB_MAX_EXPERTS), cudaHostAllocDefault) !=
+        cudaSuccess)
+        goto fail;
+    return c;
+fail:
+    if (!c->err[0]) set_err(c, "CUDA setup failed: %s", cudaGetErrorString(cudaGetLastError()));
+    fomoe_b200_destroy(c);
+    return NULL;
+}
+
+const char *fomoe_b200_last_error(fomoe_b200_ctx_t *c) { return c ? c->err : "null context"; }
+
+int fomoe_b200_status(fomoe_b200_ctx_t *c) {
+    int st = -1;
+    if (!c) return -1;
+    cudaSetDevice(c->cfg.device);
+    if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1;
+    if (cudaMemcpy(&st, c->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return st;
+}
+
+uint64_t fomoe_b200_record_bytes(fomoe_b200_ctx_t *c, int layer) {
+    if (!c || layer < 0 || layer >= c->cfg.n_layers) return 0;
+    return 2 * ggml_matrix_bytes(c->cfg.gate_type, c->cfg.n_inter, c->cfg.n_embd) +
+           ggml_matrix_bytes(c->down_types[layer], c->cfg.n_embd, c->cfg.n_inter);
+}
+
+uint64_t fomoe_b200_table_bytes(fomoe_b200_ctx_t *c) { return c ? c->table_bytes : 0; }
+uint64_t fomoe_b200_kernel_launches(fomoe_b200_ctx_t *c) { return c ? c->launches : 0; }
+
+uint64_t fomoe_b200_substitutions(fomoe_b200_ctx_t *c) {
+    unsigned v = 0;
+    if (!c) return 0;
+    cudaSetDevice(c->cfg.device);
+    cudaStreamSynchronize(c->stream);
+    cudaMemcpy(&v, c->counters + FB_CNT_SUBS, sizeof(unsigned), cudaMemcpyDeviceToHost);
+    return v;
+}
+
+int fomoe_b200_set_graphs(fomoe_b200_ctx_t *c, int enable) {
+    if (!c) return -1;
+    c->use_graphs = enable ? 1 : 0;
+    if (!enable) drop_graph(c);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ table */
+int fomoe_b200_table_generate(fomoe_b200_ctx_t *c, uint64_t seed) {
+    if (!c) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    const int n_recs = c->cfg.n_experts + (c->cfg.has_shared ? 1 : 0);
+    for (int l = 0; l < c->cfg.n_layers; l++) {
+        fb_layer_t *L = &c->layers[l];
+        fb_shard_geom_t gg = geom_gate(c), gd = geom_down(c, L->down_type);
+        CKL(c, fb_launch_gen_shards(L->table, L->rec_bytes, n_recs, seed, (uint32_t)l, FSYN_M_GATE, gg, c->stream));
+        CKL(c, fb_launch_gen_shards(L->table + c->gate_bytes, L->rec_bytes, n_recs, seed, (uint32_t)l, FSYN_M_UP, gg,
+                                    c->stream));
+        CKL(c, fb_launch_gen_shards(L->table + 2 * c->gate_bytes, L->rec_bytes, n_recs, seed, (uint32_t)l, FSYN_M_DOWN,
+                                    gd, c->stream));
+        CKL(c, fb_launch_gen_f32(L->router_w, (uint64_t)c->cfg.n_experts * c->cfg.n_embd, seed, (uint32_t)l,
+                                 FSYN_M_ROUTER, 0.0f, FOMOE_ROUTER_STD, c->stream));
+        CKL(c, fb_launch_gen_f32(L->resid, (uint64_t)c->cfg.n_embd, seed, (uint32_t)l, FSYN_M_RESID, 0.0f,
+                                 FOMOE_RESID_STD, c->stream));
+        CKL(c, fb_launch_gen_f32(L->normw, (uint64_t)c->cfg.n_embd, seed, (uint32_t)l, FSYN_M_NORMW, FOMOE_NORMW_MEAN,
+                                 FOMOE_NORMW_STD, c->stream));
+    }
+    CK(c, cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+static int check_rec(fomoe_b200_ctx_t *c, int layer, int expert) {
+    const int n_recs = c->cfg.n_experts + (c->cfg.has_shared ? 1 : 0);
+    if (layer < 0 || layer >= c->cfg.n_layers || expert < 0 || expert >= n_recs) {
+        set_err(c, "layer %d / expert %d out of range", layer, expert);
+        return -1;
+    }
+    return 0;
+}
+
+/* enqueue: H2D of one ggml record + repack of its three matrices into record slot `expert` */
+static int upload_record(fomoe_b200_ctx_t *c, int layer, int expert, const void *record) {
+    fb_layer_t *L = &c->layers[layer];
+    const uint64_t gb = ggml_matrix_bytes(c->cfg.gate_type, c->cfg.n_inter, c->cfg.n_embd);
+    const uint64_t rb = fomoe_b200_record_bytes(c, layer);
+    uint8_t *dst = L->table + (uint64_t)expert * L->rec_bytes;
+    CK(c, cudaMemcpyAsync(c->stage, record, rb, cudaMemcpyHostToDevice, c->stream));
+    CKL(c, fb_launch_repack(dst, c->stage, geom_gate(c), c->stream));
+    CKL(c, fb_launch_repack(dst + c->gate_bytes, c->stage + gb, geom_gate(c), c->stream));
+    CKL(c, fb_launch_repack(dst + 2 * c->gate_bytes, c->stage + 2 * gb, geom_down(c, L->down_type), c->stream));
+    return 0;
+}
+
+int fomoe_b200_table_upload(fomoe_b200_ctx_t *c, int layer, int expert, const void *record) {
+    if (!c || !record || check_rec(c, layer, expert)) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    if (upload_record(c, layer, expert, record)) return -1;
+    CK(c, cudaStreamSynchronize(c->stream)); /* the staging buffer is reused by the next call */
+    return 0;
+}
+
+static int shard_of(fomoe_b200_ctx_t *c, int layer, int expert, int matrix, const uint8_t **shard,
+                    fb_shard_geom_t *g) {
+    if (check_rec(c, layer, expert) || matrix < 0 || matrix > 2) return -1;
+    fb_layer_t *L = &c->layers[layer];
+    const uint8_t *rec = L->table + (uint64_t)expert * L->rec_bytes;
+    *shard = rec + (matrix == 0 ? 0 : matrix == 1 ? c->gate_bytes : 2 * c->gate_bytes);
+    *g = matrix == 2 ? geom_down(c, L->down_type) : geom_gate(c);
+    return 0;
+}
+
+int fomoe_b200_table_export(fomoe_b200_ctx_t *c, int layer, int expert, int matrix, void *out) {
+    const uint8_t *shard;
+    fb_shard_geom_t g;
+    if (!c || !out || shard_of(c, layer, expert, matrix, &shard, &g)) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    const uint64_t bytes = (uint64_t)g.rows_local * g.bpr_local * fb_block_bytes(g.type);
+    CKL(c, fb_launch_export_ggml(c->stage, shard, g, c->stream));
+    CK(c, cudaMemcpyAsync(out, c->stage, bytes, cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+int fomoe_b200_table_dequant(fomoe_b200_ctx_t *c, int layer, int expert, int matrix, float *out) {
+    const uint8_t *shard;
+    fb_shard_geom_t g;
+    if (!c || !out || shard_of(c, layer, expert, matrix, &shard, &g)) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    const uint64_t bytes = sizeof(float) * (uint64_t)g.rows_local * g.bpr_local * FB_QK;
+    float *tmp = NULL;
+    CK(c, cudaMalloc((void **)&tmp, bytes));
+    int rc = fb_launch_dequant(tmp, shard, g, c->stream);
+    c->launches++;
+    cudaError_t e = rc ? (cudaError_t)rc : cudaMemcpyAsync(out, tmp, bytes, cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    cudaFree(tmp);
+    if (e != cudaSuccess) {
+        set_err(c, "table_dequant: %s", cudaGetErrorString(e));
+        return -1;
+    }
+    return 0;
+}
+
+int fomoe_b200_router_upload(fomoe_b200_ctx_t *c, int layer, const float *w) {
+    if (!c || !w || layer < 0 || layer >= c->cfg.n_layers) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    CK(c, cudaMemcpyAsync(c->layers[layer].router_w, w, sizeof(float) * (uint64_t)c->cfg.n_experts * c->cfg.n_embd,
+                          cudaMemcpyHostToDevice, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+int fomoe_b200_glue_upload(fomoe_b200_ctx_t *c, int layer, const float *resid, const float *normw) {
+    if (!c || layer < 0 || layer >= c->cfg.n_layers) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    if (resid)
+        CK(c, cudaMemcpyAsync(c->layers[layer].resid, resid, sizeof(float) * c->cfg.n_embd, cudaMemcpyHostToDevice,
+                              c->stream));
+    if (normw)
+        CK(c, cudaMemcpyAsync(c->layers[layer].normw, normw, sizeof(float) * c->cfg.n_embd, cudaMemcpyHostToDevice,
+                              c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+int fomoe_b200_set_resident_mask(fomoe_b200_ctx_t *c, int layer, const uint32_t *mask) {
+    if (!c || layer < 0 || layer >= c->cfg.n_layers) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    drop_graph(c);
+    c->layers[layer].mask_set = mask != NULL;
+    if (mask) {
+        CK(c, cudaMemcpyAsync(c->layers[layer].mask, mask, sizeof(uint32_t) * 16, cudaMemcpyHostToDevice, c->stream));
+        CK(c, cudaStreamSynchronize(c->stream));
+    }
+    return 0;
+}
+
+int fomoe_b200_set_car(fomoe_b200_ctx_t *c, float threshold, int dampen) {
+    if (!c) return -1;
+    drop_graph(c);
+    c->cfg.car_threshold = threshold;
+    c->cfg.car_dampen = dampen ? 1 : 0;
+    return 0;
+}
+
+/* ------------------------------------------------------------------ launch sequence */
+static void fill_args(const fomoe_b200_ctx_t *c, int layer, fb_args_t *a) {
+    const fb_layer_t *L = &c->layers[layer];
+    memset(a, 0, sizeof(*a));
+    a->n_embd = c->cfg.n_embd;
+    a->n_inter = c->cfg.n_inter;
+    a->inter_local = c->inter_local;
+    a->n_experts = c->cfg.n_experts;
+    a->top_k = c->cfg.top_k;
+    a->has_shared = c->cfg.has_shared ? 1 : 0;
+    a->n_slots = c->n_slots;
+    a->tp_rank = c->cfg.tp_rank;
+    a->tp_size = c->cfg.tp_size;
+    a->gate_bpr = c->gate_bpr;
+    a->down_bpr = c->down_bpr;
+    a->gate_groups = c->gate_groups;
+    a->down_groups = c->down_groups;
+    a->up_off = c->gate_bytes;
+    a->down_off = 2 * c->gate_bytes;
+    a->rms_eps = c->cfg.rms_eps;
+    a->car_threshold = c->cfg.car_threshold;
+    a->car_dampen = c->cfg.car_dampen;
+    a->table_layer = L->table;
+    a->rec_bytes = L->rec_bytes;
+    a->down_type = L->down_type;
+    a->router_w = L->router_w;
+    a->resid = L->resid;
+    a->normw = L->normw;
+    a->resident = L->mask_set ? L->mask : NULL;
+    a->freq = c->freq ? c->freq + (size_t)layer * c->cfg.n_experts : NULL;
+    a->x = c->x;
+    a->h = c->h;
+    a->moe_out = c->moe_out;
+    a->q8h = c->q8h;
+    a->logits = c->logits + (size_t)layer * FB_MAX_EXPERTS;
+    a->all_scores = c->all_scores + (size_t)layer * FB_MAX_EXPERTS;
+    a->ids = c->ids + (size_t)layer * FB_MAX_SLOTS;
+    a->ids_orig = c->ids_orig + (size_t)layer * FB_MAX_SLOTS;
+    a->scores = c->scores + (size_t)layer * FB_MAX_SLOTS;
+    a->slot_rec = c->slot_rec + (size_t)layer * FB_MAX_SLOTS;
+    a->act = c->act;
+    a->q8a = c->q8a;
+    a->dots = c->dots;
+    a->counters = c->counters;
+    a->status = c->status;
+    a->tok_in = c->tok_in;
+    a->tok_out = c->tok_out;
+    a->tok_ctr = c->tok_ctr;
+}
+
+static int grid_router(const fomoe_b200_ctx_t *c) {
+    int g = (c->cfg.n_experts + 7) / 8;
+    return g < 1 ? 1 : g;
+}
+
+static int grid_tasks(const fomoe_b200_ctx_t *c, int tasks) {
+    /* 8 warps per block; up to 2 blocks per SM */
+    int g = (tasks + 7) / 8, cap = 2 * c->n_sm;
+    return g < 1 ? 1 : (g > cap ? cap : g);
+}
+
+/* expert phase of one layer: gate/up/SwiGLU then down/combine, on the slots already set */
+static int enqueue_experts(fomoe_b200_ctx_t *c, const fb_args_t *a) {
+    CKL(c, fb_launch_gate_up(a, grid_tasks(c, a->n_slots * a->gate_groups), c->stream));
+    CKL(c, fb_launch_down(a, grid_tasks(c, a->n_slots * a->down_groups), c->stream));
+    return 0;
+}
+
+/* layers [l0, l1) of one token; flags_first / store select where x comes from and goes to */
+static int enqueue_stack(fomoe_b200_ctx_t *c, int l0, int l1, int load_store) {
+    fb_args_t a;
+    for (int l = l0; l < l1; l++) {
+        fill_args(c, l, &a);
+        int flags = FB_PRO_RESID | FB_PRO_NORM | FB_PRO_QUANT;
+        if (l > l0) flags |= FB_PRO_ADD_PREV;
+        else if (load_store) flags |= FB_PRO_LOAD;
+        CKL(c, fb_launch_prologue(&a, flags, c->stream));
+        CKL(c, fb_launch_router(&a, grid_router(c), c->stream));
+        if (enqueue_experts(c, &a)) return -1;
+    }
+    fill_args(c, l1 - 1, &a);
+    CKL(c, fb_launch_prologue(&a, FB_PRO_ADD_PREV | (load_store ? FB_PRO_STORE : 0), c->stream));
+    return 0;
+}
+
+int fomoe_b200_moe_layer(fomoe_b200_ctx_t *c, int layer, const float *h, float *out, int *ids_out, float *scores_out,
+                         int *ids_orig_out, float *all_scores_out) {
+    if (!c || !h || !out || layer < 0 || layer >= c->cfg.n_layers) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    const size_t nb = sizeof(float) * c->cfg.n_embd;
+    fb_args_t a;
+    fill_args(c, layer, &a);
+    memcpy(c->pin, h, nb);
+    CK(c, cudaMemcpyAsync(c->x, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
+    CKL(c, fb_launch_prologue(&a, FB_PRO_QUANT, c->stream));
+    CKL(c, fb_launch_router(&a, grid_router(c), c->stream));
+    if (enqueue_experts(c, &a)) return -1;
+    CK(c, cudaMemcpyAsync(c->pin + c->cfg.n_embd, c->moe_out, nb, cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    memcpy(out, c->pin + c->cfg.n_embd, nb);
+    if (ids_out || scores_out || ids_orig_out) {
+        if (fomoe_b200_get_routing(c, layer, ids_out, scores_out, ids_orig_out)) return -1;
+    }
+    if (all_scores_out)
+        CK(c, cudaMemcpy(all_scores_out, a.all_scores, sizeof(float) * c->cfg.n_experts, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+/* shared by moe_layer_routed and the operator surfaces: n experts given by the caller */
+static int run_routed(fomoe_b200_ctx_t *c, int layer, const float *h, const int *ids, const float *scores, int n,
+                      int with_shared, int accumulate, float *out, int sync) {
+    if (n < 1 || n > FB_MAX_TOPK) {
+        set_err(c, "n experts %d out of range", n);
+        return -1;
+    }
+    const size_t nb = sizeof(float) * c->cfg.n_embd;
+    fb_args_t a;
+    if (c->pin_busy) {
+        CK(c, cudaStreamSynchronize(c->stream));
+        c->pin_busy = 0;
+    }
+    fill_args(c, layer, &a);
+    a.top_k = n;
+    a.has_shared = with_shared ? 1 : 0;
+    a.n_slots = n + a.has_shared;
+    a.accumulate = accumulate;
+    int *pi = (int *)(c->pin + 2 * c->cfg.n_embd);
+    float *ps = (float *)(pi + FB_MAX_SLOTS);
+    if (h) {
+        memcpy(c->pin, h, nb);
+        CK(c, cudaMemcpyAsync(c->x, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
+        CKL(c, fb_launch_prologue(&a, FB_PRO_QUANT, c->stream));
+    }
+    for (int i = 0; i < n; i++) {
+        pi[i] = ids[i];
+        ps[i] = scores[i];
+    }
+    CK(c, cudaMemcpyAsync(a.ids, pi, sizeof(int) * n, cudaMemcpyHostToDevice, c->stream));
+    CK(c, cudaMemcpyAsync(a.scores, ps, sizeof(float) * n, cudaMemcpyHostToDevice, c->stream));
+    CKL(c, fb_launch_set_slots(&a, c->stream));
+    if (enqueue_experts(c, &a)) return -1;
+    if (out) CK(c, cudaMemcpyAsync(c->pin + c->cfg.n_embd, c->moe_out, nb, cudaMemcpyDeviceToHost, c->stream));
+    if (sync) {
+        CK(c, cudaStreamSynchronize(c->stream));
+        if (out) memcpy(out, c->pin + c->cfg.n_embd, nb);
+    } else {
+        c->pin_busy = 1;
+    }
+    return 0;
+}
+
+int fomoe_b200_moe_layer_routed(fomoe_b200_ctx_t *c, int layer, const float *h, const int *ids, const float *scores,
+                                int n, float *out) {
+    if (!c || !h || !ids || !scores || !out || layer < 0 || layer >= c->cfg.n_layers) return -1;
+    if (n > c->cfg.top_k) {
+        set_err(c, "n %d exceeds top_k %d", n, c->cfg.top_k);
+        return -1;
+    }
+    CK(c, cudaSetDevice(c->cfg.device));
+    return run_routed(c, layer, h, ids, scores, n, c->cfg.has_shared, 0, out, 1);
+}
+
+int fomoe_b200_stack_run(fomoe_b200_ctx_t *c, const float *x_in, int l0, int l1, float *x_out) {
+    if (!c || !x_in || !x_out || l0 < 0 || l1 > c->cfg.n_layers || l0 >= l1) return -1;
+    if (c->cfg.tp_size > 1) {
+        set_err(c, "stack_run on a tensor-parallel rank needs the all-reduce hook; use the per-layer calls");
+        return -1;
+    }
+    CK(c, cudaSetDevice(c->cfg.device));
+    const size_t nb = sizeof(float) * c->cfg.n_embd;
+    memcpy(c->pin, x_in, nb);
+    CK(c, cudaMemcpyAsync(c->x, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
+    if (enqueue_stack(c, l0, l1, 0)) return -1;
+    CK(c, cudaMemcpyAsync(c->pin + c->cfg.n_embd, c->x, nb, cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    memcpy(x_out, c->pin + c->cfg.n_embd, nb);
+    return 0;
+}
+
+int fomoe_b200_tokens_upload(fomoe_b200_ctx_t *c, int first, int count, const float *x) {
+    if (!c || !x || first < 0 || count < 1 || first + count > c->max_tokens) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    CK(c, cudaMemcpyAsync(c->tok_in + (size_t)first * c->cfg.n_embd, x, sizeof(float) * (size_t)count * c->cfg.n_embd,
+                          cudaMemcpyHostToDevice, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+int fomoe_b200_tokens_download(fomoe_b200_ctx_t *c, int first, int count, float *x_out) {
+    if (!c || !x_out || first < 0 || count < 1 || first + count > c->max_tokens) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    CK(c, cudaMemcpyAsync(x_out, c->tok_out + (size_t)first * c->cfg.n_embd,
+                          sizeof(float) * (size_t)count * c->cfg.n_embd, cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+static int build_graph(fomoe_b200_ctx_t *c) {
+    cudaGraph_t g = NULL;
+    const uint64_t before = c->launches;
+    CK(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_stack(c, 0, c->cfg.n_layers, 1);
+    cudaError_t e = cudaStreamEndCapture(c->stream, &g);
+    c->graph_nodes = (int)(c->launches - before);
+    c->launches = before;
+    if (rc || e != cudaSuccess || !g) {
+        if (g) cudaGraphDestroy(g);
+        set_err(c, "graph capture failed: %s", cudaGetErrorString(e));
+        return -1;
+    }
+    e = cudaGraphInstantiate(&c->graph_exec, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) {
+        c->graph_exec = NULL;
+        set_err(c, "graph instantiate failed: %s", cudaGetErrorString(e));
+        return -1;
+    }
+    return 0;
+}
+
+int fomoe_b200_tokens_run(fomoe_b200_ctx_t *c, int first, int count, float *elapsed_ms) {
+    if (!c || first < 0 || count < 1 || first + count > c->max_tokens) return -1;
+    if (c->cfg.tp_size > 1) {
+        set_err(c, "tokens_run on a tensor-parallel rank needs the all-reduce hook");
+        return -1;
+    }
+    CK(c, cudaSetDevice(c->cfg.device));
+    if (c->use_graphs && !c->graph_exec && build_graph(c)) return -1;
+    unsigned f = (unsigned)first;
+    CK(c, cudaMemcpyAsync(c->tok_ctr, &f, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
+    CK(c, cudaEventRecord(c->ev0, c->stream));
+    for (int t = 0; t < count; t++) {
+        if (c->use_graphs) {
+            CK(c, cudaGraphLaunch(c->graph_exec, c->stream));
+            c->launches += (uint64_t)c->graph_nodes;
+        } else if (enqueue_stack(c, 0, c->cfg.n_layers, 1))
+            return -1;
+    }
+    CK(c, cudaEventRecord(c->ev1, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    if (elapsed_ms) CK(c, cudaEventElapsedTime(elapsed_ms, c->ev0, c->ev1));
+    return 0;
+}
+
+/* records an event before each kernel launch while profiling; the phase is read off the call text */
+static void prof_mark(fomoe_b200_ctx_t *c, const char *call) {
+    if (c->pev_n >= c->pev_cap) return;
+    int ph = strstr(call, "prologue") ? 0 : strstr(call, "router") ? 1 : strstr(call, "gate_up") ? 2
+           : strstr(call, "fb_launch_down") ? 3 : 4;
+    c->pev_phase[c->pev_n] = ph;
+    cudaEventRecord(c->pev[c->pev_n++], c->stream);
+}
+
+int fomoe_b200_tokens_profile(fomoe_b200_ctx_t *c, int first, int count, float *phase_ms, int *phase_launches) {
+    if (!c || !phase_ms || first < 0 || count < 1 || first + count > c->max_tokens) return -1;
+    if (c->cfg.tp_size > 1) {
+        set_err(c, "tokens_profile: single-rank only");
+        return -1;
+    }
+    CK(c, cudaSetDevice(c->cfg.device));
+    const int per_tok = 4 * c->cfg.n_layers + 1, need = per_tok * count + 1;
+    if (c->pev_cap < need) {
+        for (int i = 0; i < c->pev_cap; i++) cudaEventDestroy(c->pev[i]);
+        free(c->pev);
+        free(c->pev_phase);
+        c->pev = (cudaEvent_t *)calloc((size_t)need, sizeof(cudaEvent_t));
+        c->pev_phase = (int *)calloc((size_t)need, sizeof(int));
+        c->pev_cap = 0;
+        for (int i = 0; i < need; i++) {
+            CK(c, cudaEventCreate(&c->pev[i]));
+            c->pev_cap = i + 1;
+        }
+    }
+    unsigned f = (unsigned)first;
+    CK(c, cudaMemcpyAsync(c->tok_ctr, &f, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
+    c->pev_n = 0;
+    c->profiling = 1;
+    int rc = 0;
+    for (int t = 0; t < count && !rc; t++) rc = enqueue_stack(c, 0, c->cfg.n_layers, 1);
+    c->profiling = 0;
+    if (rc) return -1;
+    c->pev_phase[c->pev_n] = -1;
+    CK(c, cudaEventRecord(c->pev[c->pev_n], c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    for (int i = 0; i < 5; i++) phase_ms[i] = 0.0f;
+    if (phase_launches) for (int i = 0; i < 4; i++) phase_launches[i] = 0;
+    for (int i = 0; i < c->pev_n; i++) {
+        float ms = 0.0f;
+        CK(c, cudaEventElapsedTime(&ms, c->pev[i], c->pev[i + 1]));
+        const int ph = c->pev_phase[i];
+        if (ph >= 0 && ph < 4) {
+            phase_ms[ph] += ms;
+            if (phase_launches) phase_launches[ph]++;
+        }
+    }
+    CK(c, cudaEventElapsedTime(&phase_ms[4], c->pev[0], c->pev[c->pev_n]));
+    return 0;
+}
+
+int fomoe_b200_decode_token(fomoe_b200_ctx_t *c, const float *x_in, float *x_out) {
+    if (!c || !x_in || !x_out) return -1;
+    if (c->cfg.tp_size > 1) {
+        set_err(c, "decode_token on a tensor-parallel rank needs the all-reduce hook");
+        return -1;
+    }
+    CK(c, cudaSetDevice(c->cfg.device));
+    if (c->use_graphs && !c->graph_exec && build_graph(c)) return -1;
+    const size_t nb = sizeof(float) * c->cfg.n_embd;
+    unsigned *zero = (unsigned *)(c->pin + 2 * c->cfg.n_embd);
+    *zero = 0;
+    memcpy(c->pin, x_in, nb);
+    CK(c, cudaMemcpyAsync(c->tok_in, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
+    CK(c, cudaMemcpyAsync(c->tok_ctr, zero, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
+    if (c->use_graphs) {
+        CK(c, cudaGraphLaunch(c->graph_exec, c->stream));
+        c->launches += (uint64_t)c->graph_nodes;
+    } else if (enqueue_stack(c, 0, c->cfg.n_layers, 1))
+        return -1;
+    CK(c, cudaMemcpyAsync(c->pin + c->cfg.n_embd, c->tok_out, nb, cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    memcpy(x_out, c->pin + c->cfg.n_embd, nb);
+    return 0;
+}
+
+int fomoe_b200_get_routing(fomoe_b200_ctx_t *c, int layer, int *ids, float *scores, int *ids_orig) {
+    if (!c || layer < 0 || layer >= c->cfg.n_layers) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    const int k = c->cfg.top_k;
+    if (ids) CK(c, cudaMemcpy(ids, c->ids + (size_t)layer * FB_MAX_SLOTS, sizeof(int) * k, cudaMemcpyDeviceToHost));
+    if (scores)
+        CK(c, cudaMemcpy(scores, c->scores + (size_t)layer * FB_MAX_SLOTS, sizeof(float) * k, cudaMemcpyDeviceToHost));
+    if (ids_orig)
+        CK(c, cudaMemcpy(ids_orig, c->ids_orig + (size_t)layer * FB_MAX_SLOTS, sizeof(int) * k, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int fomoe_b200_peek(fomoe_b200_ctx_t *c, int what, void *out, uint64_t bytes) {
+    if (!c || !out) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    const void *src = NULL;
+    uint64_t cap = 0;
+    switch (what) {
+        case 0: src = c->act; cap = sizeof(float) * FB_MAX_SLOTS * (uint64_t)c->inter_local; break;
+        case 1: src = c->q8a; cap = sizeof(fb_q8_entry_t) * FB_MAX_SLOTS * (uint64_t)(c->inter_local / FB_QK); break;
+        case 2: src = c->q8h; cap = sizeof(fb_q8_entry_t) * (uint64_t)(c->cfg.n_embd / FB_QK); break;
+        case 3: src = c->dots; cap = sizeof(float) * FB_MAX_SLOTS * (uint64_t)c->cfg.n_embd; break;
+        case 4: src = c->h; cap = sizeof(float) * (uint64_t)c->cfg.n_embd; break;
+        default: set_err(c, "peek: unknown selector %d", what); return -1;
+    }
+    if (bytes > cap) {
+        set_err(c, "peek: %llu bytes requested, %llu available", (unsigned long long)bytes, (unsigned long long)cap);
+        return -1;
+    }
+    CK(c, cudaStreamSynchronize(c->stream));
+    CK(c, cudaMemcpy(out, src, bytes, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+/* ------------------------------------------------------------------ micro helpers */
+int fomoe_b200_matvec(fomoe_b200_ctx_t *c, int type, const void *w, int rows, int cols, const float *x, float *y) {
+    if (!c || !w || !x || !y || rows < 1 || cols % FB_QK || cols < FB_QK) return -1;
+    const int bpr = cols / FB_QK;
+    if ((type != FB_TYPE_Q4_K && type != FB_TYPE_Q6_K) || !is_pow2(bpr) || bpr > 32) {
+        set_err(c, "matvec: unsupported type %d / cols %d", type, cols);
+        return -1;
+    }
+    CK(c, cudaSetDevice(c->cfg.device));
+    fb_shard_geom_t g = {type, rows, bpr, 0, 0, bpr};
+    const uint64_t wb = ggml_matrix_bytes(type, rows, cols), sb = fb_shard_bytes(type, (uint64_t)rows * bpr);
+    uint8_t *dw = NULL, *ds = NULL;
+    float *dx = NULL, *dy = NULL;
+    fb_q8_entry_t *dq = NULL;
+    int rc = -1;
+    if (cudaMalloc((void **)&dw, wb) || cudaMalloc((void **)&ds, sb) || cudaMalloc((void **)&dx, sizeof(float) * cols) ||
+        cudaMalloc((void **)&dy, sizeof(float) * rows) || cudaMalloc((void **)&dq, sizeof(fb_q8_entry_t) * bpr)) {
+        set_err(c, "matvec: allocation failed");
+        goto done;
+    }
+    if (cudaMemcpyAsync(dw, w, wb, cudaMemcpyHostToDevice, c->stream) ||
+        cudaMemcpyAsync(dx, x, sizeof(float) * cols, cudaMemcpyHostToDevice, c->stream))
+        goto done;
+    c->launches += 3;
+    if (fb_launch_repack(ds, dw, g, c->stream) || fb_launch_quantize(dq, dx, bpr, c->stream) ||
+        fb_launch_matvec(dy, ds, g, dq, grid_tasks(c, (int)fb_n_groups((uint64_t)rows * bpr)), c->stream))
+        goto done;
+    if (cudaMemcpyAsync(y, dy, sizeof(float) * rows, cudaMemcpyDeviceToHost, c->stream) ||
+        cudaStreamSynchronize(c->stream))
+        goto done;
+    rc = 0;
+done:
+    if (rc) set_err(c, "matvec failed: %s", cudaGetErrorString(cudaGetLastError()));
+    cudaFree(dw); cudaFree(ds); cudaFree(dx); cudaFree(dy); cudaFree(dq);
+    return rc;
+}
+
+int fomoe_b200_quantize_q8k(fomoe_b200_ctx_t *c, const float *x, int n, void *out) {
+    if (!c || !x || !out || n % FB_QK || n < FB_QK) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    const int nb = n / FB_QK;
+    float *dx = NULL;
+    fb_q8_entry_t *dq = NULL, *hq = (fb_q8_entry_t *)malloc(sizeof(fb_q8_entry_t) * (size_t)nb);
+    int rc = -1;
+    if (!hq || cudaMalloc((void **)&dx, sizeof(float) * n) || cudaMalloc((void **)&dq, sizeof(fb_q8_entry_t) * nb)) goto done;
+    if (cudaMemcpyAsync(dx, x, sizeof(float) * n, cudaMemcpyHostToDevice, c->stream)) goto done;
+    c->launches++;
+    if (fb_launch_quantize(dq, dx, nb, c->stream)) goto done;
+    if (cudaMemcpyAsync(hq, dq, sizeof(fb_q8_entry_t) * nb, cudaMemcpyDeviceToHost, c->stream) ||
+        cudaStreamSynchronize(c->stream))
+        goto done;
+    for (int b = 0; b < nb; b++) { /* back to the reference's block_q8_K order: d, qs, bsums (292 B) */
+        uint8_t *o = (uint8_t *)out + (size_t)b * 292;
+        memcpy(o, &hq[b].d, 4);
+        memcpy(o + 4, hq[b].qs, 256);
+        memcpy(o + 260, hq[b].bsums, 32);
+    }
+    rc = 0;
+done:
+    if (rc) set_err(c, "quantize failed: %s", cudaGetErrorString(cudaGetLastError()));
+    cudaFree(dx); cudaFree(dq); free(hq);
+    return rc;
+}
+
+/* ------------------------------------------------------------------ host-side generator */
+void fomoe_b200_synth_matrix(uint64_t seed, int layer, int expert, int matrix, int type, int rows, int cols,
+                             void *out) {
+    const uint64_t key = fsyn_key(seed, (uint32_t)layer, (uint32_t)expert, (uint32_t)matrix);
+    const uint64_t nblk = (uint64_t)rows * (uint64_t)(cols / FB_QK);
+    uint8_t *o = (uint8_t *)out;
+    for (uint64_t b = 0; b < nblk; b++) {
+        if (type == FB_TYPE_Q4_K) {
+            uint32_t w[36];
+            fsyn_q4k_block(key, b, w);
+            memcpy(o + b * FB_Q4K_BLOCK, w, FB_Q4K_BLOCK);
+        } else {
+            uint32_t ql[32], qh[16], sc[4];
+            uint16_t d;
+            fsyn_q6k_block(key, b, ql, qh, sc, &d);
+            uint8_t *p = o + b * FB_Q6K_BLOCK;
+            memcpy(p, ql, 128);
+            memcpy(p + 128, qh, 64);
+            memcpy(p + 192, sc, 16);
+            memcpy(p + 208, &d, 2);
+        }
+    }
+}
+
+void fomoe_b200_synth_f32(uint64_t seed, int layer, int stream_id, float mean, float std, uint64_t n, float *out) {
+    const uint64_t key = fsyn_key(seed, (uint32_t)layer, 0, (uint32_t)stream_id);
+    for (uint64_t i = 0; i < n; i++) out[i] = fsyn_f32(key, i, mean, std);
+}
+
+/* ======================================================================================
+ * Reference GPU surface (include/gpu.h) and the cpu_expert twin, both on a one-layer
+ * engine whose "table" is just the experts of the current call.
+ * ====================================================================================== */
+#define OP_MAX_EXPERTS 10        /* MAX_EXPERTS,        src/gpu_kernels.hip:438-448 */
+#define OP_MAX_EMBD 4096         /* MAX_N_EMBD */
+#define OP_MAX_INTER 2048        /* MAX_INTERMEDIATE */
+#define OP_MAX_STRIDE (12ull << 20)
+#define OP_MAX_WORK 16           /* CPU_EXPERT_MAX_WORK, src/cpu_expert.c:12 */
+
+typedef struct {
+    fomoe_b200_ctx_t *eng;
+    int n_embd, inter, down_type;
+} op_engine_t;
+
+static int op_engine_get(op_engine_t *o, int n_embd, int inter, int down_type) {
+    if (o->eng && o->n_embd == n_embd && o->inter == inter && o->down_type == down_type) return 0;
+    if (o->eng) fomoe_b200_destroy(o->eng);
+    o->eng = NULL;
+    fomoe_b200_config_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cfg.device = dev;
+    cfg.n_layers = 1;
+    cfg.n_embd = n_embd;
+    cfg.n_inter = inter;
+    cfg.n_experts = OP_MAX_WORK;
+    cfg.top_k = FB_MAX_TOPK;
+    cfg.has_shared = 0;
+    cfg.gate_type = FB_TYPE_Q4_K;
+    cfg.down_types = &down_type;
+    cfg.tp_rank = 0;
+    cfg.tp_size = 1;
+    cfg.rms_eps = 1e-6f;
+    cfg.car_threshold = 1.0f;
+    o->eng = fomoe_b200_create(&cfg);
+    if (!o->eng) return -1;
+    o->n_embd = n_embd;
+    o->inter = inter;
+    o->down_type = down_type;
+    return 0;
+}
+
+struct gpu_ctx {
+    op_engine_t op;
+    uint32_t *freq_host;
+    int freq_enabled;
+};
+
+gpu_ctx_t *gpu_init(void) {
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) {
+        fprintf(stderr, "gpu_init: no CUDA device\n");
+        return NULL;
+    }
+    if (cudaSetDevice(0) != cudaSuccess) return NULL;
+    return (gpu_ctx_t *)calloc(1, sizeof(gpu_ctx_t));
+}
+
+void gpu_free(gpu_ctx_t *ctx) {
+    if (!ctx) return;
+    if (ctx->op.eng) fomoe_b200_destroy(ctx->op.eng);
+    free(ctx->freq_host);
+    free(ctx);
+}
+
+void gpu_register_buffers(gpu_ctx_t *ctx, void **buffers, int n, uint64_t size) {
+    (void)ctx;
+    for (int i = 0; i < n; i++)
+        if (buffers && buffers[i] && cudaHostRegister(buffers[i], size, cudaHostRegisterDefault) != cudaSuccess) {
+            cudaGetLastError();
+            fprintf(stderr, "gpu_register_buffers: buffer %d not pinned\n", i);
+        }
+}
+
+void gpu_unregister_buffers(gpu_ctx_t *ctx, void **buffers, int n) {
+    (void)ctx;
+    for (int i = 0; i < n; i++)
+        if (buffers && buffers[i] && cudaHostUnregister(buffers[i]) != cudaSuccess) cudaGetLastError();
+}
+
+int gpu_upload_model(gpu_ctx_t *ctx, const void *model) {
+    (void)ctx; (void)model;
+    fprintf(stderr, "gpu_upload_model: whole-model engine is not part of this library\n");
+    return -1;
+}
+void gpu_set_ram_cache_mb(gpu_ctx_t *ctx, int mb) { (void)ctx; (void)mb; }
+void gpu_set_vram_cache_mb(gpu_ctx_t *ctx, int mb) { (void)ctx; (void)mb; }
+float *gpu_forward(gpu_ctx_t *ctx, void *model, int token_id, int pos) {
+    (void)ctx; (void)model; (void)token_id; (void)pos;
+    return NULL;
+}
+void gpu_reset_state(gpu_ctx_t *ctx) { (void)ctx; }
+int gpu_seed_vram_cache(gpu_ctx_t *ctx, void *model, const char *path) {
+    (void)ctx; (void)model; (void)path;
+    return 0;
+}
+void gpu_enable_expert_freq(gpu_ctx_t *ctx) {
+    if (ctx) ctx->freq_enabled = 1;
+}
+const uint32_t *gpu_get_expert_freq(gpu_ctx_t *ctx) {
+    (void)ctx;
+    return NULL; /* the operator form receives its routing from the caller; nothing to count */
+}
+void gpu_get_expert_dims(gpu_ctx_t *ctx, int *n_layers, int *n_experts) {
+    (void)ctx;
+    if (n_layers) *n_layers = 0;
+    if (n_experts) *n_experts = 0;
+}
+void gpu_get_pingpong_relay_stats(gpu_ctx_t *ctx, uint64_t *handoffs, uint64_t *payload_bytes, uint64_t *d2h_bytes,
+                                  uint64_t *h2d_bytes, uint64_t *dma_bytes) {
+    (void)ctx;
+    if (handoffs) *handoffs = 0;
+    if (payload_bytes) *payload_bytes = 0;
+    if (d2h_bytes) *d2h_bytes = 0;
+    if (h2d_bytes) *h2d_bytes = 0;
+    if (dma_bytes) *dma_bytes = 0;
+}
+
+static int op_types_ok(int gate_type, int up_type, int down_type) {
+    return gate_type == FB_TYPE_Q4_K && up_type == FB_TYPE_Q4_K &&
+           (down_type == FB_TYPE_Q4_K || down_type == FB_TYPE_Q6_K);
+}
+
+int gpu_expert_ffn(gpu_ctx_t *ctx, const float *h, void **expert_buffers, const float *expert_scores, int n_experts,
+                   int n_embd, int expert_intermediate, uint64_t expert_gate_size, uint64_t expert_up_size,
+                   uint64_t expert_stride, int gate_type, int up_type, int down_type, float *ffn_out) {
+    if (!ctx || !h || !expert_buffers || !expert_scores || !ffn_out) return -1;
+    if (n_experts < 1 || n_experts > OP_MAX_EXPERTS || n_embd > OP_MAX_EMBD || expert_intermediate > OP_MAX_INTER ||
+        expert_stride > OP_MAX_STRIDE || !op_types_ok(gate_type, up_type, down_type))
+        return -1;
+    if (n_embd % FB_QK || expert_intermediate % FB_QK) return -1;
+    if (expert_gate_size != ggml_matrix_bytes(gate_type, expert_intermediate, n_embd) ||
+        expert_up_size != ggml_matrix_bytes(up_type, expert_intermediate, n_embd))
+        return -1;
+    if (op_engine_get(&ctx->op, n_embd, expert_intermediate, down_type)) return -1;
+    fomoe_b200_ctx_t *c = ctx->op.eng;
+    int ids[OP_MAX_EXPERTS];
+    for (int e = 0; e < n_experts; e++) {
+        if (!expert_buffers[e] || upload_record(c, 0, e, expert_buffers[e])) return -1;
+        if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1; /* staging buffer reuse */
+        ids[e] = e;
+    }
+    return run_routed(c, 0, h, ids, expert_scores, n_experts, 0, 0, ffn_out, 1);
+}
+
+struct b200_expert_ctx {
+    op_engine_t op;
+    int n_embd, inter;
+    float *partial; /* host copy handed out by b200_expert_result */
+    int input_valid; /* the hidden state of this layer is already quantised on the device */
+    int dirty;       /* device accumulator holds something */
+    double total_us;
+    int samples;
+    cudaEvent_t e0, e1;
+    int timing_pending;
+};
+
+b200_expert_ctx_t *b200_expert_create(int n_embd, int expert_intermediate) {
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) return NULL;
+    if (n_embd % FB_QK || expert_intermediate % FB_QK || n_embd < FB_QK || expert_intermediate < FB_QK) return NULL;
+    b200_expert_ctx_t *x = (b200_expert_ctx_t *)calloc(1, sizeof(*x));
+    if (!x) return NULL;
+    x->n_embd = n_embd;
+    x->inter = expert_intermediate;
+    x->partial = (float *)calloc((size_t)n_embd, sizeof(float));
+    if (!x->partial || cudaEventCreate(&x->e0) != cudaSuccess || cudaEventCreate(&x->e1) != cudaSuccess) {
+        free(x->partial);
+        free(x);
+        return NULL;
+    }
+    return x;
+}
+
+void b200_expert_free(b200_expert_ctx_t *x) {
+    if (!x) return;
+    if (x->op.eng) fomoe_b200_destroy(x->op.eng);
+    cudaEventDestroy(x->e0);
+    cudaEventDestroy(x->e1);
+    free(x->partial);
+    free(x);
+}
+
+void b200_expert_reset(b200_expert_ctx_t *x) {
+    if (!x) return;
+    x->input_valid = 0;
+    x->dirty = 0;
+    if (x->op.eng) {
+        cudaSetDevice(x->op.eng->cfg.device);
+        cudaMemsetAsync(x->op.eng->moe_out, 0, sizeof(float) * (size_t)x->n_embd, x->op.eng->stream);
+    }
+}
+
+static int expert_batch(b200_expert_ctx_t *x, const float *input, const b200_expert_work_t *work, int n, int accumulate) {
+    for (int i = 0; i < n; i++)
+        if (!op_types_ok(work[i].gate_type, work[i].up_type, work[i].down_type) ||
+            work[i].down_type != work[0].down_type || !work[i].expert_data)
+            return -1;
+    const int had = x->op.eng != NULL;
+    if (op_engine_get(&x->op, x->n_embd, x->inter, work[0].down_type)) return -1;
+    fomoe_b200_ctx_t *c = x->op.eng;
+    if (!had || !x->dirty) cudaMemsetAsync(c->moe_out, 0, sizeof(float) * (size_t)x->n_embd, c->stream);
+    int ids[OP_MAX_WORK];
+    float sc[OP_MAX_WORK];
+    cudaEventRecord(x->e0, c->stream);
+    for (int i = 0; i < n; i++) {
+        if (upload_record(c, 0, i, work[i].expert_data)) return -1;
+        if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1;
+        ids[i] = i;
+        sc[i] = work[i].score;
+    }
+    /* at most FB_MAX_TOPK experts per launch */
+    int done = 0;
+    while (done < n) {
+        const int m = n - done > FB_MAX_TOPK ? FB_MAX_TOPK : n - done;
+        if (run_routed(c, 0, (done == 0 && !x->input_valid) ? input : NULL, ids + done, sc + done, m, 0,
+                       accumulate || done > 0, NULL, 0))
+            return -1;
+        x->input_valid = 1;
+        done += m;
+    }
+    cudaEventRecord(x->e1, c->stream);
+    x->timing_pending = 1;
+    x->dirty = 1;
+    return 0;
+}
+
+void b200_expert_ffn(b200_expert_ctx_t *x, const void *expert_data, const float *input, float score, int gate_type,
+                     int up_type, int down_type, uint64_t expert_gate_size, uint64_t expert_up_size) {
+    if (!x || !expert_data || !input) return;
+    b200_expert_work_t w = {expert_data, score, gate_type, up_type, down_type, expert_gate_size, expert_up_size};
+    if (expert_batch(x, input, &w, 1, 1)) fprintf(stderr, "b200_expert_ffn: unsupported expert or CUDA failure\n");
+    b200_expert_wait(x);
+}
+
+void b200_expert_submit_async(b200_expert_ctx_t *x, const float *input, const b200_expert_work_t *work, int n_work) {
+    if (!x || !input || !work || n_work <= 0) return;
+    if (n_work > OP_MAX_WORK) n_work = OP_MAX_WORK; /* src/cpu_expert.c:246 */
+    b200_expert_reset(x);                            /* a batch starts from zero, src/cpu_expert.c:141-142 */
+    if (expert_batch(x, input, work, n_work, 0)) fprintf(stderr, "b200_expert_submit_async: unsupported expert or CUDA failure\n");
+}
+
+void b200_expert_wait(b200_expert_ctx_t *x) {
+    if (!x || !x->op.eng) return;
+    cudaSetDevice(x->op.eng->cfg.device);
+    cudaStreamSynchronize(x->op.eng->stream);
+    if (x->timing_pending) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, x->e0, x->e1) == cudaSuccess) {
+            x->total_us += 1e3 * ms;
+            x->samples++;
+        }
+        x->timing_pending = 0;
+    }
+}
+
+float *b200_expert_result(b200_expert_ctx_t *x) {
+    if (!x) return NULL;
+    if (x->op.eng && x->dirty) {
+        b200_expert_wait(x);
+        cudaMemcpy(x->partial, x->op.eng->moe_out, sizeof(float) * (size_t)x->n_embd, cudaMemcpyDeviceToHost);
+    } else {
+        memset(x->partial, 0, sizeof(float) * (size_t)x->n_embd);
+    }
+    return x->partial;
+}
+
+void b200_expert_get_timing(b200_expert_ctx_t *x, double *avg_wakeup_us, double *avg_compute_us, int *samples) {
+    if (samples) *samples = x ? x->samples : 0;
+    if (avg_wakeup_us) *avg_wakeup_us = 0.0; /* no worker thread to wake: work is enqueued on a stream */
+    if (avg_compute_us) *avg_compute_us = (x && x->samples > 0) ? x->total_us / x->samples : 0.0;
+}

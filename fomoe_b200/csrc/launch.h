@@ -1,0 +1,123 @@
+/*
+ * launch.h -- the thin C-ABI between the C host library and the CUDA kernels.
+ *
+ * Everything here is plain C: device pointers travel as ordinary pointers, streams as
+ * void*.  The host side (engine.c) owns all memory and ordering; the functions below
+ * only enqueue kernels on the given stream and return the CUDA error code (0 = ok).
+ */
+#ifndef FOMOE_B200_LAUNCH_H
+#define FOMOE_B200_LAUNCH_H
+
+#include <stdint.h>
+
+#include "layout.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* One quantised activation block as the kernels consume it (304 B, 16-byte aligned):
+ * the reference's block_q8_K (include/quant.h:94-98) re-ordered so the 256 int8 values
+ * come first.  19 uint4 per entry keeps 8 consecutive entries on distinct shared-memory
+ * bank groups. */
+typedef struct {
+    int8_t qs[256];
+    int16_t bsums[16];
+    float d;
+    uint32_t pad[3];
+} fb_q8_entry_t;
+
+/* status word values written by kernels (0 = ok) */
+#define FB_ST_OK 0
+#define FB_ST_BAD_ID 1      /* router produced an expert id outside the table */
+#define FB_ST_WAIT_TIMEOUT 2 /* a bounded wait ran out */
+
+/* Argument block passed by value to every hot-path kernel. */
+typedef struct {
+    /* shapes */
+    int n_embd, n_inter, inter_local, n_experts, top_k, n_slots, has_shared;
+    int tp_rank, tp_size;
+    int gate_bpr, down_bpr;       /* 256-column blocks per row in this rank's gate/up and down shards */
+    int gate_groups, down_groups; /* 32-block groups per shard */
+    uint64_t up_off, down_off;    /* byte offsets of the up and down shards inside an expert record */
+    float rms_eps, car_threshold;
+    int car_dampen;
+    /* this layer */
+    const uint8_t *table_layer; /* record of expert e at table_layer + e * rec_bytes; shared expert = index n_experts */
+    uint64_t rec_bytes;
+    int down_type;
+    const float *router_w;    /* [n_experts][n_embd] */
+    const float *resid;       /* [n_embd] or NULL */
+    const float *normw;       /* [n_embd] or NULL */
+    const uint32_t *resident; /* [16] residency bit mask or NULL */
+    uint32_t *freq;           /* [n_experts] selection histogram for this layer or NULL */
+    /* state */
+    float *x;       /* residual stream [n_embd] */
+    float *h;       /* normalised hidden state [n_embd] */
+    float *moe_out; /* MoE block output (this rank's partial under TP) [n_embd] */
+    fb_q8_entry_t *q8h; /* [n_embd/256] */
+    float *logits;      /* [n_experts] */
+    float *all_scores;  /* [n_experts] softmax over all experts */
+    int *ids;           /* [n_slots] selected expert ids (slot top_k = shared) */
+    int *ids_orig;      /* [top_k] ids before CAR */
+    float *scores;      /* [n_slots] routing weights */
+    const uint8_t **slot_rec; /* [n_slots] record pointers */
+    float *act;         /* [n_slots][inter_local] silu(gate)*up */
+    fb_q8_entry_t *q8a; /* [n_slots][inter_local/256] */
+    float *dots;        /* [n_slots][n_embd] per-expert down outputs */
+    unsigned *counters; /* arrival counters: [0] router, [1] substitutions, then windows, then row groups */
+    int *status;
+    int accumulate;        /* 1: the combine adds onto moe_out instead of overwriting it */
+    const float *tok_in;   /* device-resident token inputs [max_tokens][n_embd] */
+    float *tok_out;        /* device-resident token outputs */
+    unsigned *tok_ctr;     /* index of the token in flight */
+} fb_args_t;
+
+#define FB_CNT_ROUTER 0
+#define FB_CNT_SUBS 1
+#define FB_CNT_WIN 8 /* first window counter; n_slots * (inter_local/256) of them, row groups follow */
+
+/* prologue flags */
+#define FB_PRO_ADD_PREV 1 /* x += moe_out */
+#define FB_PRO_RESID 2    /* x += resid */
+#define FB_PRO_NORM 4     /* h = rmsnorm(x) * normw (else h = x) */
+#define FB_PRO_QUANT 8    /* q8h = Q8_K(h) */
+#define FB_PRO_LOAD 16    /* x = tok_in[*tok_ctr] first */
+#define FB_PRO_STORE 32   /* tok_out[*tok_ctr] = x at the end, then ++*tok_ctr */
+
+int fb_launch_prologue(const fb_args_t *a, int flags, void *stream);
+int fb_launch_router(const fb_args_t *a, int grid, void *stream);
+/* route from host-provided ids/scores already in a->ids / a->scores: only fills slot_rec */
+int fb_launch_set_slots(const fb_args_t *a, void *stream);
+int fb_launch_gate_up(const fb_args_t *a, int grid, void *stream);
+int fb_launch_down(const fb_args_t *a, int grid, void *stream);
+
+/* ---- table construction ---- */
+typedef struct {
+    int type;
+    int rows_local, bpr_local; /* shard geometry */
+    int row0, b0, bpr_full;    /* position of the shard inside the full matrix */
+} fb_shard_geom_t;
+
+/* generate expert `e`'s matrix stream (seed, layer, e, matrix) for e in [0, n_recs) straight into
+ * the device layout; dst0 = first record's shard, rec_stride between experts */
+int fb_launch_gen_shards(uint8_t *dst0, uint64_t rec_stride, int n_recs, uint64_t seed, uint32_t layer,
+                         uint32_t matrix, fb_shard_geom_t g, void *stream);
+int fb_launch_gen_f32(float *dst, uint64_t n, uint64_t seed, uint32_t layer, uint32_t stream_id, float mean,
+                      float std, void *stream);
+/* ggml-ordered bytes of the full matrix (device memory) -> this rank's shard */
+int fb_launch_repack(uint8_t *dst, const uint8_t *src_ggml, fb_shard_geom_t g, void *stream);
+/* shard -> ggml-ordered bytes of the shard's blocks, row-major (rows_local x bpr_local blocks) */
+int fb_launch_export_ggml(uint8_t *dst_ggml, const uint8_t *shard, fb_shard_geom_t g, void *stream);
+/* shard -> fp32 [rows_local][bpr_local*256] */
+int fb_launch_dequant(float *dst, const uint8_t *shard, fb_shard_geom_t g, void *stream);
+
+/* standalone matvec (microbenchmark / parity): out[rows_local] = shard . q8 (bpr_local entries) */
+int fb_launch_matvec(float *out, const uint8_t *shard, fb_shard_geom_t g, const fb_q8_entry_t *q8, int grid,
+                     void *stream);
+int fb_launch_quantize(fb_q8_entry_t *dst, const float *src, int n_blocks, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

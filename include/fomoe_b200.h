@@ -1,0 +1,202 @@
+/*
+ * fomoe_b200.h -- C ABI of libfomoe_b200.so: fomoe's routed-expert FFN decode path on B200.
+ *
+ * Three groups of entry points:
+ *   1. the reference's own GPU operator surface, same names and signatures
+ *      (reference include/gpu.h:13-83), so a build of the reference can link this
+ *      library in place of src/gpu_kernels.hip for the expert FFN;
+ *   2. a CUDA-backed twin of the reference's CPU expert engine
+ *      (reference include/cpu_expert.h:13-62) under the b200_expert_ prefix;
+ *   3. extensions for what the reference has no call for: an HBM-resident expert table
+ *      (instead of its VRAM/DRAM/NVMe tiers), the on-device router + cache-aware routing,
+ *      and the multi-layer decode stack used by the benchmark.
+ *
+ * Conventions are the reference's: opaque contexts, constructors return NULL on failure,
+ * int functions return 0 on success and -1 on failure, diagnostics go to stderr, nothing
+ * aborts.  All pointers are HOST pointers unless a comment says "device".  A context is
+ * used from one thread at a time.  There is no CPU fallback inside this library: when
+ * CUDA is unavailable every constructor returns NULL.
+ */
+#ifndef FOMOE_B200_H
+#define FOMOE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ggml type ids, reference include/quant_types.h:56-64 */
+#define FOMOE_TYPE_Q4_K 12
+#define FOMOE_TYPE_Q5_K 13
+#define FOMOE_TYPE_Q6_K 14
+
+/* ======================================================================================
+ * 1. Reference GPU surface (include/gpu.h).  gpu_expert_ffn is the operator on the hot
+ *    path; the tier-management calls are accepted and do nothing because every expert is
+ *    resident; gpu_forward / gpu_upload_model belong to the reference's whole-model engine,
+ *    which is outside this library: they report failure so the caller takes its own path
+ *    (reference src/inference.c:427-432).
+ * ====================================================================================== */
+typedef struct gpu_ctx gpu_ctx_t;
+
+gpu_ctx_t *gpu_init(void);                                                         /* gpu.h:13 */
+void gpu_free(gpu_ctx_t *ctx);                                                     /* gpu.h:16 */
+void gpu_register_buffers(gpu_ctx_t *ctx, void **buffers, int n, uint64_t size);   /* gpu.h:19 */
+void gpu_unregister_buffers(gpu_ctx_t *ctx, void **buffers, int n);                /* gpu.h:22 */
+int gpu_upload_model(gpu_ctx_t *ctx, const void *model);                           /* gpu.h:26, returns -1 */
+void gpu_set_ram_cache_mb(gpu_ctx_t *ctx, int mb);                                 /* gpu.h:30, no-op */
+void gpu_set_vram_cache_mb(gpu_ctx_t *ctx, int mb);                                /* gpu.h:34, no-op */
+float *gpu_forward(gpu_ctx_t *ctx, void *model, int token_id, int pos);            /* gpu.h:38, returns NULL */
+void gpu_reset_state(gpu_ctx_t *ctx);                                              /* gpu.h:41, no-op */
+int gpu_seed_vram_cache(gpu_ctx_t *ctx, void *model, const char *freq_profile_path); /* gpu.h:46, returns 0 */
+void gpu_enable_expert_freq(gpu_ctx_t *ctx);                                       /* gpu.h:50 */
+const uint32_t *gpu_get_expert_freq(gpu_ctx_t *ctx);                               /* gpu.h:54 */
+void gpu_get_expert_dims(gpu_ctx_t *ctx, int *n_layers, int *n_experts);           /* gpu.h:57 */
+void gpu_get_pingpong_relay_stats(gpu_ctx_t *ctx, uint64_t *handoffs, uint64_t *payload_bytes,
+                                  uint64_t *d2h_bytes, uint64_t *h2d_bytes, uint64_t *dma_bytes); /* gpu.h:61, zeros */
+
+/* Batched expert FFN: ffn_out[n_embd] = sum_e expert_scores[e] * FFN_e(h).
+ * Same arguments as reference gpu.h:70-83.  expert_buffers[e] points at one expert record
+ * in ggml byte order (gate | up | down back to back).  Returns 0, or -1 for shapes/types
+ * outside the supported set (the reference's limits, src/gpu_kernels.hip:8393-8403, plus:
+ * gate/up must be Q4_K, down Q4_K or Q6_K), in which case the caller falls back
+ * (src/inference.c:551).  Activations are quantised to Q8_K as in src/cpu_expert.c. */
+int gpu_expert_ffn(gpu_ctx_t *ctx, const float *h, void **expert_buffers, const float *expert_scores,
+                   int n_experts, int n_embd, int expert_intermediate, uint64_t expert_gate_size,
+                   uint64_t expert_up_size, uint64_t expert_stride, int gate_type, int up_type, int down_type,
+                   float *ffn_out);
+
+/* ======================================================================================
+ * 2. CUDA twin of the reference CPU expert engine (include/cpu_expert.h).
+ * ====================================================================================== */
+typedef struct b200_expert_ctx b200_expert_ctx_t;
+
+typedef struct { /* cpu_expert.h:13-18 */
+    const void *expert_data;
+    float score;
+    int gate_type, up_type, down_type;
+    uint64_t expert_gate_size, expert_up_size;
+} b200_expert_work_t;
+
+b200_expert_ctx_t *b200_expert_create(int n_embd, int expert_intermediate);        /* cpu_expert.h:23 */
+void b200_expert_free(b200_expert_ctx_t *ctx);                                     /* cpu_expert.h:26 */
+void b200_expert_reset(b200_expert_ctx_t *ctx);                                    /* cpu_expert.h:29 */
+void b200_expert_ffn(b200_expert_ctx_t *ctx, const void *expert_data, const float *input, float score,
+                     int gate_type, int up_type, int down_type, uint64_t expert_gate_size,
+                     uint64_t expert_up_size);                                      /* cpu_expert.h:39 */
+void b200_expert_submit_async(b200_expert_ctx_t *ctx, const float *input, const b200_expert_work_t *work,
+                              int n_work);                                          /* cpu_expert.h:50 */
+void b200_expert_wait(b200_expert_ctx_t *ctx);                                     /* cpu_expert.h:55 */
+float *b200_expert_result(b200_expert_ctx_t *ctx);                                 /* cpu_expert.h:59 */
+void b200_expert_get_timing(b200_expert_ctx_t *ctx, double *avg_wakeup_us, double *avg_compute_us,
+                            int *samples);                                          /* cpu_expert.h:62 */
+
+/* ======================================================================================
+ * 3. Extensions: resident expert table, on-device routing, decode stack.
+ * ====================================================================================== */
+typedef struct fomoe_b200_ctx fomoe_b200_ctx_t;
+
+typedef struct {
+    int device;              /* CUDA device ordinal */
+    int n_layers;
+    int n_embd;              /* hidden size, multiple of 256, <= 8192 */
+    int n_inter;             /* expert intermediate size, multiple of 256 * tp_size */
+    int n_experts;           /* routed experts per layer, <= 512 */
+    int top_k;               /* experts used per token, <= 15 */
+    int has_shared;          /* 1: one shared expert per layer (record index n_experts) */
+    int gate_type;           /* gate and up type: FOMOE_TYPE_Q4_K */
+    const int *down_types;   /* [n_layers] FOMOE_TYPE_Q4_K / FOMOE_TYPE_Q6_K; NULL = all Q6_K */
+    int tp_rank, tp_size;    /* tensor parallelism over the intermediate dimension */
+    float rms_eps;
+    float car_threshold;     /* CAR runs when 0 < threshold < 1 (reference src/car.c:68, gpu_kernels.hip:7170) */
+    int car_dampen;          /* 1: substitute weight = original weight * ratio, no renormalise */
+    int max_tokens;          /* capacity of the device-resident token buffers (0 = 1) */
+} fomoe_b200_config_t;
+
+fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg);
+void fomoe_b200_destroy(fomoe_b200_ctx_t *ctx);
+const char *fomoe_b200_last_error(fomoe_b200_ctx_t *ctx);
+/* device status word written by kernels: 0 ok, 1 bad expert id, 2 bounded wait ran out */
+int fomoe_b200_status(fomoe_b200_ctx_t *ctx);
+/* bytes of one expert record in the reference's ggml order (gate | up | down), full (unsharded) */
+uint64_t fomoe_b200_record_bytes(fomoe_b200_ctx_t *ctx, int layer);
+/* bytes this rank holds in HBM for the table */
+uint64_t fomoe_b200_table_bytes(fomoe_b200_ctx_t *ctx);
+
+/* Fill table, routers, residuals and norm weights of every layer on the device from `seed`
+ * (generator: fomoe_b200_synth_* below produce the same bytes on the host). */
+int fomoe_b200_table_generate(fomoe_b200_ctx_t *ctx, uint64_t seed);
+/* Upload one expert record in ggml order (expert == n_experts addresses the shared expert). */
+int fomoe_b200_table_upload(fomoe_b200_ctx_t *ctx, int layer, int expert, const void *record);
+/* Read this rank's shard of one matrix (0 gate, 1 up, 2 down) back in ggml order / as fp32. */
+int fomoe_b200_table_export(fomoe_b200_ctx_t *ctx, int layer, int expert, int matrix, void *ggml_out);
+int fomoe_b200_table_dequant(fomoe_b200_ctx_t *ctx, int layer, int expert, int matrix, float *out);
+int fomoe_b200_router_upload(fomoe_b200_ctx_t *ctx, int layer, const float *w);
+int fomoe_b200_glue_upload(fomoe_b200_ctx_t *ctx, int layer, const float *resid, const float *normw);
+int fomoe_b200_set_resident_mask(fomoe_b200_ctx_t *ctx, int layer, const uint32_t *mask /* [16] or NULL */);
+int fomoe_b200_set_car(fomoe_b200_ctx_t *ctx, float threshold, int dampen);
+
+/* One MoE block on an already normalised hidden state: route on the device, run the selected
+ * experts and the shared expert, return out[n_embd] (this rank's partial when tp_size > 1).
+ * ids_out / scores_out ([top_k], optional) receive the routing after CAR, ids_orig_out the
+ * top-k before CAR, all_scores_out [n_experts] the softmax. */
+int fomoe_b200_moe_layer(fomoe_b200_ctx_t *ctx, int layer, const float *h, float *out, int *ids_out,
+                         float *scores_out, int *ids_orig_out, float *all_scores_out);
+/* Same with routing supplied by the caller (n <= top_k experts of `layer`). */
+int fomoe_b200_moe_layer_routed(fomoe_b200_ctx_t *ctx, int layer, const float *h, const int *ids,
+                                const float *scores, int n, float *out);
+/* Decode stack, layers [l0, l1): x += resid_l; h = rmsnorm(x) * normw_l; x += moe_l(h).
+ * Host in, host out; copies are part of the call. */
+int fomoe_b200_stack_run(fomoe_b200_ctx_t *ctx, const float *x_in, int l0, int l1, float *x_out);
+/* Device-resident variant for throughput: tokens are uploaded once, then `count` tokens run
+ * back to back through all layers without touching the host; elapsed_ms (optional) is the
+ * CUDA-event time of the run on the library's stream. */
+int fomoe_b200_tokens_upload(fomoe_b200_ctx_t *ctx, int first, int count, const float *x);
+int fomoe_b200_tokens_run(fomoe_b200_ctx_t *ctx, int first, int count, float *elapsed_ms);
+int fomoe_b200_tokens_download(fomoe_b200_ctx_t *ctx, int first, int count, float *x_out);
+/* One token, host to host, through every layer as one graph launch: pinned H2D of x_in, the stack,
+ * pinned D2H of the result, one synchronise.  This is the end-to-end call. */
+int fomoe_b200_decode_token(fomoe_b200_ctx_t *ctx, const float *x_in, float *x_out);
+/* Like tokens_run but with plain launches bracketed by CUDA events per kernel; phase_ms[5] receives
+ * the summed device time of prologue, router, gate/up, down kernels and the whole run;
+ * phase_launches[4] the number of launches of each. */
+int fomoe_b200_tokens_profile(fomoe_b200_ctx_t *ctx, int first, int count, float *phase_ms, int *phase_launches);
+/* Routing of the most recent token at `layer`. */
+int fomoe_b200_get_routing(fomoe_b200_ctx_t *ctx, int layer, int *ids, float *scores, int *ids_orig);
+/* Counters since creation: CAR substitutions, kernels launched by this library. */
+uint64_t fomoe_b200_substitutions(fomoe_b200_ctx_t *ctx);
+uint64_t fomoe_b200_kernel_launches(fomoe_b200_ctx_t *ctx);
+/* 1: replay each token as one CUDA graph (default), 0: plain stream launches. */
+int fomoe_b200_set_graphs(fomoe_b200_ctx_t *ctx, int enable);
+
+/* Copy an intermediate of the most recent layer call to the host (parity tests look inside the
+ * block): what = 0 act float[n_slots][inter_local]; 1 quantised act, 304-byte entries
+ * {int8 qs[256]; int16 bsums[16]; float d; pad[12]} [n_slots][inter_local/256]; 2 quantised hidden
+ * state, same entries [n_embd/256]; 3 per-expert down outputs float[n_slots][n_embd];
+ * 4 normalised hidden state float[n_embd]. */
+int fomoe_b200_peek(fomoe_b200_ctx_t *ctx, int what, void *out, uint64_t bytes);
+
+/* Microbenchmark / parity helpers: y[rows] = W[rows x cols] . Q8_K(x), W given in ggml order. */
+int fomoe_b200_matvec(fomoe_b200_ctx_t *ctx, int type, const void *w_ggml, int rows, int cols, const float *x,
+                      float *y);
+int fomoe_b200_quantize_q8k(fomoe_b200_ctx_t *ctx, const float *x, int n, void *q8k_out /* n/256 * 292 B, reference block_q8_K */);
+
+/* Host-side synthetic generator (same bytes as fomoe_b200_table_generate puts on the device). */
+void fomoe_b200_synth_matrix(uint64_t seed, int layer, int expert, int matrix, int type, int rows, int cols,
+                             void *ggml_out);
+void fomoe_b200_synth_f32(uint64_t seed, int layer, int stream_id, float mean, float std, uint64_t n, float *out);
+#define FOMOE_STREAM_ROUTER 3
+#define FOMOE_STREAM_RESID 4
+#define FOMOE_STREAM_NORMW 5
+#define FOMOE_STREAM_HIDDEN 6
+/* distribution parameters table_generate uses */
+#define FOMOE_ROUTER_STD 0.02f
+#define FOMOE_RESID_STD 1.0f
+#define FOMOE_NORMW_MEAN 1.0f
+#define FOMOE_NORMW_STD 0.1f
+
+#ifdef __cplusplus
+}
+#endif
+#endif

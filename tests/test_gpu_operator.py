@@ -1,0 +1,70 @@
+"""The reference's operator surfaces: gpu_expert_ffn (include/gpu.h:70-83) and the CUDA twin of the
+cpu_expert engine (include/cpu_expert.h:23-62), checked against the CPU oracle / compiled reference."""
+import numpy as np
+import pytest
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def _experts(fb, seed, n, down_type, n_embd, inter):
+    return [H.expert_record(fb, seed, 0, e, down_type, n_embd, inter) for e in range(n)]
+
+
+@pytest.mark.parametrize("down_type,n", [(H.Q6, 10), (H.Q4, 8), (H.Q6, 1)])
+def test_gpu_expert_ffn_matches_cpu_expert(fb, oracle, down_type, n):
+    n_embd, inter, seed = 4096, 1024, 61
+    op = fb.GpuOperator()
+    ex = _experts(fb, seed, n, down_type, n_embd, inter)
+    h = H.hidden(fb, seed, 0, n_embd)
+    sc = np.random.default_rng(1).dirichlet(np.ones(n)).astype(np.float32)
+    gs = fb.matrix_bytes(H.Q4, inter, n_embd)
+    rc, out = op.expert_ffn(h, ex, sc, n_embd, inter, gs, gs, ex[0].size, H.Q4, H.Q4, down_type)
+    assert rc == 0
+    want = oracle.moe_block(h, ex, sc, None, H.Q4, H.Q4, down_type, gs, gs, n_embd, inter)
+    assert H.rel_l2(out, want) < 3e-4
+    op.close()
+
+
+def test_gpu_expert_ffn_rejects_like_the_reference(fb):
+    """-1 = "fall back to CPU" for the reference's limits (src/gpu_kernels.hip:8393-8403)."""
+    n_embd, inter, seed = 512, 256, 3
+    op = fb.GpuOperator()
+    ex = _experts(fb, seed, 11, H.Q6, n_embd, inter)
+    h = H.hidden(fb, seed, 0, n_embd)
+    gs = fb.matrix_bytes(H.Q4, inter, n_embd)
+    sc = np.full(11, 1 / 11, dtype=np.float32)
+    assert op.expert_ffn(h, ex, sc, n_embd, inter, gs, gs, ex[0].size, H.Q4, H.Q4, H.Q6)[0] == -1      # 11 experts
+    assert op.expert_ffn(h, ex[:2], sc[:2], n_embd, inter, gs, gs, ex[0].size, H.Q4, H.Q4, 8)[0] == -1  # Q8_0 down
+    assert op.expert_ffn(h, ex[:2], sc[:2], n_embd, inter, gs, gs, 13 << 20, H.Q4, H.Q4, H.Q6)[0] == -1  # stride
+    assert op.expert_ffn(h, ex[:2], sc[:2], n_embd, inter, gs, gs, ex[0].size, H.Q4, H.Q4, H.Q6)[0] == 0
+    l = fb.lib()
+    assert l.gpu_upload_model(op._h, None) == -1
+    assert l.gpu_forward(op._h, None, 0, 0) is None
+    assert l.gpu_seed_vram_cache(op._h, None, None) == 0
+    op.close()
+
+
+def test_expert_engine_twin(fb, oracle):
+    n_embd, inter, seed = 2048, 512, 71
+    eng = fb.ExpertEngine(n_embd, inter)
+    ex = _experts(fb, seed, 5, H.Q6, n_embd, inter)
+    h = H.hidden(fb, seed, 0, n_embd)
+    sc = np.array([0.3, 0.25, 0.2, 0.15, 0.1], dtype=np.float32)
+    gs = fb.matrix_bytes(H.Q4, inter, n_embd)
+    want = oracle.moe_block(h, ex, sc, None, H.Q4, H.Q4, H.Q6, gs, gs, n_embd, inter)
+    # synchronous form: reset + one ffn per expert accumulates (src/cpu_expert.c:226-240)
+    eng.reset()
+    for e, s in zip(ex, sc):
+        eng.ffn(e, h, float(s), H.Q4, H.Q4, H.Q6, gs, gs)
+    assert H.rel_l2(eng.result(), want) < 3e-4
+    # batch form (src/cpu_expert.c:242-279): starts from zero
+    eng.submit_async(h, ex, sc, H.Q4, H.Q4, H.Q6, gs, gs)
+    eng.wait()
+    assert H.rel_l2(eng.result(), want) < 3e-4
+    eng.reset()
+    assert np.abs(eng.result()).max() == 0.0
+    _, comp_us, n = eng.timing()
+    assert n >= 2 and comp_us > 0
+    eng.close()
