@@ -94,6 +94,9 @@ _SIGS = {
     "fomoe_b200_substitutions": (C.c_uint64, [C.c_void_p]),
     "fomoe_b200_kernel_launches": (C.c_uint64, [C.c_void_p]),
     "fomoe_b200_set_graphs": (C.c_int, [C.c_void_p, C.c_int]),
+    "fomoe_b200_set_variant": (C.c_int, [C.c_void_p, C.c_int]),
+    "fomoe_b200_trace_enable": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
+    "fomoe_b200_trace_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64), C.c_int]),
     "fomoe_b200_peek": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_uint64]),
     "fomoe_b200_matvec": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p, _f32p]),
     "fomoe_b200_quantize_q8k": (C.c_int, [C.c_void_p, _f32p, C.c_int, C.c_void_p]),
@@ -312,6 +315,25 @@ class MoeDecoder:
 
     def kernel_launches(self):
         return int(self._l.fomoe_b200_kernel_launches(self._h))
+
+    def trace(self, first, count, cta=0):
+        """Run `count` resident tokens with phase stamps of block `cta`; returns (index, ns) arrays."""
+        cap = 9 * self.n_layers * count
+        self._ck(self._l.fomoe_b200_trace_enable(self._h, cap, cta), "trace_enable")
+        self.tokens_run(first, count)
+        buf = np.zeros(cap * (self.n_blocks() if cta < 0 else 1), dtype=np.uint64)
+        self._ck(self._l.fomoe_b200_trace_read(self._h, buf.ctypes.data_as(C.POINTER(C.c_uint64)), buf.size),
+                 "trace_read")
+        self._ck(self._l.fomoe_b200_trace_enable(self._h, 0, 0), "trace_enable")
+        return (buf >> np.uint64(56)).astype(np.int64), (buf & np.uint64((1 << 56) - 1)).astype(np.int64)
+
+    def n_blocks(self):
+        import torch
+        return torch.cuda.get_device_properties(0).multi_processor_count
+
+    def set_variant(self, variant):
+        """2: persistent stack kernel for whole tokens (default); 0 / 1: per-phase kernels (plain / ring)."""
+        self._ck(self._l.fomoe_b200_set_variant(self._h, variant), "set_variant")
 
     def set_graphs(self, enable):
         self._ck(self._l.fomoe_b200_set_graphs(self._h, int(bool(enable))), "set_graphs")

@@ -64,6 +64,15 @@ struct fomoe_b200_ctx {
     cudaEvent_t *pev;
     int *pev_phase;
     int pev_cap, pev_n, profiling;
+    int variant; /* 0: per-phase kernels, plain loads; 1: per-phase kernels, bulk-copy rings; 2 (default): the
+                    persistent stack kernel for whole-token runs, per-phase kernels (plain) elsewhere.
+                    Environment override: FOMOE_B200_VARIANT */
+    fb_args_t *d_layer_args; /* device copy of every layer's arguments for the stack kernel */
+    int layer_args_valid;
+    unsigned long long *d_bar, *d_trace;
+    unsigned long long bar_count; /* arrivals every finished launch has added to *d_bar */
+    int trace_cap, trace_cta;
+    int *d_abort;
     char err[256];
 };
 
@@ -126,6 +135,7 @@ static fb_shard_geom_t geom_down(const fomoe_b200_ctx_t *c, int type) {
 }
 
 static void drop_graph(fomoe_b200_ctx_t *c) {
+    c->layer_args_valid = 0;
     if (c->graph_exec) {
         cudaGraphExecDestroy(c->graph_exec);
         c->graph_exec = NULL;
@@ -152,7 +162,7 @@ void fomoe_b200_destroy(fomoe_b200_ctx_t *c) {
     cudaFree(c->scores); cudaFree(c->act); cudaFree(c->dots); cudaFree(c->ids); cudaFree(c->ids_orig);
     cudaFree(c->status); cudaFree((void *)c->slot_rec); cudaFree(c->q8h); cudaFree(c->q8a);
     cudaFree(c->counters); cudaFree(c->tok_ctr); cudaFree(c->freq); cudaFree(c->tok_in); cudaFree(c->tok_out);
-    cudaFree(c->stage);
+    cudaFree(c->d_trace); cudaFree(c->stage); cudaFree(c->d_layer_args); cudaFree(c->d_bar); cudaFree(c->d_abort);
     if (c->pin) cudaFreeHost(c->pin);
     for (int i = 0; i < c->pev_cap; i++) cudaEventDestroy(c->pev[i]);
     free(c->pev);
@@ -181,6 +191,7 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
     if (!c) return NULL;
     c->cfg = *cfg;
     c->use_graphs = 1;
+    c->variant = getenv("FOMOE_B200_VARIANT") ? atoi(getenv("FOMOE_B200_VARIANT")) : 2;
     const int N = cfg->tp_size > 0 ? cfg->tp_size : 1;
     c->cfg.tp_size = N;
     if (cfg->device < 0 || cfg->device >= ndev || cfg->n_layers < 1 || cfg->n_embd % FB_QK || cfg->n_embd > 8192 ||
@@ -263,8 +274,10 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
         dev_alloc(c, (void **)&c->q8a, sizeof(fb_q8_entry_t) * FB_MAX_SLOTS * (c->inter_local / FB_QK)) ||
         dev_alloc(c, (void **)&c->counters, sizeof(unsigned) * (FB_CNT_WIN + FB_MAX_SLOTS * 32 + c->down_groups)) ||
         dev_alloc(c, (void **)&c->status, sizeof(int)) || dev_alloc(c, (void **)&c->tok_ctr, sizeof(unsigned)) ||
-        dev_alloc(c, (void **)&c->tok_in, sizeof(float) * (uint64_t)c->max_tokens * ne) ||
-        dev_alloc(c, (void **)&c->tok_out, sizeof(float) * (uint64_t)c->max_tokens * ne))
+        dev_alloc(c, (void **)&c->d_layer_args, sizeof(fb_args_t) * (uint64_t)nl) ||
+        dev_alloc(c, (void **)&c->d_bar, sizeof(unsigned long long)) || dev_alloc(c, (void **)&c->d_abort, sizeof(int)) ||
+        dev_alloc(c, (void **)&c->tok_in, sizeof(float) * (uint64_t)(c->max_tokens + 1) * ne) ||
+        dev_alloc(c, (void **)&c->tok_out, sizeof(float) * (uint64_t)(c->max_tokens + 1) * ne))
         goto fail;
     c->stage_bytes = max_rec_ggml > sizeof(float) * (uint64_t)ne * 1024 ? max_rec_ggml : sizeof(float) * (uint64_t)ne * 1024;
     if (cudaMalloc((void **)&c->stage, c->stage_bytes) != cudaSuccess) goto fail;
@@ -286,6 +299,10 @@ int fomoe_b200_status(fomoe_b200_ctx_t *c) {
     cudaSetDevice(c->cfg.device);
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1;
     if (cudaMemcpy(&st, c->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (st == FB_ST_WAIT_TIMEOUT) { /* a stack launch gave up: its barrier count is unknown, start over */
+        cudaMemset(c->d_bar, 0, sizeof(unsigned long long));
+        c->bar_count = 0;
+    }
     return st;
 }
 
@@ -305,6 +322,43 @@ uint64_t fomoe_b200_substitutions(fomoe_b200_ctx_t *c) {
     cudaStreamSynchronize(c->stream);
     cudaMemcpy(&v, c->counters + FB_CNT_SUBS, sizeof(unsigned), cudaMemcpyDeviceToHost);
     return v;
+}
+
+/* Profiling aid: record %globaltimer stamps of block `cta` at the phase boundaries of the stack kernel
+ * for the next run; cap = 0 switches it off.  fomoe_b200_trace_read copies them out: the top byte of each
+ * word is the stamp index (0 layer top, 1 joined previous barrier, 2 after RMSNorm/Q8_K, 3 router rows done,
+ * 4 logits barrier passed, 5 routing done, 6 gate/up done, 7 activation barrier passed, 8 down done). */
+int fomoe_b200_trace_enable(fomoe_b200_ctx_t *c, int cap, int cta) {
+    if (!c) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    cudaFree(c->d_trace);
+    c->d_trace = NULL;
+    c->trace_cap = 0;
+    if (cap > 0) {
+        const size_t words = (size_t)cap * (cta < 0 ? (size_t)c->n_sm : 1);
+        CK(c, cudaMalloc((void **)&c->d_trace, sizeof(unsigned long long) * words));
+        CK(c, cudaMemset(c->d_trace, 0, sizeof(unsigned long long) * words));
+        c->trace_cap = cap;
+        c->trace_cta = cta;
+    }
+    return 0;
+}
+
+int fomoe_b200_trace_read(fomoe_b200_ctx_t *c, unsigned long long *out, int n) {
+    if (!c || !out || !c->d_trace || (size_t)n > (size_t)c->trace_cap * (c->trace_cta < 0 ? (size_t)c->n_sm : 1)) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    CK(c, cudaMemcpy(out, c->d_trace, sizeof(unsigned long long) * (size_t)n, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int fomoe_b200_set_variant(fomoe_b200_ctx_t *c, int variant) {
+    if (!c || variant < 0 || variant > 2) return -1;
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    drop_graph(c);
+    c->variant = variant;
+    return 0;
 }
 
 int fomoe_b200_set_graphs(fomoe_b200_ctx_t *c, int enable) {
@@ -515,8 +569,15 @@ static int grid_tasks(const fomoe_b200_ctx_t *c, int tasks) {
 
 /* expert phase of one layer: gate/up/SwiGLU then down/combine, on the slots already set */
 static int enqueue_experts(fomoe_b200_ctx_t *c, const fb_args_t *a) {
-    CKL(c, fb_launch_gate_up(a, grid_tasks(c, a->n_slots * a->gate_groups), c->stream));
-    CKL(c, fb_launch_down(a, grid_tasks(c, a->n_slots * a->down_groups), c->stream));
+    if (c->variant != 1 || a->n_slots > 15) {
+        CKL(c, fb_launch_gate_up(a, grid_tasks(c, a->n_slots * a->gate_groups), c->stream));
+        CKL(c, fb_launch_down(a, grid_tasks(c, a->n_slots * a->down_groups), c->stream));
+        return 0;
+    }
+    /* bulk-copy rings: one block per SM */
+    int g1 = (a->n_slots * a->gate_groups + 7) / 8, g2 = a->down_groups;
+    CKL(c, fb_launch_gate_up_ring(a, g1 < c->n_sm ? g1 : c->n_sm, c->stream));
+    CKL(c, fb_launch_down_ring(a, g2 < c->n_sm ? g2 : c->n_sm, c->stream));
     return 0;
 }
 
@@ -534,6 +595,48 @@ static int enqueue_stack(fomoe_b200_ctx_t *c, int l0, int l1, int load_store) {
     }
     fill_args(c, l1 - 1, &a);
     CKL(c, fb_launch_prologue(&a, FB_PRO_ADD_PREV | (load_store ? FB_PRO_STORE : 0), c->stream));
+    return 0;
+}
+
+static int stack_kernel_usable(fomoe_b200_ctx_t *c) {
+    fb_args_t a;
+    if (c->variant != 2) return 0;
+    fill_args(c, 0, &a);
+    return fb_stack_supported(&a, c->n_sm);
+}
+
+/* layers [l0, l1) of `count` tokens starting at the token index already stored in tok_ctr: one launch */
+static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int count) {
+    if (!c->layer_args_valid) {
+        fb_args_t *tmp = (fb_args_t *)malloc(sizeof(fb_args_t) * (size_t)c->cfg.n_layers);
+        if (!tmp) return -1;
+        for (int l = 0; l < c->cfg.n_layers; l++) fill_args(c, l, &tmp[l]);
+        cudaError_t e = cudaMemcpy(c->d_layer_args, tmp, sizeof(fb_args_t) * (size_t)c->cfg.n_layers, cudaMemcpyHostToDevice);
+        free(tmp);
+        if (e != cudaSuccess) {
+            set_err(c, "uploading layer arguments: %s", cudaGetErrorString(e));
+            return -1;
+        }
+        c->layer_args_valid = 1;
+    }
+    fb_stack_args_t k;
+    k.layers = c->d_layer_args + l0;
+    k.n_layers = l1 - l0;
+    k.tok_count = count;
+    k.tok_in = c->tok_in;
+    k.tok_out = c->tok_out;
+    k.tok_ctr = c->tok_ctr;
+    k.bar = c->d_bar;
+    k.bar_base = c->bar_count;
+    k.abort_flag = c->d_abort;
+    k.status = c->status;
+    k.trace = c->d_trace;
+    k.trace_cap = c->d_trace ? c->trace_cap : 0;
+    k.trace_cta = c->trace_cta;
+    CK(c, cudaMemsetAsync(c->d_abort, 0, sizeof(int), c->stream));
+    CKL(c, fb_launch_stack(&k, c->n_sm, c->stream));
+    /* three grid barriers per layer per token, every block arrives once at each */
+    c->bar_count += 3ull * (unsigned long long)(l1 - l0) * (unsigned long long)count * (unsigned long long)c->n_sm;
     return 0;
 }
 
@@ -623,6 +726,17 @@ int fomoe_b200_stack_run(fomoe_b200_ctx_t *c, const float *x_in, int l0, int l1,
     CK(c, cudaSetDevice(c->cfg.device));
     const size_t nb = sizeof(float) * c->cfg.n_embd;
     memcpy(c->pin, x_in, nb);
+    if (stack_kernel_usable(c)) { /* the spare token slot past max_tokens carries host-to-host calls */
+        unsigned *slot = (unsigned *)(c->pin + 2 * c->cfg.n_embd);
+        *slot = (unsigned)c->max_tokens;
+        CK(c, cudaMemcpyAsync(c->tok_in + (size_t)c->max_tokens * c->cfg.n_embd, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
+        CK(c, cudaMemcpyAsync(c->tok_ctr, slot, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
+        if (launch_stack_kernel(c, l0, l1, 1)) return -1;
+        CK(c, cudaMemcpyAsync(c->pin + c->cfg.n_embd, c->tok_out + (size_t)c->max_tokens * c->cfg.n_embd, nb, cudaMemcpyDeviceToHost, c->stream));
+        CK(c, cudaStreamSynchronize(c->stream));
+        memcpy(x_out, c->pin + c->cfg.n_embd, nb);
+        return 0;
+    }
     CK(c, cudaMemcpyAsync(c->x, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
     if (enqueue_stack(c, l0, l1, 0)) return -1;
     CK(c, cudaMemcpyAsync(c->pin + c->cfg.n_embd, c->x, nb, cudaMemcpyDeviceToHost, c->stream));
@@ -679,8 +793,18 @@ int fomoe_b200_tokens_run(fomoe_b200_ctx_t *c, int first, int count, float *elap
         return -1;
     }
     CK(c, cudaSetDevice(c->cfg.device));
-    if (c->use_graphs && !c->graph_exec && build_graph(c)) return -1;
     unsigned f = (unsigned)first;
+    if (stack_kernel_usable(c)) {
+        CK(c, cudaMemcpyAsync(c->tok_ctr, &f, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
+        CK(c, cudaMemsetAsync(c->d_abort, 0, sizeof(int), c->stream));
+        CK(c, cudaEventRecord(c->ev0, c->stream));
+        if (launch_stack_kernel(c, 0, c->cfg.n_layers, count)) return -1;
+        CK(c, cudaEventRecord(c->ev1, c->stream));
+        CK(c, cudaStreamSynchronize(c->stream));
+        if (elapsed_ms) CK(c, cudaEventElapsedTime(elapsed_ms, c->ev0, c->ev1));
+        return 0;
+    }
+    if (c->use_graphs && !c->graph_exec && build_graph(c)) return -1;
     CK(c, cudaMemcpyAsync(c->tok_ctr, &f, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
     CK(c, cudaEventRecord(c->ev0, c->stream));
     for (int t = 0; t < count; t++) {
@@ -758,19 +882,23 @@ int fomoe_b200_decode_token(fomoe_b200_ctx_t *c, const float *x_in, float *x_out
         return -1;
     }
     CK(c, cudaSetDevice(c->cfg.device));
-    if (c->use_graphs && !c->graph_exec && build_graph(c)) return -1;
+    const int use_kernel = stack_kernel_usable(c);
+    if (!use_kernel && c->use_graphs && !c->graph_exec && build_graph(c)) return -1;
     const size_t nb = sizeof(float) * c->cfg.n_embd;
-    unsigned *zero = (unsigned *)(c->pin + 2 * c->cfg.n_embd);
-    *zero = 0;
+    unsigned *slot = (unsigned *)(c->pin + 2 * c->cfg.n_embd); /* the spare slot past max_tokens */
+    *slot = (unsigned)c->max_tokens;
+    const size_t spare = (size_t)c->max_tokens * c->cfg.n_embd;
     memcpy(c->pin, x_in, nb);
-    CK(c, cudaMemcpyAsync(c->tok_in, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
-    CK(c, cudaMemcpyAsync(c->tok_ctr, zero, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
-    if (c->use_graphs) {
+    CK(c, cudaMemcpyAsync(c->tok_in + spare, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
+    CK(c, cudaMemcpyAsync(c->tok_ctr, slot, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
+    if (use_kernel) {
+        if (launch_stack_kernel(c, 0, c->cfg.n_layers, 1)) return -1;
+    } else if (c->use_graphs) {
         CK(c, cudaGraphLaunch(c->graph_exec, c->stream));
         c->launches += (uint64_t)c->graph_nodes;
     } else if (enqueue_stack(c, 0, c->cfg.n_layers, 1))
         return -1;
-    CK(c, cudaMemcpyAsync(c->pin + c->cfg.n_embd, c->tok_out, nb, cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaMemcpyAsync(c->pin + c->cfg.n_embd, c->tok_out + spare, nb, cudaMemcpyDeviceToHost, c->stream));
     CK(c, cudaStreamSynchronize(c->stream));
     memcpy(x_out, c->pin + c->cfg.n_embd, nb);
     return 0;

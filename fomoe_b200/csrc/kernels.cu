@@ -23,8 +23,12 @@
 
 #include "dots.cuh"
 #include "launch.h"
+#include "route.cuh"
+#include "stream.cuh"
 
+#ifndef FULL
 #define FULL 0xffffffffu
+#endif
 
 __device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
     /* weights are read exactly once: keep them out of L1 */
@@ -90,248 +94,6 @@ __global__ void __launch_bounds__(1024) k_prologue(fb_args_t A, int flags) {
 }
 
 /* ------------------------------------------------------------------ router */
-__device__ __forceinline__ bool fb_better(float av, int ai, float bv, int bi) {
-    return av > bv || (av == bv && ai < bi);
-}
-
-/* warp-wide arg-best over (value desc, index asc); every lane returns the winner */
-__device__ __forceinline__ void fb_warp_best(float &v, int &i) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(FULL, v, o);
-        const int oi = __shfl_xor_sync(FULL, i, o);
-        if (fb_better(ov, oi, v, i)) {
-            v = ov;
-            i = oi;
-        }
-    }
-}
-
-#define FB_EPL 16 /* experts per lane: 512 / 32 */
-
-/* Softmax, ordered top-k, renormalise and cache-aware routing in one warp.
- *
- * Ordering rule is the CPU's (src/tensor.c:226-252): value descending, lower index first on
- * ties.  The fast logits are summed in a different order from the CPU's sequential loop
- * (src/tensor.c:104-113), so whenever two neighbours among the best k+1 are closer than
- * `tie_tol` the affected rows are recomputed in exactly the CPU's order (sequential
- * multiply-then-add) before ranking.  CAR follows src/car.c:36-264 with one residency tier. */
-__device__ void fb_route_select(const fb_args_t &A, int lane) {
-    const int nE = A.n_experts, k = A.top_k;
-    float lg[FB_EPL];
-#pragma unroll
-    for (int j = 0; j < FB_EPL; j++) {
-        const int e = j * 32 + lane;
-        lg[j] = (e < nE) ? __ldcg(A.logits + e) : -INFINITY;
-    }
-    int cand_id[FB_MAX_TOPK + 1];
-    float cand_v[FB_MAX_TOPK + 1];
-    const int kk = min(k + 1, nE);
-
-    for (int pass = 0; pass < 2; pass++) {
-        uint32_t taken = 0;
-        for (int r = 0; r < kk; r++) {
-            float bv = -INFINITY;
-            int bi = 0x7fffffff;
-#pragma unroll
-            for (int j = 0; j < FB_EPL; j++) {
-                const int e = j * 32 + lane;
-                if (e < nE && !((taken >> j) & 1u) && fb_better(lg[j], e, bv, bi)) {
-                    bv = lg[j];
-                    bi = e;
-                }
-            }
-            fb_warp_best(bv, bi);
-            cand_id[r] = bi;
-            cand_v[r] = bv;
-            if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-        }
-        if (pass == 1) break;
-        /* near-tie arbiter */
-        uint32_t flag = 0;
-        for (int r = 0; r + 1 < kk; r++) {
-            const float tol = 1e-4f * fmaxf(1.0f, fabsf(cand_v[r]));
-            if (cand_v[r] - cand_v[r + 1] <= tol) flag |= (1u << r) | (1u << (r + 1));
-        }
-        if (!flag) break;
-        /* lane r recomputes row cand_id[r] in the CPU's order */
-        float exact = 0.0f;
-        int my_row = -1;
-        for (int r = 0; r < kk; r++)
-            if (r == lane && ((flag >> r) & 1u)) my_row = cand_id[r];
-        if (my_row >= 0) {
-            const float *w = A.router_w + (size_t)my_row * A.n_embd;
-            for (int j = 0; j < A.n_embd; j++) exact = __fadd_rn(exact, __fmul_rn(__ldg(w + j), __ldcg(A.h + j)));
-        }
-        for (int r = 0; r < kk; r++) {
-            if (!((flag >> r) & 1u)) continue;
-            const float ev = __shfl_sync(FULL, exact, r);
-            const int e = cand_id[r];
-            if ((e & 31) == lane) {
-#pragma unroll
-                for (int j = 0; j < FB_EPL; j++)
-                    if (j == (e >> 5)) lg[j] = ev;
-                A.logits[e] = ev;
-            }
-        }
-    }
-
-    /* softmax over all experts (src/tensor.c:186-200) */
-    float mx = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < FB_EPL; j++) mx = fmaxf(mx, lg[j]);
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, o));
-    float p[FB_EPL], sum = 0.0f;
-#pragma unroll
-    for (int j = 0; j < FB_EPL; j++) {
-        const int e = j * 32 + lane;
-        p[j] = (e < nE) ? expf(lg[j] - mx) : 0.0f;
-        sum += p[j];
-    }
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(FULL, sum, o);
-    const float inv = __fdiv_rn(1.0f, sum);
-#pragma unroll
-    for (int j = 0; j < FB_EPL; j++) {
-        const int e = j * 32 + lane;
-        p[j] = __fmul_rn(p[j], inv);
-        if (e < nE) A.all_scores[e] = p[j];
-    }
-    /* scores of the candidates; equal probabilities order by index like the CPU */
-    for (int r = 0; r < kk; r++) {
-        const int e = cand_id[r];
-        float v = 0.0f;
-#pragma unroll
-        for (int j = 0; j < FB_EPL; j++)
-            if (j == (e >> 5)) v = p[j];
-        cand_v[r] = __shfl_sync(FULL, v, e & 31);
-    }
-    for (int a = 1; a < kk; a++) { /* stable insertion by (score desc, index asc) */
-        const float tv = cand_v[a];
-        const int ti = cand_id[a];
-        int b = a - 1;
-        while (b >= 0 && fb_better(tv, ti, cand_v[b], cand_id[b])) {
-            cand_v[b + 1] = cand_v[b];
-            cand_id[b + 1] = cand_id[b];
-            b--;
-        }
-        cand_v[b + 1] = tv;
-        cand_id[b + 1] = ti;
-    }
-    /* renormalise (src/inference.c:496-502) */
-    float ssum = 0.0f;
-    for (int r = 0; r < k; r++) ssum = __fadd_rn(ssum, cand_v[r]);
-    if (ssum > 0.0f) {
-        const float sinv = __fdiv_rn(1.0f, ssum);
-        for (int r = 0; r < k; r++) cand_v[r] = __fmul_rn(cand_v[r], sinv);
-    }
-    if (lane == 0)
-        for (int r = 0; r < k; r++) A.ids_orig[r] = cand_id[r];
-    if (A.freq && lane < k) {
-        int e = 0;
-        for (int r = 0; r < k; r++)
-            if (r == lane) e = cand_id[r];
-        atomicAdd(A.freq + e, 1u); /* histogram counts the ids before substitution (src/gpu_kernels.hip:7832-7835) */
-    }
-
-    /* ---- CAR ---- */
-    int n_subs = 0;
-    if (A.resident && A.car_threshold > 0.0f && A.car_threshold < 1.0f) {
-        /* per-lane view: bit j <-> expert j*32 + lane */
-        uint32_t res = 0, sel = 0;
-#pragma unroll
-        for (int j = 0; j < FB_EPL; j++)
-            if ((__ldg(A.resident + j) >> lane) & 1u) res |= 1u << j;
-        for (int r = 0; r < k; r++)
-            if ((cand_id[r] & 31) == lane) sel |= 1u << (cand_id[r] >> 5);
-        int c_idx[FB_MAX_TOPK], c_best[FB_MAX_TOPK];
-        float c_score[FB_MAX_TOPK], c_ratio[FB_MAX_TOPK];
-        int nc = 0;
-        for (int r = 0; r < k; r++) {
-            const int orig = cand_id[r];
-            const bool cached = (__ldg(A.resident + (orig >> 5)) >> (orig & 31)) & 1u;
-            if (cached) continue; /* uniform across the warp */
-            float bv = 0.0f; /* strict improvement over 0: src/car.c:104-112 */
-            int bi = 0x7fffffff;
-#pragma unroll
-            for (int j = 0; j < FB_EPL; j++) {
-                const int e = j * 32 + lane;
-                if (((res >> j) & 1u) && !((sel >> j) & 1u) && e < nE && p[j] > 0.0f && fb_better(p[j], e, bv, bi)) {
-                    bv = p[j];
-                    bi = e;
-                }
-            }
-            fb_warp_best(bv, bi);
-            float ov = 0.0f;
-#pragma unroll
-            for (int j = 0; j < FB_EPL; j++)
-                if (j == (orig >> 5)) ov = p[j];
-            ov = __shfl_sync(FULL, ov, orig & 31);
-            const float ratio = (ov > 0.0f) ? __fdiv_rn(bv, ov) : 0.0f;
-            if (bi != 0x7fffffff && ratio >= A.car_threshold) {
-                c_idx[nc] = r;
-                c_best[nc] = bi;
-                c_score[nc] = bv;
-                c_ratio[nc] = ratio;
-                nc++;
-                if ((bi & 31) == lane) sel |= 1u << (bi >> 5); /* reserved at once */
-            }
-        }
-        /* stable insertion sort by ratio descending (src/car.c:168-176); application order only
-         * matters with budgets, which are off, but keep the reference's order */
-        for (int a = 1; a < nc; a++) {
-            const int ti = c_idx[a], tb = c_best[a];
-            const float ts = c_score[a], tr = c_ratio[a];
-            int b = a - 1;
-            while (b >= 0 && c_ratio[b] < tr) {
-                c_idx[b + 1] = c_idx[b];
-                c_best[b + 1] = c_best[b];
-                c_score[b + 1] = c_score[b];
-                c_ratio[b + 1] = c_ratio[b];
-                b--;
-            }
-            c_idx[b + 1] = ti;
-            c_best[b + 1] = tb;
-            c_score[b + 1] = ts;
-            c_ratio[b + 1] = tr;
-        }
-        for (int c = 0; c < nc; c++) {
-            for (int r = 0; r < k; r++) {
-                if (r == c_idx[c]) {
-                    cand_id[r] = c_best[c];
-                    cand_v[r] = A.car_dampen ? __fmul_rn(cand_v[r], c_ratio[c]) : c_score[c];
-                }
-            }
-        }
-        n_subs = nc;
-        if (nc > 0 && !A.car_dampen) {
-            float s2 = 0.0f;
-            for (int r = 0; r < k; r++) s2 = __fadd_rn(s2, cand_v[r]);
-            if (s2 > 0.0f) {
-                const float i2 = __fdiv_rn(1.0f, s2);
-                for (int r = 0; r < k; r++) cand_v[r] = __fmul_rn(cand_v[r], i2);
-            }
-        }
-    }
-    if (lane == 0) {
-        for (int r = 0; r < k; r++) {
-            int e = cand_id[r];
-            if (e < 0 || e >= nE) {
-                atomicExch(A.status, FB_ST_BAD_ID);
-                e = 0;
-            }
-            A.ids[r] = e;
-            A.scores[r] = cand_v[r];
-            A.slot_rec[r] = A.table_layer + (uint64_t)e * A.rec_bytes;
-        }
-        if (A.has_shared) {
-            A.ids[k] = nE;
-            A.scores[k] = 1.0f;
-            A.slot_rec[k] = A.table_layer + (uint64_t)nE * A.rec_bytes;
-        }
-        if (n_subs) atomicAdd(A.counters + FB_CNT_SUBS, (unsigned)n_subs);
-    }
-}
-
 __global__ void __launch_bounds__(256) k_router(fb_args_t A) {
     __shared__ int s_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -372,7 +134,7 @@ __global__ void __launch_bounds__(256) k_router(fb_args_t A) {
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    if (warp == 0) fb_route_select(A, lane);
+    if (warp == 0) fb_route_select(A, lane, true);
 }
 
 /* ids/scores given by the caller (operator form: the reference's gpu_expert_ffn takes them) */
@@ -517,6 +279,211 @@ __global__ void __launch_bounds__(256) k_down(fb_args_t A) {
     }
 }
 
+/* ------------------------------------------------------------------ bulk-copy ring variants */
+#define GU_WARPS 8
+#define GU_STAGES 3
+#define GU_STAGE_BYTES (2 * FB_Q4K_GROUP) /* gate group + up group */
+
+/* Same work split and arithmetic as k_gate_up; weights arrive through per-warp rings of
+ * bulk copies and the quantised hidden state sits in registers (a lane always meets the
+ * same 256-column block). */
+__global__ void __launch_bounds__(GU_WARPS * 32, 1) k_gate_up_ring(fb_args_t A) {
+    extern __shared__ __align__(128) uint8_t dsm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int bpr = A.gate_bpr;
+    uint8_t *ring = dsm + (size_t)warp * GU_STAGES * GU_STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(dsm + (size_t)GU_WARPS * GU_STAGES * GU_STAGE_BYTES) + warp * GU_STAGES;
+    const uint32_t ring_u = fb_smem_u32(ring), bar_u = fb_smem_u32(bars);
+    if (lane == 0) {
+        for (int s = 0; s < GU_STAGES; s++) fb_mbar_init(bar_u + 8 * s, 1);
+        fb_mbar_init_fence();
+    }
+    __syncwarp();
+
+    const int rpg = 32 / bpr, gpw = FB_QK / rpg, nwin = A.inter_local / FB_QK;
+    const int total = A.n_slots * A.gate_groups;
+    const int first = blockIdx.x * GU_WARPS + warp, stride = gridDim.x * GU_WARPS;
+    const int n_my = first < total ? (total - first + stride - 1) / stride : 0;
+
+    auto issue = [&](int i) {
+        const int t = first + i * stride;
+        const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
+        const uint8_t *rec = A.slot_rec[slot];
+        const uint32_t st = ring_u + (i % GU_STAGES) * GU_STAGE_BYTES, bar = bar_u + 8 * (i % GU_STAGES);
+        fb_mbar_expect_tx(bar, GU_STAGE_BYTES);
+        fb_bulk_g2s(st, rec + (uint64_t)g * FB_Q4K_GROUP, FB_Q4K_GROUP, bar);
+        fb_bulk_g2s(st + FB_Q4K_GROUP, rec + A.up_off + (uint64_t)g * FB_Q4K_GROUP, FB_Q4K_GROUP, bar);
+    };
+    if (lane == 0)
+        for (int i = 0; i < GU_STAGES && i < n_my; i++) issue(i);
+
+    /* this lane's activation block, in registers */
+    uint4 a[FB_Q8_U4];
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(A.q8h + (lane % bpr));
+#pragma unroll
+        for (int i = 0; i < FB_Q8_U4; i++) a[i] = src[i];
+    }
+
+    for (int i = 0; i < n_my; i++) {
+        const int s = i % GU_STAGES;
+        if (!fb_mbar_wait(bar_u + 8 * s, (i / GU_STAGES) & 1)) {
+            if (lane == 0) atomicExch(A.status, FB_ST_WAIT_TIMEOUT);
+            break;
+        }
+        const uint32_t st = ring_u + s * GU_STAGE_BYTES + 16 * lane;
+        float fg, fu;
+        {
+            const uint4 hd = fb_lds128(st);
+            uint4 q[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) q[k] = fb_lds128(st + 512 * (k + 1));
+            fg = fb_dot_q4k(hd, q, a);
+        }
+        {
+            const uint4 hd = fb_lds128(st + FB_Q4K_GROUP);
+            uint4 q[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) q[k] = fb_lds128(st + FB_Q4K_GROUP + 512 * (k + 1));
+            fu = fb_dot_q4k(hd, q, a);
+        }
+        __syncwarp(); /* every lane has read the stage: refill it */
+        if (lane == 0 && i + GU_STAGES < n_my) issue(i + GU_STAGES);
+        fg = fb_span_sum(fg, bpr);
+        fu = fb_span_sum(fu, bpr);
+        const int t = first + i * stride;
+        const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
+        const int row = g * rpg + lane / bpr;
+        if (lane % bpr == 0 && row < A.inter_local) {
+            const float sl = __fdiv_rn(fg, __fadd_rn(1.0f, expf(-fg)));
+            A.act[slot * A.inter_local + row] = __fmul_rn(sl, fu);
+        }
+        const int win = (g * rpg) / FB_QK;
+        int last = 0;
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence();
+            const unsigned old = atomicAdd(A.counters + FB_CNT_WIN + slot * nwin + win, 1u);
+            last = (old == (unsigned)gpw - 1);
+        }
+        last = __shfl_sync(FULL, last, 0);
+        if (last) {
+            __threadfence();
+            const float *src = A.act + slot * A.inter_local + win * FB_QK + 8 * lane;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = __ldcg(src + j);
+            fb_warp_quantize(v, &A.q8a[slot * nwin + win], lane);
+            if (lane == 0) A.counters[FB_CNT_WIN + slot * nwin + win] = 0;
+        }
+    }
+}
+
+#define DN_STAGES 2
+#define DN_STAGE_BYTES FB_Q6K_GROUP /* room for either type */
+
+/* Down projection + combine inside one block: warp s streams expert slot s's groups, one extra
+ * warp adds the experts up in list order as soon as a row group is complete.  No global scratch,
+ * no atomics: the per-expert results pass through double-buffered shared memory. */
+template <int TYPE>
+__global__ void __launch_bounds__(512, 1) k_down_ring(fb_args_t A) {
+    extern __shared__ __align__(128) uint8_t dsm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ns = A.n_slots, bpr = A.down_bpr, rpg = 32 / bpr;
+    constexpr uint32_t GB = (TYPE == FB_TYPE_Q4_K) ? FB_Q4K_GROUP : FB_Q6K_GROUP;
+    uint8_t *rings = dsm;
+    float *dots = reinterpret_cast<float *>(dsm + (size_t)ns * DN_STAGES * DN_STAGE_BYTES); /* [2][ns][32] */
+    uint64_t *bars = reinterpret_cast<uint64_t *>(dots + 2 * ns * 32);
+    /* bars: full[ns][DN_STAGES], ready[2], empty[2] */
+    const uint32_t bar0 = fb_smem_u32(bars);
+    const uint32_t ready_u = bar0 + 8 * ns * DN_STAGES, empty_u = ready_u + 16;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < ns * DN_STAGES; i++) fb_mbar_init(bar0 + 8 * i, 1);
+        for (int b = 0; b < 2; b++) {
+            fb_mbar_init(ready_u + 8 * b, ns);
+            fb_mbar_init(empty_u + 8 * b, 1);
+        }
+        fb_mbar_init_fence();
+    }
+    __syncthreads();
+    const int n_my = (int)blockIdx.x < A.down_groups ? (A.down_groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+    if (warp < ns) {
+        const int slot = warp;
+        const uint32_t ring_u = fb_smem_u32(rings + (size_t)slot * DN_STAGES * DN_STAGE_BYTES);
+        const uint32_t full_u = bar0 + 8 * slot * DN_STAGES;
+        const uint8_t *base = A.slot_rec[slot] + A.down_off;
+        auto issue = [&](int i) {
+            const int rg = blockIdx.x + i * gridDim.x;
+            const uint32_t bar = full_u + 8 * (i % DN_STAGES);
+            fb_mbar_expect_tx(bar, GB);
+            fb_bulk_g2s(ring_u + (i % DN_STAGES) * DN_STAGE_BYTES, base + (uint64_t)rg * GB, GB, bar);
+        };
+        if (lane == 0)
+            for (int i = 0; i < DN_STAGES && i < n_my; i++) issue(i);
+        uint4 a[FB_Q8_U4];
+        {
+            const uint4 *src = reinterpret_cast<const uint4 *>(A.q8a + slot * bpr + (lane % bpr));
+#pragma unroll
+            for (int i = 0; i < FB_Q8_U4; i++) a[i] = src[i];
+        }
+        for (int i = 0; i < n_my; i++) {
+            const int s = i % DN_STAGES;
+            if (!fb_mbar_wait(full_u + 8 * s, (i / DN_STAGES) & 1)) {
+                if (lane == 0) atomicExch(A.status, FB_ST_WAIT_TIMEOUT);
+                break;
+            }
+            const uint32_t st = ring_u + s * DN_STAGE_BYTES + 16 * lane;
+            float f;
+            if (TYPE == FB_TYPE_Q4_K) {
+                const uint4 hd = fb_lds128(st);
+                uint4 q[8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) q[k] = fb_lds128(st + 512 * (k + 1));
+                f = fb_dot_q4k(hd, q, a);
+            } else {
+                uint4 ql[8], qh[4];
+#pragma unroll
+                for (int k = 0; k < 8; k++) ql[k] = fb_lds128(st + 512 * k);
+#pragma unroll
+                for (int k = 0; k < 4; k++) qh[k] = fb_lds128(st + 512 * (8 + k));
+                const uint4 sc = fb_lds128(st + 512 * 12);
+                uint32_t d16;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d16) : "r"(ring_u + s * DN_STAGE_BYTES + FB_Q6K_OFF_D + 2 * lane));
+                f = fb_dot_q6k(ql, qh, sc, d16, a);
+            }
+            __syncwarp();
+            if (lane == 0 && i + DN_STAGES < n_my) issue(i + DN_STAGES);
+            f = fb_span_sum(f, bpr);
+            const int buf = i & 1;
+            if (i >= 2 && !fb_mbar_wait(empty_u + 8 * buf, ((i >> 1) - 1) & 1)) {
+                if (lane == 0) atomicExch(A.status, FB_ST_WAIT_TIMEOUT);
+                break;
+            }
+            if (lane % bpr == 0) dots[(buf * ns + slot) * 32 + lane / bpr] = f;
+            __syncwarp();
+            if (lane == 0) fb_mbar_arrive(ready_u + 8 * buf);
+        }
+    } else if (warp == ns) {
+        for (int i = 0; i < n_my; i++) {
+            const int buf = i & 1, rg = blockIdx.x + i * gridDim.x;
+            if (!fb_mbar_wait(ready_u + 8 * buf, (i >> 1) & 1)) {
+                if (lane == 0) atomicExch(A.status, FB_ST_WAIT_TIMEOUT);
+                break;
+            }
+            const int r = rg * rpg + lane;
+            if (lane < rpg && r < A.n_embd) {
+                float acc = A.accumulate ? A.moe_out[r] : 0.0f;
+                for (int s = 0; s < A.top_k; s++) acc = __fmaf_rn(A.scores[s], dots[(buf * ns + s) * 32 + lane], acc);
+                if (A.has_shared) acc = __fadd_rn(acc, dots[(buf * ns + A.top_k) * 32 + lane]);
+                A.moe_out[r] = acc;
+            }
+            __syncwarp();
+            if (lane == 0) fb_mbar_arrive(empty_u + 8 * buf);
+        }
+    }
+}
+
 /* ------------------------------------------------------------------ launchers */
 extern "C" int fb_launch_prologue(const fb_args_t *a, int flags, void *stream) {
     k_prologue<<<1, 1024, 0, (cudaStream_t)stream>>>(*a, flags);
@@ -536,6 +503,37 @@ extern "C" int fb_launch_set_slots(const fb_args_t *a, void *stream) {
 extern "C" int fb_launch_gate_up(const fb_args_t *a, int grid, void *stream) {
     const size_t sm = (size_t)a->gate_bpr * sizeof(fb_q8_entry_t);
     k_gate_up<<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int fb_launch_gate_up_ring(const fb_args_t *a, int grid, void *stream) {
+    const size_t sm = (size_t)GU_WARPS * GU_STAGES * GU_STAGE_BYTES + (size_t)GU_WARPS * GU_STAGES * 8;
+    static int configured = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(k_gate_up_ring, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        if (e != cudaSuccess) return (int)e;
+        configured = 1;
+    }
+    k_gate_up_ring<<<grid, GU_WARPS * 32, sm, (cudaStream_t)stream>>>(*a);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int fb_launch_down_ring(const fb_args_t *a, int grid, void *stream) {
+    const int ns = a->n_slots;
+    const size_t sm = (size_t)ns * DN_STAGES * DN_STAGE_BYTES + sizeof(float) * 2 * ns * 32 + 8 * (ns * DN_STAGES + 4);
+    static int configured = 0;
+    if (!configured) {
+        const int mx = FB_MAX_SLOTS * DN_STAGES * DN_STAGE_BYTES + 4 * 2 * FB_MAX_SLOTS * 32 + 8 * (FB_MAX_SLOTS * DN_STAGES + 4);
+        cudaError_t e = cudaFuncSetAttribute(k_down_ring<FB_TYPE_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, mx);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(k_down_ring<FB_TYPE_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, mx);
+        if (e != cudaSuccess) return (int)e;
+        configured = 1;
+    }
+    if (a->down_type == FB_TYPE_Q4_K)
+        k_down_ring<FB_TYPE_Q4_K><<<grid, (ns + 1) * 32, sm, (cudaStream_t)stream>>>(*a);
+    else
+        k_down_ring<FB_TYPE_Q6_K><<<grid, (ns + 1) * 32, sm, (cudaStream_t)stream>>>(*a);
     return (int)cudaGetLastError();
 }
 

@@ -25,7 +25,7 @@ typedef struct {
     int16_t bsums[16];
     float d;
     uint32_t pad[3];
-} fb_q8_entry_t;
+} __attribute__((aligned(16))) fb_q8_entry_t;
 
 /* status word values written by kernels (0 = ok) */
 #define FB_ST_OK 0
@@ -91,6 +91,29 @@ int fb_launch_router(const fb_args_t *a, int grid, void *stream);
 int fb_launch_set_slots(const fb_args_t *a, void *stream);
 int fb_launch_gate_up(const fb_args_t *a, int grid, void *stream);
 int fb_launch_down(const fb_args_t *a, int grid, void *stream);
+/* same phases with weights streamed by bulk copies into per-warp shared-memory rings */
+int fb_launch_gate_up_ring(const fb_args_t *a, int grid, void *stream);
+int fb_launch_down_ring(const fb_args_t *a, int grid, void *stream);
+
+/* ---- the persistent stack kernel: all layers of `tok_count` tokens in one launch ---- */
+typedef struct {
+    const fb_args_t *layers; /* device array, one entry per layer of the range to run */
+    int n_layers;
+    int tok_count;           /* tokens *tok_ctr .. *tok_ctr + tok_count - 1 */
+    const float *tok_in;
+    float *tok_out;
+    unsigned *tok_ctr;
+    unsigned long long *bar; /* grid barrier arrival counter */
+    unsigned long long bar_base; /* its value when this launch starts (the host keeps count) */
+    int *abort_flag;         /* raised by a block that gave up a wait; cleared by the host before a launch */
+    int *status;
+    unsigned long long *trace; /* optional phase stamps of one block (profiling), or NULL */
+    int trace_cap, trace_cta;
+} fb_stack_args_t;
+
+int fb_stack_smem_bytes(void);
+int fb_stack_supported(const fb_args_t *a, int grid);
+int fb_launch_stack(const fb_stack_args_t *k, int grid, void *stream);
 
 /* ---- table construction ---- */
 typedef struct {

@@ -1,0 +1,541 @@
+/*
+ * stack.cu -- the whole decode stack as ONE persistent kernel (sm_100a).
+ *
+ * One block per SM stays resident for every layer of every token of a run and walks the
+ * phases of a routed-MoE layer itself, so nothing returns to the host between the router
+ * and the experts (the reference synchronises with the host once per layer to classify
+ * and run car_evaluate, src/gpu_kernels.hip:6984, 7097-7187) and no kernel boundary drains
+ * the memory pipeline:
+ *
+ *   P0  every block, redundantly: x += moe_out(prev) + resid; h = rmsnorm(x) * w; q8h = Q8_K(h)
+ *       (x lives in registers, 8 elements per thread; src/tensor.c:175-184, src/quant.c:343-375)
+ *   P1  router rows are dealt round-robin to the blocks; each thread multiplies its 8 columns of a
+ *       row (prefetched into registers before the previous layer's barrier) and the block reduces
+ *   --- grid barrier (logits) ---
+ *   SEL every block, redundantly: softmax, ordered top-k, renormalise, CAR (route.cuh)
+ *   P2  gate/up Q4_K dequant-matvec + SwiGLU: (expert, 32-block group) tasks dealt to 16 warps per
+ *       block, weights streamed by bulk copies into per-warp shared-memory rings (stream.cuh)
+ *   --- grid barrier (activations) --- the first down groups are already in flight
+ *   P3  down Q4_K/Q6_K dequant-matvec over (row group, expert) tasks, then the experts of each row group are
+ *       combined in list order with their routing weights into moe_out
+ *   --- grid barrier (moe_out), joined at the top of the next layer after its router rows
+ *       have been requested ---
+ *
+ * Grid barriers are a monotonically increasing 64-bit arrival counter in global memory; every
+ * spin is bounded and, when a limit runs out, the block raises an abort flag that releases all
+ * other blocks, records FB_ST_WAIT_TIMEOUT and returns.  The kernel needs all blocks co-resident:
+ * it is launched cooperatively with one block per SM.
+ */
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "dots.cuh"
+#include "launch.h"
+#include "route.cuh"
+#include "select.cuh"
+#include "stream.cuh"
+
+#define SK_THREADS 512
+#define SK_WARPS 16
+#define SK_DOWN_WARPS 12                              /* expert slots the down phase can serve */
+#define SK_RING_BYTES (SK_DOWN_WARPS * 2 * FB_Q6K_GROUP) /* 161,280 B: 12 x 2 x 6720 or 16 x 2 x 4608 */
+#define SK_MAX_Q8A 48                                 /* n_slots * down blocks per row */
+#define SK_MAX_RG 8                                   /* row groups one block's run of down tasks can touch */
+#define SK_SPIN_LIMIT (1u << 22)
+
+struct sk_smem_t {
+    fb_args_t A;                         /* this layer's arguments */
+    fb_q8_entry_t q8h[16];               /* quantised hidden state */
+    fb_q8_entry_t q8a[SK_MAX_Q8A];       /* quantised activations of every slot */
+    float dots[SK_MAX_RG][SK_DOWN_WARPS][32]; /* per-expert down outputs of this block's row groups */
+    float red[4][SK_WARPS];
+    float all_scores[FB_MAX_EXPERTS];
+    float h[4096];                       /* normalised hidden state (the near-tie arbiter re-sums rows from it) */
+    fb_sel_smem_t sel;
+    int ids[FB_MAX_SLOTS], ids_orig[FB_MAX_SLOTS];
+    float scores[FB_MAX_SLOTS];
+    const uint8_t *slot_rec[FB_MAX_SLOTS];
+    float scale;
+    int ok;
+    uint64_t full[SK_WARPS][2];          /* ring stages */
+};
+
+struct sk_bar_t {
+    unsigned long long *ctr;
+    int *abort_flag;
+    int *status;
+    unsigned grid;
+    unsigned long long base; /* arrivals before this launch */
+    unsigned epoch;          /* barriers this block has arrived at */
+};
+
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ int ld_volatile_s32(const int *p) {
+    int v;
+    asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+/* arrive: everything this block wrote before is visible to blocks that pass the barrier.  The arrival is a
+ * release reduction (no value comes back); the target is computed from the launch's base count and the
+ * number of barriers this block has been through, so polling starts at once. */
+__device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S) {
+    __syncthreads();
+    B.epoch++;
+    if (threadIdx.x == 0)
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(B.ctr), "l"(1ULL) : "memory");
+}
+
+/* wait: returns false (for every thread of the block) when the wait was given up */
+__device__ __forceinline__ bool sk_wait(const sk_bar_t &B, sk_smem_t *S) {
+    if (threadIdx.x == 0) {
+        const unsigned long long target = B.base + (unsigned long long)B.epoch * B.grid;
+        int ok = 1;
+        unsigned n = 0;
+        while (ld_acquire_u64(B.ctr) < target) {
+            if (++n > SK_SPIN_LIMIT || ((n & 63u) == 0 && ld_volatile_s32(B.abort_flag))) {
+                ok = 0;
+                break;
+            }
+        }
+        if (!ok) {
+            atomicExch(B.abort_flag, 1);
+            atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
+        }
+        S->ok = ok;
+    }
+    __syncthreads();
+    return S->ok != 0;
+}
+
+__device__ __forceinline__ unsigned long long sk_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+/* phase stamps of block `trace_cta` (of every block when trace_cta < 0; trace_cap is then per block), in
+ * nanoseconds of %globaltimer, 9 per layer, for profiling only */
+#define SK_STAMP(idx)                                                                        \
+    do {                                                                                     \
+        if (K.trace && (K.trace_cta < 0 || cta == K.trace_cta) && tid == 0 && trace_n < K.trace_cap) \
+            K.trace[(K.trace_cta < 0 ? (size_t)cta * K.trace_cap : 0) + trace_n++] =         \
+                ((unsigned long long)(idx) << 56) | (sk_now() & 0x00ffffffffffffffULL);      \
+    } while (0)
+
+__global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
+    extern __shared__ __align__(128) uint8_t dsm[];
+    uint8_t *ring = dsm;
+    sk_smem_t *S = reinterpret_cast<sk_smem_t *>(dsm + SK_RING_BYTES);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cta = blockIdx.x, G = gridDim.x;
+    const bool leader = (cta == 0);
+    sk_bar_t B = {K.bar, K.abort_flag, K.status, (unsigned)G, K.bar_base, 0u};
+
+    const uint32_t full_u = fb_smem_u32(&S->full[warp][0]);
+    if (tid == 0) {
+        for (int w = 0; w < SK_WARPS; w++)
+            for (int s = 0; s < 2; s++) fb_mbar_init(fb_smem_u32(&S->full[w][s]), 1);
+        fb_mbar_init_fence();
+    }
+    __syncthreads();
+    uint32_t full_uses[2] = {0, 0}; /* completed phases of this warp's two stage barriers */
+
+    const unsigned tok_first = *K.tok_ctr;
+    int trace_n = 0;
+    bool alive = true;
+    bool pending_join = false; /* a barrier has been arrived at but not yet waited for */
+
+    for (int tk = 0; tk < K.tok_count && alive; tk++) {
+        const unsigned tok = tok_first + (unsigned)tk;
+        float x[8];
+        for (int l = 0; l < K.n_layers && alive; l++) {
+            /* ---- this layer's arguments into shared memory */
+            {
+                const uint32_t *src = reinterpret_cast<const uint32_t *>(K.layers + l);
+                uint32_t *dst = reinterpret_cast<uint32_t *>(&S->A);
+                for (int i = tid; i < (int)(sizeof(fb_args_t) / 4); i += SK_THREADS) dst[i] = src[i];
+            }
+            __syncthreads();
+            const fb_args_t &A = S->A;
+            const int n = A.n_embd, e0 = 8 * tid;
+            const bool own = e0 < n;
+
+            /* ---- router rows of this block: request them now, they depend on nothing */
+            float4 wr[4][2];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int row = cta + j * G;
+                if (own && row < A.n_experts) {
+                    const float4 *p = reinterpret_cast<const float4 *>(A.router_w + (size_t)row * n + e0);
+                    wr[j][0] = __ldg(p);
+                    wr[j][1] = __ldg(p + 1);
+                } else {
+                    wr[j][0] = wr[j][1] = make_float4(0, 0, 0, 0);
+                }
+            }
+            float4 r0 = make_float4(0, 0, 0, 0), r1 = r0, w0 = make_float4(1, 1, 1, 1), w1 = w0;
+            if (own) { /* residual and norm weight of this layer: constants, requested before the join as well */
+                const float4 *r = reinterpret_cast<const float4 *>(A.resid + e0);
+                const float4 *wp = reinterpret_cast<const float4 *>(A.normw + e0);
+                r0 = __ldg(r);
+                r1 = __ldg(r + 1);
+                w0 = __ldg(wp);
+                w1 = __ldg(wp + 1);
+            }
+            SK_STAMP(0);
+            /* ---- join the barrier that publishes the previous layer's moe_out */
+            if (pending_join) {
+                alive = sk_wait(B, S);
+                pending_join = false;
+                if (!alive) break;
+            }
+
+            SK_STAMP(1);
+            /* ---- P0: residual stream, RMSNorm, Q8_K */
+            float ss = 0.0f;
+            if (own) {
+                float4 v0, v1;
+                if (l == 0) {
+                    const float4 *p = reinterpret_cast<const float4 *>(K.tok_in + (size_t)tok * n + e0);
+                    v0 = p[0];
+                    v1 = p[1];
+                } else {
+                    const float4 *m = reinterpret_cast<const float4 *>(A.moe_out + e0);
+                    const float4 m0 = __ldcg(m), m1 = __ldcg(m + 1);
+                    v0 = make_float4(__fadd_rn(x[0], m0.x), __fadd_rn(x[1], m0.y), __fadd_rn(x[2], m0.z), __fadd_rn(x[3], m0.w));
+                    v1 = make_float4(__fadd_rn(x[4], m1.x), __fadd_rn(x[5], m1.y), __fadd_rn(x[6], m1.z), __fadd_rn(x[7], m1.w));
+                }
+                x[0] = __fadd_rn(v0.x, r0.x); x[1] = __fadd_rn(v0.y, r0.y); x[2] = __fadd_rn(v0.z, r0.z); x[3] = __fadd_rn(v0.w, r0.w);
+                x[4] = __fadd_rn(v1.x, r1.x); x[5] = __fadd_rn(v1.y, r1.y); x[6] = __fadd_rn(v1.z, r1.z); x[7] = __fadd_rn(v1.w, r1.w);
+#pragma unroll
+                for (int i = 0; i < 8; i++) ss = __fmaf_rn(x[i], x[i], ss);
+            }
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(FULL, ss, o);
+            if (lane == 0) S->red[0][warp] = ss;
+            __syncthreads();
+            if (tid == 0) {
+                float t = 0.0f;
+                for (int w = 0; w < SK_WARPS; w++) t += S->red[0][w];
+                S->scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)n), A.rms_eps)));
+            }
+            __syncthreads();
+            float h[8];
+            {
+                const float sc = S->scale;
+                const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int i = 0; i < 8; i++) h[i] = own ? __fmul_rn(__fmul_rn(x[i], sc), wv[i]) : 0.0f;
+            }
+            if (warp < n / FB_QK) fb_warp_quantize(h, &S->q8h[warp], lane);
+            if (own) {
+                float4 *hp = reinterpret_cast<float4 *>(S->h + e0);
+                hp[0] = make_float4(h[0], h[1], h[2], h[3]);
+                hp[1] = make_float4(h[4], h[5], h[6], h[7]);
+                if (leader) { /* kept in global memory as well, for inspection from the host */
+                    float4 *gp = reinterpret_cast<float4 *>(A.h + e0);
+                    gp[0] = hp[0];
+                    gp[1] = hp[1];
+                }
+            }
+
+            SK_STAMP(2);
+            /* ---- P1: router logits of this block's rows */
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float p = 0.0f;
+                p = fmaf(wr[j][0].x, h[0], p); p = fmaf(wr[j][0].y, h[1], p); p = fmaf(wr[j][0].z, h[2], p); p = fmaf(wr[j][0].w, h[3], p);
+                p = fmaf(wr[j][1].x, h[4], p); p = fmaf(wr[j][1].y, h[5], p); p = fmaf(wr[j][1].z, h[6], p); p = fmaf(wr[j][1].w, h[7], p);
+                for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(FULL, p, o);
+                if (lane == 0) S->red[j][warp] = p;
+            }
+            __syncthreads();
+            if (tid < 4) {
+                const int row = cta + tid * G;
+                if (row < A.n_experts) {
+                    float t = 0.0f;
+                    for (int w = 0; w < SK_WARPS; w++) t += S->red[tid][w];
+                    A.logits[row] = t;
+                }
+            }
+            for (int row = cta + 4 * G; row < A.n_experts; row += G) { /* more than 4 rows per block: rare shapes */
+                float p = 0.0f;
+                if (own) {
+                    const float4 *q = reinterpret_cast<const float4 *>(A.router_w + (size_t)row * n + e0);
+                    const float4 a0 = __ldg(q), a1 = __ldg(q + 1);
+                    p = fmaf(a0.x, h[0], p); p = fmaf(a0.y, h[1], p); p = fmaf(a0.z, h[2], p); p = fmaf(a0.w, h[3], p);
+                    p = fmaf(a1.x, h[4], p); p = fmaf(a1.y, h[5], p); p = fmaf(a1.z, h[6], p); p = fmaf(a1.w, h[7], p);
+                }
+                for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(FULL, p, o);
+                __syncthreads();
+                if (lane == 0) S->red[0][warp] = p;
+                __syncthreads();
+                if (tid == 0) {
+                    float t = 0.0f;
+                    for (int w = 0; w < SK_WARPS; w++) t += S->red[0][w];
+                    A.logits[row] = t;
+                }
+            }
+            SK_STAMP(3);
+            sk_arrive(B, S);
+            alive = sk_wait(B, S);
+            if (!alive) break;
+            SK_STAMP(4);
+
+            /* ---- SEL: routing, redundantly in every block (results identical by construction) */
+            fb_block_select(A, &S->sel, S->h, S->all_scores, S->ids, S->ids_orig, S->scores, S->slot_rec, leader);
+            if (leader) {
+                if (tid < A.n_slots) {
+                    A.ids[tid] = S->ids[tid];
+                    A.scores[tid] = S->scores[tid];
+                    if (tid < A.top_k) A.ids_orig[tid] = S->ids_orig[tid];
+                }
+                for (int e = tid; e < A.n_experts; e += SK_THREADS) A.all_scores[e] = S->all_scores[e];
+            }
+
+            SK_STAMP(5);
+            /* ---- P2: gate/up + SwiGLU.  Tasks = (expert slot, 32-block group) in slot-major order; every block owns
+             *      a contiguous, equally long run of them (so all SMs stream the same number of bytes) and deals
+             *      its run round-robin to its 16 warps. */
+            {
+                const int bpr = A.gate_bpr, rpg = 32 / bpr;
+                const int total = A.n_slots * A.gate_groups;
+                const int t0 = (int)(((long long)cta * total) / G), t1 = (int)(((long long)(cta + 1) * total) / G);
+                const uint32_t ring_u = fb_smem_u32(ring) + warp * 2 * FB_Q4K_GROUP;
+                auto issue = [&](int t, int which) {
+                    const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
+                    const uint8_t *src = S->slot_rec[slot] + (which ? A.up_off : 0) + (uint64_t)g * FB_Q4K_GROUP;
+                    fb_mbar_expect_tx(full_u + 8 * which, FB_Q4K_GROUP);
+                    fb_bulk_g2s(ring_u + which * FB_Q4K_GROUP, src, FB_Q4K_GROUP, full_u + 8 * which);
+                };
+                if (lane == 0 && t0 + warp < t1) {
+                    issue(t0 + warp, 0);
+                    issue(t0 + warp, 1);
+                }
+                uint4 a[FB_Q8_U4];
+                {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(&S->q8h[lane % bpr]);
+#pragma unroll
+                    for (int i = 0; i < FB_Q8_U4; i++) a[i] = src[i];
+                }
+                for (int t = t0 + warp; t < t1 && alive; t += SK_WARPS) {
+                    float f[2];
+#pragma unroll
+                    for (int which = 0; which < 2; which++) {
+                        if (!fb_mbar_wait(full_u + 8 * which, full_uses[which] & 1)) {
+                            alive = false;
+                            break;
+                        }
+                        full_uses[which]++;
+                        const uint32_t st = ring_u + which * FB_Q4K_GROUP + 16 * lane;
+                        const uint4 hd = fb_lds128(st);
+                        uint4 q[8];
+#pragma unroll
+                        for (int k = 0; k < 8; k++) q[k] = fb_lds128(st + 512 * (k + 1));
+                        __syncwarp();
+                        if (lane == 0 && t + SK_WARPS < t1) issue(t + SK_WARPS, which);
+                        f[which] = fb_dot_q4k(hd, q, a);
+                    }
+                    if (!alive) break;
+                    const float fg = fb_span_sum(f[0], bpr), fu = fb_span_sum(f[1], bpr);
+                    const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
+                    const int row = g * rpg + lane / bpr;
+                    if (lane % bpr == 0 && row < A.inter_local) {
+                        const float sl = __fdiv_rn(fg, __fadd_rn(1.0f, expf(-fg)));
+                        A.act[slot * A.inter_local + row] = __fmul_rn(sl, fu);
+                    }
+                }
+                if (!__syncthreads_and(alive ? 1 : 0)) {
+                    if (tid == 0) {
+                        atomicExch(B.abort_flag, 1);
+                        atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
+                    }
+                    alive = false;
+                    break;
+                }
+            }
+
+            SK_STAMP(6);
+            /* ---- barrier (activations); this block's first down groups are requested while it completes.
+             *      P3 tasks = (row group, expert slot) in row-group-major order, again one contiguous, equally
+             *      long run per block dealt round-robin to 12 warps (two ring stages of one group each). */
+            sk_arrive(B, S);
+            const int ns = A.n_slots, dbpr = A.down_bpr, drpg = 32 / dbpr;
+            const uint32_t GB = (A.down_type == FB_TYPE_Q4_K) ? FB_Q4K_GROUP : FB_Q6K_GROUP;
+            const int dtotal = A.down_groups * ns;
+            const int d0 = (int)(((long long)cta * dtotal) / G), d1 = (int)(((long long)(cta + 1) * dtotal) / G);
+            const uint32_t dring_u = fb_smem_u32(ring) + warp * 2 * FB_Q6K_GROUP;
+            auto dissue = [&](int t, int s) {
+                const int rg = t / ns, slot = t - rg * ns;
+                fb_mbar_expect_tx(full_u + 8 * s, GB);
+                fb_bulk_g2s(dring_u + s * FB_Q6K_GROUP, S->slot_rec[slot] + A.down_off + (uint64_t)rg * GB, GB, full_u + 8 * s);
+            };
+            if (warp < SK_DOWN_WARPS && lane == 0)
+                for (int i = 0; i < 2; i++)
+                    if (d0 + warp + i * SK_DOWN_WARPS < d1) dissue(d0 + warp + i * SK_DOWN_WARPS, i);
+            alive = sk_wait(B, S);
+            if (!alive) break;
+            SK_STAMP(7);
+
+            /* ---- P3: down + combine */
+            for (int wd = warp; wd < ns * dbpr; wd += SK_WARPS) { /* quantise the activations (src/cpu_expert.c:109-110) */
+                const float *src = A.act + (wd / dbpr) * A.inter_local + (wd % dbpr) * FB_QK + 8 * lane;
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = __ldcg(src + j);
+                fb_warp_quantize(v, &S->q8a[wd], lane);
+            }
+            __syncthreads();
+            const int rg_first = d0 < d1 ? d0 / ns : 0;
+            if (warp < SK_DOWN_WARPS) {
+                int it = 0;
+                for (int t = d0 + warp; t < d1; t += SK_DOWN_WARPS, it++) {
+                    const int s = it & 1;
+                    if (!fb_mbar_wait(full_u + 8 * s, full_uses[s] & 1)) {
+                        alive = false;
+                        break;
+                    }
+                    full_uses[s]++;
+                    const int rg = t / ns, slot = t - rg * ns;
+                    const uint32_t st = dring_u + s * FB_Q6K_GROUP + 16 * lane;
+                    uint4 a[FB_Q8_U4];
+                    {
+                        const uint4 *src = reinterpret_cast<const uint4 *>(&S->q8a[slot * dbpr + lane % dbpr]);
+#pragma unroll
+                        for (int i = 0; i < FB_Q8_U4; i++) a[i] = src[i];
+                    }
+                    float f;
+                    if (A.down_type == FB_TYPE_Q4_K) {
+                        const uint4 hd = fb_lds128(st);
+                        uint4 q[8];
+#pragma unroll
+                        for (int k = 0; k < 8; k++) q[k] = fb_lds128(st + 512 * (k + 1));
+                        __syncwarp();
+                        if (lane == 0 && t + 2 * SK_DOWN_WARPS < d1) dissue(t + 2 * SK_DOWN_WARPS, s);
+                        f = fb_dot_q4k(hd, q, a);
+                    } else {
+                        uint4 ql[8], qh[4];
+#pragma unroll
+                        for (int k = 0; k < 8; k++) ql[k] = fb_lds128(st + 512 * k);
+#pragma unroll
+                        for (int k = 0; k < 4; k++) qh[k] = fb_lds128(st + 512 * (8 + k));
+                        const uint4 sc = fb_lds128(st + 512 * 12);
+                        uint32_t d16;
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d16) : "r"(dring_u + s * FB_Q6K_GROUP + FB_Q6K_OFF_D + 2 * lane));
+                        __syncwarp();
+                        if (lane == 0 && t + 2 * SK_DOWN_WARPS < d1) dissue(t + 2 * SK_DOWN_WARPS, s);
+                        f = fb_dot_q6k(ql, qh, sc, d16, a);
+                    }
+                    f = fb_span_sum(f, dbpr);
+                    if (lane % dbpr == 0) S->dots[rg - rg_first][slot][lane / dbpr] = f;
+                }
+            }
+            if (!__syncthreads_and(alive ? 1 : 0)) {
+                if (tid == 0) {
+                    atomicExch(B.abort_flag, 1);
+                    atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
+                }
+                alive = false;
+                break;
+            }
+            /* combine: partial += score * down in list order (src/cpu_expert.c:114-115), shared expert added after
+             * (src/inference.c:595).  A row group whose slots all ran in this block is combined from shared memory;
+             * one split between two blocks goes through global memory and is combined by whichever finishes last. */
+            if (d0 < d1) {
+                const int rg_last = (d1 - 1) / ns;
+                unsigned *cnt_rg = A.counters + FB_CNT_WIN + FB_MAX_SLOTS * 32;
+                for (int q = warp; q <= rg_last - rg_first; q += SK_WARPS) {
+                    const int rg = rg_first + q;
+                    const int s_lo = max(d0, rg * ns) - rg * ns, s_hi = min(d1, (rg + 1) * ns) - rg * ns;
+                    const int r = rg * drpg + lane;
+                    const bool row_ok = lane < drpg && r < n;
+                    if (s_lo == 0 && s_hi == ns) {
+                        if (row_ok) {
+                            float acc = 0.0f;
+                            for (int s = 0; s < A.top_k; s++) acc = __fmaf_rn(S->scores[s], S->dots[q][s][lane], acc);
+                            if (A.has_shared) acc = __fadd_rn(acc, S->dots[q][A.top_k][lane]);
+                            A.moe_out[r] = acc;
+                        }
+                    } else {
+                        if (row_ok)
+                            for (int s = s_lo; s < s_hi; s++) A.dots[s * n + r] = S->dots[q][s][lane];
+                        __syncwarp();
+                        int last = 0;
+                        if (lane == 0) {
+                            __threadfence();
+                            const unsigned old = atomicAdd(cnt_rg + rg, (unsigned)(s_hi - s_lo));
+                            last = (old + (unsigned)(s_hi - s_lo) == (unsigned)ns);
+                        }
+                        last = __shfl_sync(FULL, last, 0);
+                        if (last) {
+                            __threadfence();
+                            if (row_ok) {
+                                float acc = 0.0f;
+                                for (int s = 0; s < A.top_k; s++) acc = __fmaf_rn(S->scores[s], __ldcg(A.dots + s * n + r), acc);
+                                if (A.has_shared) acc = __fadd_rn(acc, __ldcg(A.dots + A.top_k * n + r));
+                                A.moe_out[r] = acc;
+                            }
+                            if (lane == 0) cnt_rg[rg] = 0;
+                        }
+                    }
+                }
+            }
+            SK_STAMP(8);
+            sk_arrive(B, S);
+            pending_join = true;
+        } /* layers */
+        if (!alive) break;
+        /* ---- end of token: join the last barrier, x += moe_out, publish */
+        alive = sk_wait(B, S);
+        pending_join = false;
+        if (!alive) break;
+        if (leader) {
+            const fb_args_t &A = S->A;
+            const int e0 = 8 * tid;
+            if (e0 < A.n_embd) {
+                const float4 *m = reinterpret_cast<const float4 *>(A.moe_out + e0);
+                const float4 m0 = __ldcg(m), m1 = __ldcg(m + 1);
+                float4 *o = reinterpret_cast<float4 *>(K.tok_out + (size_t)tok * A.n_embd + e0);
+                o[0] = make_float4(__fadd_rn(x[0], m0.x), __fadd_rn(x[1], m0.y), __fadd_rn(x[2], m0.z), __fadd_rn(x[3], m0.w));
+                o[1] = make_float4(__fadd_rn(x[4], m1.x), __fadd_rn(x[5], m1.y), __fadd_rn(x[6], m1.z), __fadd_rn(x[7], m1.w));
+                float4 *xo = reinterpret_cast<float4 *>(A.x + e0);
+                xo[0] = o[0];
+                xo[1] = o[1];
+            }
+        }
+        __syncthreads(); /* S->A is rewritten at the top of the next token */
+        /* the next token's P0 overwrites nothing another block still reads before its own first
+         * barrier, except moe_out, which is only rewritten after two more barriers */
+    }
+    if (leader && tid == 0 && alive) *K.tok_ctr = tok_first + (unsigned)K.tok_count;
+}
+
+extern "C" int fb_stack_smem_bytes(void) { return (int)(SK_RING_BYTES + sizeof(sk_smem_t)); }
+
+extern "C" int fb_stack_supported(const fb_args_t *a, int grid) {
+    const int dtotal = a->down_groups * a->n_slots;
+    const int run = (dtotal + grid - 1) / grid;                       /* longest run of down tasks of one block */
+    const int max_rg = (run + a->n_slots - 2) / a->n_slots + 2;       /* row groups such a run can touch */
+    return a->n_embd <= 4096 && a->n_slots <= SK_DOWN_WARPS && a->n_slots * a->down_bpr <= SK_MAX_Q8A &&
+           a->n_embd / FB_QK <= 16 && a->tp_size == 1 && max_rg <= SK_MAX_RG;
+}
+
+extern "C" int fb_launch_stack(const fb_stack_args_t *k, int grid, void *stream) {
+    static int configured = 0;
+    const int sm = fb_stack_smem_bytes();
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(k_stack, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
+        if (e != cudaSuccess) return (int)e;
+        configured = 1;
+    }
+    fb_stack_args_t kk = *k;
+    void *params[] = {&kk};
+    return (int)cudaLaunchCooperativeKernel((const void *)k_stack, dim3(grid), dim3(SK_THREADS), params, (size_t)sm,
+                                            (cudaStream_t)stream);
+}

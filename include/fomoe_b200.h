@@ -167,7 +167,18 @@ int fomoe_b200_get_routing(fomoe_b200_ctx_t *ctx, int layer, int *ids, float *sc
 /* Counters since creation: CAR substitutions, kernels launched by this library. */
 uint64_t fomoe_b200_substitutions(fomoe_b200_ctx_t *ctx);
 uint64_t fomoe_b200_kernel_launches(fomoe_b200_ctx_t *ctx);
-/* 1: replay each token as one CUDA graph (default), 0: plain stream launches. */
+/* Profiling aid for the persistent stack kernel: record up to `cap` %globaltimer stamps of block `cta` at its
+ * phase boundaries during the following runs (cap 0 = off; cta < 0 = every block, `cap` stamps each, block-major);
+ * trace_read copies the first n out.  Each word is
+ * (index << 56) | nanoseconds; index 0 layer top, 1 previous barrier joined, 2 RMSNorm/Q8_K done, 3 router rows
+ * done, 4 logits barrier passed, 5 routing done, 6 gate/up done, 7 activation barrier passed, 8 down done. */
+int fomoe_b200_trace_enable(fomoe_b200_ctx_t *ctx, int cap, int cta);
+int fomoe_b200_trace_read(fomoe_b200_ctx_t *ctx, unsigned long long *out, int n);
+/* Execution variant: 2 (default) the persistent stack kernel runs whole tokens (stack_run, tokens_run,
+ * decode_token) and per-phase kernels serve the single-layer calls; 0 per-phase kernels with plain
+ * coalesced loads everywhere; 1 per-phase kernels with bulk-copy shared-memory rings. */
+int fomoe_b200_set_variant(fomoe_b200_ctx_t *ctx, int variant);
+/* For the per-phase variants: 1 replays each token as one CUDA graph (default), 0 plain stream launches. */
 int fomoe_b200_set_graphs(fomoe_b200_ctx_t *ctx, int enable);
 
 /* Copy an intermediate of the most recent layer call to the host (parity tests look inside the
