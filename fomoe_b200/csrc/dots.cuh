@@ -114,6 +114,102 @@ __device__ __forceinline__ float fb_dot_q6k(const uint4 (&ql)[8], const uint4 (&
     return __fmul_rn(d, (float)total);
 }
 
+
+/* ---- the same two dots with the activation entry left in SHARED memory (a_u = its shared-space address) and
+ * read sixteen bytes at a time where it is used.  A Q8_K entry is 76 registers wide; holding it in registers
+ * next to a whole weight block overflowed the register file of the persistent kernel, so there the activations
+ * stay in shared memory (reads of one entry by the lanes that share it are broadcasts). */
+__device__ __forceinline__ uint4 fb_lds128_a(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ float fb_dot_q4k_sm(const uint4 &hdr, const uint4 (&qs)[8], uint32_t a_u) {
+    const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+    const uint32_t sc_lo = u0 & 0x3f3f3f3fu;
+    const uint32_t sc_hi = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
+    const uint32_t m_lo = u1 & 0x3f3f3f3fu;
+    const uint32_t m_hi = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
+    int isum = 0;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        int lo = 0, hi = 0;
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            const uint4 w = qs[2 * c + kk];
+            const uint4 al = fb_lds128_a(a_u + 16 * (4 * c + kk));
+            const uint4 ah = fb_lds128_a(a_u + 16 * (4 * c + 2 + kk));
+            lo = fb_dp4a(w.x & 0x0f0f0f0fu, al.x, lo);
+            lo = fb_dp4a(w.y & 0x0f0f0f0fu, al.y, lo);
+            lo = fb_dp4a(w.z & 0x0f0f0f0fu, al.z, lo);
+            lo = fb_dp4a(w.w & 0x0f0f0f0fu, al.w, lo);
+            hi = fb_dp4a((w.x >> 4) & 0x0f0f0f0fu, ah.x, hi);
+            hi = fb_dp4a((w.y >> 4) & 0x0f0f0f0fu, ah.y, hi);
+            hi = fb_dp4a((w.z >> 4) & 0x0f0f0f0fu, ah.z, hi);
+            hi = fb_dp4a((w.w >> 4) & 0x0f0f0f0fu, ah.w, hi);
+        }
+        const uint32_t scw = (c < 2) ? sc_lo : sc_hi;
+        const int s0 = (scw >> (16 * (c & 1))) & 0xff, s1 = (scw >> (16 * (c & 1) + 8)) & 0xff;
+        isum += s0 * lo + s1 * hi;
+    }
+    const uint4 b0 = fb_lds128_a(a_u + 256), b1 = fb_lds128_a(a_u + 272);
+    int msum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const uint32_t pr = fb_u4c(j < 4 ? b0 : b1, j & 3);
+        const int bs = (int)(short)(pr & 0xffff) + (int)(short)(pr >> 16);
+        const uint32_t mw = (j < 4) ? m_lo : m_hi;
+        msum += (int)((mw >> (8 * (j & 3))) & 0xff) * bs;
+    }
+    float yd;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(yd) : "r"(a_u + 288));
+    const float d = __fmul_rn(yd, fb_half_bits_to_float(hdr.x & 0xffff));
+    const float dmin = __fmul_rn(yd, fb_half_bits_to_float(hdr.x >> 16));
+    return __fmaf_rn(d, (float)isum, -__fmul_rn(dmin, (float)msum));
+}
+
+__device__ __forceinline__ float fb_dot_q6k_sm(const uint4 (&ql)[8], const uint4 (&qh)[4], const uint4 &sc,
+                                               uint32_t d16, uint32_t a_u) {
+    int total = 0;
+    const uint4 b0 = fb_lds128_a(a_u + 256), b1 = fb_lds128_a(a_u + 272);
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+#pragma unroll
+        for (int tq = 0; tq < 2; tq++) {
+            const uint4 A = ql[4 * h + tq], B = ql[4 * h + 2 + tq], H = qh[2 * h + tq];
+            const uint4 a0 = fb_lds128_a(a_u + 16 * (8 * h + 0 + tq)), a1 = fb_lds128_a(a_u + 16 * (8 * h + 2 + tq));
+            const uint4 a2 = fb_lds128_a(a_u + 16 * (8 * h + 4 + tq)), a3 = fb_lds128_a(a_u + 16 * (8 * h + 6 + tq));
+            int d0 = 0, d1 = 0, d2 = 0, d3 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t qa = fb_u4c(A, i), qb = fb_u4c(B, i), hh = fb_u4c(H, i);
+                const uint32_t v0 = (qa & 0x0f0f0f0fu) | ((hh << 4) & 0x30303030u);
+                const uint32_t v1 = (qb & 0x0f0f0f0fu) | ((hh << 2) & 0x30303030u);
+                const uint32_t v2 = ((qa >> 4) & 0x0f0f0f0fu) | (hh & 0x30303030u);
+                const uint32_t v3 = ((qb >> 4) & 0x0f0f0f0fu) | ((hh >> 2) & 0x30303030u);
+                d0 = fb_dp4a(v0, fb_u4c(a0, i), d0);
+                d1 = fb_dp4a(v1, fb_u4c(a1, i), d1);
+                d2 = fb_dp4a(v2, fb_u4c(a2, i), d2);
+                d3 = fb_dp4a(v3, fb_u4c(a3, i), d3);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int g = 8 * h + 2 * i + tq;
+                const uint32_t pr = fb_u4c(g < 8 ? b0 : b1, (g & 7) >> 1);
+                const int bs = (g & 1) ? (int)(short)(pr >> 16) : (int)(short)(pr & 0xffff);
+                const int scv = (int)(signed char)((fb_u4c(sc, g >> 2) >> (8 * (g & 3))) & 0xff);
+                const int dv = i == 0 ? d0 : i == 1 ? d1 : i == 2 ? d2 : d3;
+                total += scv * (dv - 32 * bs);
+            }
+        }
+    }
+    float yd;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(yd) : "r"(a_u + 288));
+    const float d = __fmul_rn(yd, fb_half_bits_to_float(d16));
+    return __fmul_rn(d, (float)total);
+}
+
 /* Sum over the `span` consecutive lanes (span a power of two <= 32) that share a row. */
 __device__ __forceinline__ float fb_span_sum(float v, int span) {
     for (int o = span >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -275,7 +275,7 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
         dev_alloc(c, (void **)&c->counters, sizeof(unsigned) * (FB_CNT_WIN + FB_MAX_SLOTS * 32 + c->down_groups)) ||
         dev_alloc(c, (void **)&c->status, sizeof(int)) || dev_alloc(c, (void **)&c->tok_ctr, sizeof(unsigned)) ||
         dev_alloc(c, (void **)&c->d_layer_args, sizeof(fb_args_t) * (uint64_t)nl) ||
-        dev_alloc(c, (void **)&c->d_bar, sizeof(unsigned long long)) || dev_alloc(c, (void **)&c->d_abort, sizeof(int)) ||
+        dev_alloc(c, (void **)&c->d_bar, 32 * sizeof(unsigned long long)) || dev_alloc(c, (void **)&c->d_abort, sizeof(int)) ||
         dev_alloc(c, (void **)&c->tok_in, sizeof(float) * (uint64_t)(c->max_tokens + 1) * ne) ||
         dev_alloc(c, (void **)&c->tok_out, sizeof(float) * (uint64_t)(c->max_tokens + 1) * ne))
         goto fail;
@@ -300,7 +300,8 @@ int fomoe_b200_status(fomoe_b200_ctx_t *c) {
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1;
     if (cudaMemcpy(&st, c->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     if (st == FB_ST_WAIT_TIMEOUT) { /* a stack launch gave up: its barrier count is unknown, start over */
-        cudaMemset(c->d_bar, 0, sizeof(unsigned long long));
+        cudaMemset(c->d_bar, 0, 32 * sizeof(unsigned long long));
+        cudaMemset(c->counters, 0, sizeof(unsigned) * (FB_CNT_WIN + FB_MAX_SLOTS * 32 + c->down_groups));
         c->bar_count = 0;
     }
     return st;

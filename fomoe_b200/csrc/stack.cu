@@ -43,6 +43,7 @@
 #define SK_MAX_Q8A 48                                 /* n_slots * down blocks per row */
 #define SK_MAX_RG 8                                   /* row groups one block's run of down tasks can touch */
 #define SK_SPIN_LIMIT (1u << 22)
+#define SK_BAR_THREAD (SK_THREADS - 32) /* lane 0 of the last warp runs the grid barrier; it issues no copies */
 
 struct sk_smem_t {
     fb_args_t A;                         /* this layer's arguments */
@@ -82,23 +83,30 @@ __device__ __forceinline__ int ld_volatile_s32(const int *p) {
     return v;
 }
 
-/* arrive: everything this block wrote before is visible to blocks that pass the barrier.  The arrival is a
- * release reduction (no value comes back); the target is computed from the launch's base count and the
- * number of barriers this block has been through, so polling starts at once. */
+/* Grid barrier.  Arrivals are counted on one cache line (an atomic that returns the count, so the last block
+ * knows it is last); the last block then publishes the barrier's generation number on ANOTHER line, which is the
+ * only one the waiting blocks poll.  Keeping the polls off the arrival line matters: 148 pollers on the line the
+ * atomics land on made every barrier cost several microseconds.  Both words only ever grow; the host tells the
+ * kernel where they stand when a launch starts. */
 __device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S) {
     __syncthreads();
     B.epoch++;
-    if (threadIdx.x == 0)
-        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(B.ctr), "l"(1ULL) : "memory");
+    if (threadIdx.x == SK_BAR_THREAD) {
+        unsigned long long old;
+        asm volatile("atom.add.acq_rel.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
+        const unsigned long long gen = B.base / B.grid + B.epoch;
+        if (old + 1ULL == gen * B.grid)
+            asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(B.ctr + 16), "l"(gen) : "memory");
+    }
 }
 
 /* wait: returns false (for every thread of the block) when the wait was given up */
 __device__ __forceinline__ bool sk_wait(const sk_bar_t &B, sk_smem_t *S) {
-    if (threadIdx.x == 0) {
-        const unsigned long long target = B.base + (unsigned long long)B.epoch * B.grid;
+    if (threadIdx.x == SK_BAR_THREAD) {
+        const unsigned long long gen = B.base / B.grid + B.epoch;
         int ok = 1;
         unsigned n = 0;
-        while (ld_acquire_u64(B.ctr) < target) {
+        while (ld_acquire_u64(B.ctr + 16) < gen) {
             if (++n > SK_SPIN_LIMIT || ((n & 63u) == 0 && ld_volatile_s32(B.abort_flag))) {
                 ok = 0;
                 break;
@@ -318,12 +326,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     issue(t0 + warp, 0);
                     issue(t0 + warp, 1);
                 }
-                uint4 a[FB_Q8_U4];
-                {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(&S->q8h[lane % bpr]);
-#pragma unroll
-                    for (int i = 0; i < FB_Q8_U4; i++) a[i] = src[i];
-                }
+                const uint32_t a_u = fb_smem_u32(&S->q8h[lane % bpr]);
                 for (int t = t0 + warp; t < t1 && alive; t += SK_WARPS) {
                     float f[2];
 #pragma unroll
@@ -340,7 +343,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         for (int k = 0; k < 8; k++) q[k] = fb_lds128(st + 512 * (k + 1));
                         __syncwarp();
                         if (lane == 0 && t + SK_WARPS < t1) issue(t + SK_WARPS, which);
-                        f[which] = fb_dot_q4k(hd, q, a);
+                        f[which] = fb_dot_q4k_sm(hd, q, a_u);
                     }
                     if (!alive) break;
                     const float fg = fb_span_sum(f[0], bpr), fu = fb_span_sum(f[1], bpr);
@@ -370,6 +373,13 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             const uint32_t GB = (A.down_type == FB_TYPE_Q4_K) ? FB_Q4K_GROUP : FB_Q6K_GROUP;
             const int dtotal = A.down_groups * ns;
             const int d0 = (int)(((long long)cta * dtotal) / G), d1 = (int)(((long long)(cta + 1) * dtotal) / G);
+            /* the run [d0, d1): its last row group continues in the next block when d1 is not a multiple of ns;
+             * those n_tail tasks run first.  Row groups owned here: those whose last slot lies in the run. */
+            const int n_tail = (d1 > d0 && d1 % ns != 0) ? min(d1 - d0, d1 % ns) : 0;
+            const int rg_first = d0 / ns;
+            const int n_own_rg = (d1 > d0) ? (d1 / ns - rg_first) : 0;
+            unsigned *cnt_rg = A.counters + FB_CNT_WIN + FB_MAX_SLOTS * 32;
+            auto dtask = [&](int j) { return j < n_tail ? d1 - n_tail + j : d0 + (j - n_tail); };
             const uint32_t dring_u = fb_smem_u32(ring) + warp * 2 * FB_Q6K_GROUP;
             auto dissue = [&](int t, int s) {
                 const int rg = t / ns, slot = t - rg * ns;
@@ -378,38 +388,44 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             };
             if (warp < SK_DOWN_WARPS && lane == 0)
                 for (int i = 0; i < 2; i++)
-                    if (d0 + warp + i * SK_DOWN_WARPS < d1) dissue(d0 + warp + i * SK_DOWN_WARPS, i);
+                    if (warp + i * SK_DOWN_WARPS < d1 - d0) dissue(dtask(warp + i * SK_DOWN_WARPS), i);
             alive = sk_wait(B, S);
             if (!alive) break;
             SK_STAMP(7);
 
             /* ---- P3: down + combine */
-            for (int wd = warp; wd < ns * dbpr; wd += SK_WARPS) { /* quantise the activations (src/cpu_expert.c:109-110) */
-                const float *src = A.act + (wd / dbpr) * A.inter_local + (wd % dbpr) * FB_QK + 8 * lane;
-                float v[8];
+            {   /* quantise the activations of every slot (src/cpu_expert.c:109-110): all loads first, then the math */
+                float v[3][8];
 #pragma unroll
-                for (int j = 0; j < 8; j++) v[j] = __ldcg(src + j);
-                fb_warp_quantize(v, &S->q8a[wd], lane);
+                for (int u = 0; u < 3; u++) {
+                    const int wd = warp + u * SK_WARPS;
+                    if (wd < ns * dbpr) {
+                        const float4 *src = reinterpret_cast<const float4 *>(A.act + (wd / dbpr) * A.inter_local + (wd % dbpr) * FB_QK + 8 * lane);
+                        const float4 p0 = __ldcg(src), p1 = __ldcg(src + 1);
+                        v[u][0] = p0.x; v[u][1] = p0.y; v[u][2] = p0.z; v[u][3] = p0.w;
+                        v[u][4] = p1.x; v[u][5] = p1.y; v[u][6] = p1.z; v[u][7] = p1.w;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 3; u++) {
+                    const int wd = warp + u * SK_WARPS;
+                    if (wd < ns * dbpr) fb_warp_quantize(v[u], &S->q8a[wd], lane);
+                }
             }
             __syncthreads();
-            const int rg_first = d0 < d1 ? d0 / ns : 0;
             if (warp < SK_DOWN_WARPS) {
                 int it = 0;
-                for (int t = d0 + warp; t < d1; t += SK_DOWN_WARPS, it++) {
+                for (int j = warp; j < d1 - d0; j += SK_DOWN_WARPS, it++) {
                     const int s = it & 1;
                     if (!fb_mbar_wait(full_u + 8 * s, full_uses[s] & 1)) {
                         alive = false;
                         break;
                     }
                     full_uses[s]++;
+                    const int t = dtask(j);
                     const int rg = t / ns, slot = t - rg * ns;
                     const uint32_t st = dring_u + s * FB_Q6K_GROUP + 16 * lane;
-                    uint4 a[FB_Q8_U4];
-                    {
-                        const uint4 *src = reinterpret_cast<const uint4 *>(&S->q8a[slot * dbpr + lane % dbpr]);
-#pragma unroll
-                        for (int i = 0; i < FB_Q8_U4; i++) a[i] = src[i];
-                    }
+                    const uint32_t a_u = fb_smem_u32(&S->q8a[slot * dbpr + lane % dbpr]);
                     float f;
                     if (A.down_type == FB_TYPE_Q4_K) {
                         const uint4 hd = fb_lds128(st);
@@ -417,8 +433,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
 #pragma unroll
                         for (int k = 0; k < 8; k++) q[k] = fb_lds128(st + 512 * (k + 1));
                         __syncwarp();
-                        if (lane == 0 && t + 2 * SK_DOWN_WARPS < d1) dissue(t + 2 * SK_DOWN_WARPS, s);
-                        f = fb_dot_q4k(hd, q, a);
+                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        f = fb_dot_q4k_sm(hd, q, a_u);
                     } else {
                         uint4 ql[8], qh[4];
 #pragma unroll
@@ -429,11 +445,20 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         uint32_t d16;
                         asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d16) : "r"(dring_u + s * FB_Q6K_GROUP + FB_Q6K_OFF_D + 2 * lane));
                         __syncwarp();
-                        if (lane == 0 && t + 2 * SK_DOWN_WARPS < d1) dissue(t + 2 * SK_DOWN_WARPS, s);
-                        f = fb_dot_q6k(ql, qh, sc, d16, a);
+                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        f = fb_dot_q6k_sm(ql, qh, sc, d16, a_u);
                     }
                     f = fb_span_sum(f, dbpr);
-                    if (lane % dbpr == 0) S->dots[rg - rg_first][slot][lane / dbpr] = f;
+                    if (j < n_tail) {
+                        /* a row group that continues in the next block: hand this slot's rows over through global
+                         * memory right away (the owner combines at the end of its own run) */
+                        const int r = rg * drpg + lane / dbpr;
+                        if (lane % dbpr == 0 && r < n) A.dots[slot * n + r] = f;
+                        __syncwarp();
+                        if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(cnt_rg + rg), "r"(1u) : "memory");
+                    } else if (lane % dbpr == 0) {
+                        S->dots[rg - rg_first][slot][lane / dbpr] = f;
+                    }
                 }
             }
             if (!__syncthreads_and(alive ? 1 : 0)) {
@@ -445,45 +470,41 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 break;
             }
             /* combine: partial += score * down in list order (src/cpu_expert.c:114-115), shared expert added after
-             * (src/inference.c:595).  A row group whose slots all ran in this block is combined from shared memory;
-             * one split between two blocks goes through global memory and is combined by whichever finishes last. */
-            if (d0 < d1) {
-                const int rg_last = (d1 - 1) / ns;
-                unsigned *cnt_rg = A.counters + FB_CNT_WIN + FB_MAX_SLOTS * 32;
-                for (int q = warp; q <= rg_last - rg_first; q += SK_WARPS) {
-                    const int rg = rg_first + q;
-                    const int s_lo = max(d0, rg * ns) - rg * ns, s_hi = min(d1, (rg + 1) * ns) - rg * ns;
-                    const int r = rg * drpg + lane;
-                    const bool row_ok = lane < drpg && r < n;
-                    if (s_lo == 0 && s_hi == ns) {
-                        if (row_ok) {
-                            float acc = 0.0f;
-                            for (int s = 0; s < A.top_k; s++) acc = __fmaf_rn(S->scores[s], S->dots[q][s][lane], acc);
-                            if (A.has_shared) acc = __fadd_rn(acc, S->dots[q][A.top_k][lane]);
-                            A.moe_out[r] = acc;
-                        }
-                    } else {
-                        if (row_ok)
-                            for (int s = s_lo; s < s_hi; s++) A.dots[s * n + r] = S->dots[q][s][lane];
-                        __syncwarp();
-                        int last = 0;
-                        if (lane == 0) {
-                            __threadfence();
-                            const unsigned old = atomicAdd(cnt_rg + rg, (unsigned)(s_hi - s_lo));
-                            last = (old + (unsigned)(s_hi - s_lo) == (unsigned)ns);
-                        }
-                        last = __shfl_sync(FULL, last, 0);
-                        if (last) {
-                            __threadfence();
-                            if (row_ok) {
-                                float acc = 0.0f;
-                                for (int s = 0; s < A.top_k; s++) acc = __fmaf_rn(S->scores[s], __ldcg(A.dots + s * n + r), acc);
-                                if (A.has_shared) acc = __fadd_rn(acc, __ldcg(A.dots + A.top_k * n + r));
-                                A.moe_out[r] = acc;
-                            }
-                            if (lane == 0) cnt_rg[rg] = 0;
-                        }
+             * (src/inference.c:595).  The block that ran a row group's LAST slot owns it; slots that ran in earlier
+             * blocks arrive through global memory (those blocks ran them first, so the wait is normally over). */
+            for (int q = warp; q < n_own_rg && alive; q += SK_WARPS) {
+                const int rg = rg_first + q;
+                const int s_lo = max(d0, rg * ns) - rg * ns; /* slots below s_lo ran elsewhere */
+                const int r = rg * drpg + lane;
+                const bool row_ok = lane < drpg && r < n;
+                if (s_lo > 0) {
+                    int ok = 1;
+                    if (lane == 0) {
+                        unsigned nspin = 0;
+                        unsigned seen;
+                        do {
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt_rg + rg) : "memory");
+                        } while (seen < (unsigned)s_lo && ++nspin < SK_SPIN_LIMIT);
+                        ok = seen >= (unsigned)s_lo;
+                        cnt_rg[rg] = 0;
                     }
+                    ok = __shfl_sync(FULL, ok, 0);
+                    if (!ok) {
+                        if (lane == 0) {
+                            atomicExch(B.abort_flag, 1);
+                            atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
+                        }
+                        break; /* the grid barrier that follows sees the abort flag */
+                    }
+                }
+                if (row_ok) {
+                    float acc = 0.0f;
+                    for (int s = 0; s < A.top_k; s++) {
+                        const float dv = (s < s_lo) ? __ldcg(A.dots + s * n + r) : S->dots[q][s][lane];
+                        acc = __fmaf_rn(S->scores[s], dv, acc);
+                    }
+                    if (A.has_shared) acc = __fadd_rn(acc, (A.top_k < s_lo) ? __ldcg(A.dots + A.top_k * n + r) : S->dots[q][A.top_k][lane]);
+                    A.moe_out[r] = acc;
                 }
             }
             SK_STAMP(8);
