@@ -99,6 +99,7 @@ _SIGS = {
     "fomoe_b200_trace_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64), C.c_int]),
     "fomoe_b200_peek": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_uint64]),
     "fomoe_b200_matvec": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p, _f32p]),
+    "fomoe_b200_matvec_noalloc": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "fomoe_b200_quantize_q8k": (C.c_int, [C.c_void_p, _f32p, C.c_int, C.c_void_p]),
     "fomoe_b200_synth_matrix": (None, [C.c_uint64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "fomoe_b200_synth_f32": (None, [C.c_uint64, C.c_int, C.c_int, C.c_float, C.c_float, C.c_uint64, _f32p]),

@@ -13,6 +13,7 @@
  */
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 
 #include "dots.cuh"
 #include "launch.h"
@@ -292,4 +293,76 @@ extern "C" int fb_launch_matvec(float *out, const uint8_t *shard, fb_shard_geom_
 extern "C" int fb_launch_quantize(fb_q8_entry_t *dst, const float *src, int n_blocks, void *stream) {
     k_quantize<<<(n_blocks * 32 + 255) / 256, 256, 0, (cudaStream_t)stream>>>(dst, src, n_blocks);
     return (int)cudaGetLastError();
+}
+
+/* ------------------------------------------------------------------ matvec without any allocation
+ *
+ * Some callers may not allocate device memory while they run: a serving loop whose memory pool was sized and
+ * handed out at start-up, code running under a framework that owns every byte of the GPU, or a latency-critical
+ * path where cudaMalloc's implicit device synchronisation is not acceptable.  fomoe_b200_matvec() allocates its
+ * two temporaries (the weight matrix regrouped into the lane-striped layout, and the Q8_K-quantised input) on
+ * every call; this variant keeps them in one fixed array that is part of the library image instead.
+ *
+ * The array lives in every GPU context that loads the library until the process exits (FB_NOALLOC_BYTES, 4 MiB
+ * plus the quantised input).  All calls on a device share it and it keeps the previous call's contents, so two
+ * calls whose kernels could overlap on the GPU (different streams, no ordering between them) race; calls on one
+ * stream are safe.  Nothing in it needs to start at zero: every byte that is read has been written by the same
+ * call's kernels (the regrouping kernel also writes the zero padding of the last group).
+ */
+#define FB_NOALLOC_SHARD_BYTES (4u << 20)                                  /* regrouped weights: up to 4 MiB */
+#define FB_NOALLOC_Q8_ENTRIES 32                                           /* cols <= 8192 */
+#define FB_NOALLOC_BYTES (FB_NOALLOC_SHARD_BYTES + FB_NOALLOC_Q8_ENTRIES * sizeof(fb_q8_entry_t))
+#define FB_NOALLOC_MAX_DEVICES 64
+
+static __device__ __align__(256) unsigned char fb_noalloc_scratch[FB_NOALLOC_BYTES];
+
+/* In host code the name above is only a stand-in for the symbol, not an address the GPU can use: the device
+ * address is looked up once per device, with that device current, and that pointer is what the kernels get. */
+static unsigned char *fb_noalloc_ptr[FB_NOALLOC_MAX_DEVICES];
+
+extern "C" int fomoe_b200_matvec_noalloc(int type, const void *w_ggml_dev, int rows, int cols, const float *x_dev,
+                                         float *y_dev, void *stream) {
+    if (!w_ggml_dev || !x_dev || !y_dev || rows < 1 || cols < FB_QK || cols % FB_QK) {
+        fprintf(stderr, "fomoe_b200_matvec_noalloc: bad arguments\n");
+        return -1;
+    }
+    const int bpr = cols / FB_QK;
+    if ((type != FB_TYPE_Q4_K && type != FB_TYPE_Q6_K) || (bpr & (bpr - 1)) || bpr > FB_NOALLOC_Q8_ENTRIES) {
+        fprintf(stderr, "fomoe_b200_matvec_noalloc: unsupported type %d or column count %d (a power-of-two number of "
+                        "256-column blocks, at most %d columns)\n", type, cols, FB_NOALLOC_Q8_ENTRIES * FB_QK);
+        return -1;
+    }
+    const uint64_t shard_bytes = fb_shard_bytes(type, (uint64_t)rows * bpr);
+    if (shard_bytes > FB_NOALLOC_SHARD_BYTES) {
+        fprintf(stderr, "fomoe_b200_matvec_noalloc: a %d x %d matrix needs %llu bytes of scratch, the fixed array holds "
+                        "%u; use fomoe_b200_matvec for larger matrices\n", rows, cols, (unsigned long long)shard_bytes,
+                FB_NOALLOC_SHARD_BYTES);
+        return -1;
+    }
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= FB_NOALLOC_MAX_DEVICES) {
+        fprintf(stderr, "fomoe_b200_matvec_noalloc: no current CUDA device\n");
+        return -1;
+    }
+    if (!fb_noalloc_ptr[dev]) { /* first call on this device: not capturable, do it before any stream capture */
+        void *p = NULL;
+        const cudaError_t e = cudaGetSymbolAddress(&p, fb_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            fprintf(stderr, "fomoe_b200_matvec_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+            return -1;
+        }
+        fb_noalloc_ptr[dev] = (unsigned char *)p;
+    }
+    unsigned char *shard = fb_noalloc_ptr[dev];
+    fb_q8_entry_t *q8 = reinterpret_cast<fb_q8_entry_t *>(fb_noalloc_ptr[dev] + FB_NOALLOC_SHARD_BYTES);
+    const fb_shard_geom_t g = {type, rows, bpr, 0, 0, bpr};
+    const int n_groups = (int)fb_n_groups((uint64_t)rows * bpr);
+    int rc = fb_launch_repack(shard, (const uint8_t *)w_ggml_dev, g, stream);
+    if (!rc) rc = fb_launch_quantize(q8, x_dev, bpr, stream);
+    if (!rc) rc = fb_launch_matvec(y_dev, shard, g, q8, grid_for(n_groups, 8), stream);
+    if (rc) {
+        fprintf(stderr, "fomoe_b200_matvec_noalloc: launch failed: %s\n", cudaGetErrorString((cudaError_t)rc));
+        return -1;
+    }
+    return 0;
 }

@@ -191,6 +191,18 @@ int fomoe_b200_peek(fomoe_b200_ctx_t *ctx, int what, void *out, uint64_t bytes);
 /* Microbenchmark / parity helpers: y[rows] = W[rows x cols] . Q8_K(x), W given in ggml order. */
 int fomoe_b200_matvec(fomoe_b200_ctx_t *ctx, int type, const void *w_ggml, int rows, int cols, const float *x,
                       float *y);
+/* y[rows] = W[rows x cols] . Q8_K(x) with NO allocation of any kind.  (No counterpart in the reference: added for
+ * callers that cannot call cudaMalloc while they run, such as a serving loop whose device memory was all handed out
+ * at start-up or a latency-critical path that must not take cudaMalloc's device synchronisation.)
+ * w_ggml_dev (ggml-ordered blocks, type Q4_K or Q6_K), x_dev and y_dev are DEVICE pointers supplied by the caller;
+ * the kernels are enqueued on `stream` (a cudaStream_t, NULL = default stream) of the current device and the call
+ * does not synchronise.  The two temporaries fomoe_b200_matvec allocates per call live in a fixed array inside the
+ * library instead, which limits the matrix to 4 MiB of quantised weights (e.g. 1024 x 4096 Q4_K, 4096 x 1024 Q6_K)
+ * and 8192 columns; larger requests return -1 with a message.  Every call on a device shares that array: calls
+ * that may overlap on the GPU race, calls on one stream do not.  The first call on a device looks the array's
+ * address up; make that call before starting any stream capture.  Returns 0 or -1. */
+int fomoe_b200_matvec_noalloc(int type, const void *w_ggml_dev, int rows, int cols, const float *x_dev, float *y_dev,
+                              void *stream);
 int fomoe_b200_quantize_q8k(fomoe_b200_ctx_t *ctx, const float *x, int n, void *q8k_out /* n/256 * 292 B, reference block_q8_K */);
 
 /* Host-side synthetic generator (same bytes as fomoe_b200_table_generate puts on the device). */
