@@ -95,6 +95,8 @@ _SIGS = {
     "fomoe_b200_kernel_launches": (C.c_uint64, [C.c_void_p]),
     "fomoe_b200_set_graphs": (C.c_int, [C.c_void_p, C.c_int]),
     "fomoe_b200_set_variant": (C.c_int, [C.c_void_p, C.c_int]),
+    "fomoe_b200_tp_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "fomoe_b200_tp_connect": (C.c_int, [C.c_void_p, C.c_void_p]),
     "fomoe_b200_trace_enable": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
     "fomoe_b200_trace_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64), C.c_int]),
     "fomoe_b200_peek": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_uint64]),
@@ -331,6 +333,18 @@ class MoeDecoder:
     def n_blocks(self):
         import torch
         return torch.cuda.get_device_properties(0).multi_processor_count
+
+    def tp_export(self):
+        """64-byte handle of this rank's receive buffer (bytes)."""
+        buf = C.create_string_buffer(64)
+        self._ck(self._l.fomoe_b200_tp_export(self._h, buf), "tp_export")
+        return buf.raw
+
+    def tp_connect(self, handles):
+        """handles: list of tp_size 64-byte handles in rank order."""
+        blob = b"".join(handles)
+        assert len(blob) == 64 * self.tp_size
+        self._ck(self._l.fomoe_b200_tp_connect(self._h, blob), "tp_connect")
 
     def set_variant(self, variant):
         """2: persistent stack kernel for whole tokens (default); 0 / 1: per-phase kernels (plain / ring)."""

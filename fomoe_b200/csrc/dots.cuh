@@ -20,6 +20,35 @@
 
 __device__ __forceinline__ int fb_dp4a(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
 
+/* unsigned bytes of a times signed bytes of b */
+__device__ __forceinline__ int fb_dp4a_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+/* c + a.lo16 * b.byte0 + a.hi16 * b.byte1 (lo) / b.byte2, b.byte3 (hi); a signed halves */
+__device__ __forceinline__ int fb_dp2a_lo_su(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int fb_dp2a_hi_su(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int fb_dp2a_lo_ss(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.lo.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int fb_dp2a_hi_ss(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.hi.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t fb_u4c(const uint4 &v, int i) {
     return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
 }
@@ -134,7 +163,7 @@ __device__ __forceinline__ float fb_dot_q4k_sm(const uint4 &hdr, const uint4 (&q
     int isum = 0;
 #pragma unroll
     for (int c = 0; c < 4; c++) {
-        int lo = 0, hi = 0;
+        int lo = 0, hi16 = 0; /* hi16 = 16 * sum(high nibble * q8): the nibbles are used where they stand */
 #pragma unroll
         for (int kk = 0; kk < 2; kk++) {
             const uint4 w = qs[2 * c + kk];
@@ -144,23 +173,30 @@ __device__ __forceinline__ float fb_dot_q4k_sm(const uint4 &hdr, const uint4 (&q
             lo = fb_dp4a(w.y & 0x0f0f0f0fu, al.y, lo);
             lo = fb_dp4a(w.z & 0x0f0f0f0fu, al.z, lo);
             lo = fb_dp4a(w.w & 0x0f0f0f0fu, al.w, lo);
-            hi = fb_dp4a((w.x >> 4) & 0x0f0f0f0fu, ah.x, hi);
-            hi = fb_dp4a((w.y >> 4) & 0x0f0f0f0fu, ah.y, hi);
-            hi = fb_dp4a((w.z >> 4) & 0x0f0f0f0fu, ah.z, hi);
-            hi = fb_dp4a((w.w >> 4) & 0x0f0f0f0fu, ah.w, hi);
+            hi16 = fb_dp4a_us(w.x & 0xf0f0f0f0u, ah.x, hi16);
+            hi16 = fb_dp4a_us(w.y & 0xf0f0f0f0u, ah.y, hi16);
+            hi16 = fb_dp4a_us(w.z & 0xf0f0f0f0u, ah.z, hi16);
+            hi16 = fb_dp4a_us(w.w & 0xf0f0f0f0u, ah.w, hi16);
         }
         const uint32_t scw = (c < 2) ? sc_lo : sc_hi;
         const int s0 = (scw >> (16 * (c & 1))) & 0xff, s1 = (scw >> (16 * (c & 1) + 8)) & 0xff;
-        isum += s0 * lo + s1 * hi;
+        isum += s0 * lo + s1 * (hi16 >> 4); /* exact: hi16 is a multiple of 16 */
     }
+    /* mins: sum_j m_j * (bsums[2j] + bsums[2j+1]) with two-way dot products: the int16 pair as it lies in the
+     * entry times the byte m_j placed twice */
     const uint4 b0 = fb_lds128_a(a_u + 256), b1 = fb_lds128_a(a_u + 272);
     int msum = 0;
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const uint32_t pr = fb_u4c(j < 4 ? b0 : b1, j & 3);
-        const int bs = (int)(short)(pr & 0xffff) + (int)(short)(pr >> 16);
-        const uint32_t mw = (j < 4) ? m_lo : m_hi;
-        msum += (int)((mw >> (8 * (j & 3))) & 0xff) * bs;
+    {
+        const uint32_t d01 = __byte_perm(m_lo, 0, 0x1100), d23 = __byte_perm(m_lo, 0, 0x3322);
+        const uint32_t d45 = __byte_perm(m_hi, 0, 0x1100), d67 = __byte_perm(m_hi, 0, 0x3322);
+        msum = fb_dp2a_lo_su(b0.x, d01, msum);
+        msum = fb_dp2a_hi_su(b0.y, d01, msum);
+        msum = fb_dp2a_lo_su(b0.z, d23, msum);
+        msum = fb_dp2a_hi_su(b0.w, d23, msum);
+        msum = fb_dp2a_lo_su(b1.x, d45, msum);
+        msum = fb_dp2a_hi_su(b1.y, d45, msum);
+        msum = fb_dp2a_lo_su(b1.z, d67, msum);
+        msum = fb_dp2a_hi_su(b1.w, d67, msum);
     }
     float yd;
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(yd) : "r"(a_u + 288));
@@ -172,7 +208,6 @@ __device__ __forceinline__ float fb_dot_q4k_sm(const uint4 &hdr, const uint4 (&q
 __device__ __forceinline__ float fb_dot_q6k_sm(const uint4 (&ql)[8], const uint4 (&qh)[4], const uint4 &sc,
                                                uint32_t d16, uint32_t a_u) {
     int total = 0;
-    const uint4 b0 = fb_lds128_a(a_u + 256), b1 = fb_lds128_a(a_u + 272);
 #pragma unroll
     for (int h = 0; h < 2; h++) {
 #pragma unroll
@@ -193,17 +228,28 @@ __device__ __forceinline__ float fb_dot_q6k_sm(const uint4 (&ql)[8], const uint4
                 d2 = fb_dp4a(v2, fb_u4c(a2, i), d2);
                 d3 = fb_dp4a(v3, fb_u4c(a3, i), d3);
             }
+            /* groups g = 8h + 2i + tq */
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int g = 8 * h + 2 * i + tq;
-                const uint32_t pr = fb_u4c(g < 8 ? b0 : b1, (g & 7) >> 1);
-                const int bs = (g & 1) ? (int)(short)(pr >> 16) : (int)(short)(pr & 0xffff);
                 const int scv = (int)(signed char)((fb_u4c(sc, g >> 2) >> (8 * (g & 3))) & 0xff);
                 const int dv = i == 0 ? d0 : i == 1 ? d1 : i == 2 ? d2 : d3;
-                total += scv * (dv - 32 * bs);
+                total += scv * dv;
             }
         }
     }
+    /* q6 = v - 32: subtract 32 * sum_g sc_g * bsum_g, two groups per instruction (int16 pair times int8 pair) */
+    const uint4 b0 = fb_lds128_a(a_u + 256), b1 = fb_lds128_a(a_u + 272);
+    int corr = 0;
+    corr = fb_dp2a_lo_ss(b0.x, sc.x, corr);
+    corr = fb_dp2a_hi_ss(b0.y, sc.x, corr);
+    corr = fb_dp2a_lo_ss(b0.z, sc.y, corr);
+    corr = fb_dp2a_hi_ss(b0.w, sc.y, corr);
+    corr = fb_dp2a_lo_ss(b1.x, sc.z, corr);
+    corr = fb_dp2a_hi_ss(b1.y, sc.z, corr);
+    corr = fb_dp2a_lo_ss(b1.z, sc.w, corr);
+    corr = fb_dp2a_hi_ss(b1.w, sc.w, corr);
+    total -= 32 * corr;
     float yd;
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(yd) : "r"(a_u + 288));
     const float d = __fmul_rn(yd, fb_half_bits_to_float(d16));

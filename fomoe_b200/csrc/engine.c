@@ -69,8 +69,13 @@ struct fomoe_b200_ctx {
                     Environment override: FOMOE_B200_VARIANT */
     fb_args_t *d_layer_args; /* device copy of every layer's arguments for the stack kernel */
     int layer_args_valid;
-    unsigned long long *d_bar, *d_trace;
-    unsigned long long bar_count; /* arrivals every finished launch has added to *d_bar */
+    unsigned long long *d_trace, *d_ll_dots;
+    /* tensor parallelism: this rank's receive buffer and every rank's buffer as mapped here */
+    unsigned long long *tp_recv, *tp_peer[FB_MAX_TP];
+    int tp_connected;
+    unsigned long long *d_bar;     /* grid barrier words */
+    unsigned long long bar_count;  /* arrivals all finished stack launches have added */
+    unsigned gen_count;            /* layer-tokens of all finished stack launches */
     int trace_cap, trace_cta;
     int *d_abort;
     char err[256];
@@ -162,7 +167,10 @@ void fomoe_b200_destroy(fomoe_b200_ctx_t *c) {
     cudaFree(c->scores); cudaFree(c->act); cudaFree(c->dots); cudaFree(c->ids); cudaFree(c->ids_orig);
     cudaFree(c->status); cudaFree((void *)c->slot_rec); cudaFree(c->q8h); cudaFree(c->q8a);
     cudaFree(c->counters); cudaFree(c->tok_ctr); cudaFree(c->freq); cudaFree(c->tok_in); cudaFree(c->tok_out);
-    cudaFree(c->d_trace); cudaFree(c->stage); cudaFree(c->d_layer_args); cudaFree(c->d_bar); cudaFree(c->d_abort);
+    for (int p = 0; p < FB_MAX_TP; p++)
+        if (c->tp_peer[p] && c->tp_peer[p] != c->tp_recv) cudaIpcCloseMemHandle(c->tp_peer[p]);
+    cudaFree(c->tp_recv);
+    cudaFree(c->d_trace); cudaFree(c->stage); cudaFree(c->d_layer_args); cudaFree(c->d_bar); cudaFree(c->d_ll_dots); cudaFree(c->d_abort);
     if (c->pin) cudaFreeHost(c->pin);
     for (int i = 0; i < c->pev_cap; i++) cudaEventDestroy(c->pev[i]);
     free(c->pev);
@@ -275,10 +283,16 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
         dev_alloc(c, (void **)&c->counters, sizeof(unsigned) * (FB_CNT_WIN + FB_MAX_SLOTS * 32 + c->down_groups)) ||
         dev_alloc(c, (void **)&c->status, sizeof(int)) || dev_alloc(c, (void **)&c->tok_ctr, sizeof(unsigned)) ||
         dev_alloc(c, (void **)&c->d_layer_args, sizeof(fb_args_t) * (uint64_t)nl) ||
-        dev_alloc(c, (void **)&c->d_bar, 32 * sizeof(unsigned long long)) || dev_alloc(c, (void **)&c->d_abort, sizeof(int)) ||
+        dev_alloc(c, (void **)&c->d_bar, 32 * sizeof(unsigned long long)) ||
+        dev_alloc(c, (void **)&c->d_ll_dots, sizeof(unsigned long long) * FB_MAX_SLOTS * (uint64_t)ne) || dev_alloc(c, (void **)&c->d_abort, sizeof(int)) ||
         dev_alloc(c, (void **)&c->tok_in, sizeof(float) * (uint64_t)(c->max_tokens + 1) * ne) ||
         dev_alloc(c, (void **)&c->tok_out, sizeof(float) * (uint64_t)(c->max_tokens + 1) * ne))
         goto fail;
+    if (N > 1) { /* [tp_size][n_embd] words; plain cudaMalloc so that it can be shared with the other ranks */
+        if (N > FB_MAX_TP || cudaMalloc((void **)&c->tp_recv, sizeof(unsigned long long) * (size_t)N * ne) != cudaSuccess ||
+            cudaMemset(c->tp_recv, 0, sizeof(unsigned long long) * (size_t)N * ne) != cudaSuccess)
+            goto fail;
+    }
     c->stage_bytes = max_rec_ggml > sizeof(float) * (uint64_t)ne * 1024 ? max_rec_ggml : sizeof(float) * (uint64_t)ne * 1024;
     if (cudaMalloc((void **)&c->stage, c->stage_bytes) != cudaSuccess) goto fail;
     if (cudaHostAlloc((void **)&c->pin, sizeof(float) * (4 * (size_t)ne + 4 * FB_MAX_EXPERTS), cudaHostAllocDefault) !=
@@ -299,10 +313,11 @@ int fomoe_b200_status(fomoe_b200_ctx_t *c) {
     cudaSetDevice(c->cfg.device);
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1;
     if (cudaMemcpy(&st, c->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (st == FB_ST_WAIT_TIMEOUT) { /* a stack launch gave up: its barrier count is unknown, start over */
+    if (st == FB_ST_WAIT_TIMEOUT) { /* a stack launch gave up half way: its flags are in an unknown state, start over */
         cudaMemset(c->d_bar, 0, 32 * sizeof(unsigned long long));
-        cudaMemset(c->counters, 0, sizeof(unsigned) * (FB_CNT_WIN + FB_MAX_SLOTS * 32 + c->down_groups));
+        cudaMemset(c->d_ll_dots, 0, sizeof(unsigned long long) * FB_MAX_SLOTS * (size_t)c->cfg.n_embd);
         c->bar_count = 0;
+        c->gen_count = 0;
     }
     return st;
 }
@@ -351,6 +366,37 @@ int fomoe_b200_trace_read(fomoe_b200_ctx_t *c, unsigned long long *out, int n) {
     CK(c, cudaSetDevice(c->cfg.device));
     CK(c, cudaStreamSynchronize(c->stream));
     CK(c, cudaMemcpy(out, c->d_trace, sizeof(unsigned long long) * (size_t)n, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+/* ---- tensor parallelism: one process per GPU; the ranks exchange the handle of their receive buffer (through
+ * whatever channel the caller has, e.g. torch.distributed) and map each other's buffers.  The reference's
+ * counterpart is tp_init / tp_allreduce_sum (include/tp.h:30-79), a host-staged copy between two GPUs of one
+ * process; here the sum is fused into the stack kernel and travels as peer stores over NVLink. */
+int fomoe_b200_tp_export(fomoe_b200_ctx_t *c, void *handle64) {
+    if (!c || !handle64 || !c->tp_recv) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    cudaIpcMemHandle_t h;
+    CK(c, cudaIpcGetMemHandle(&h, c->tp_recv));
+    memcpy(handle64, &h, sizeof(h));
+    return 0;
+}
+
+int fomoe_b200_tp_connect(fomoe_b200_ctx_t *c, const void *handles) {
+    if (!c || !handles || !c->tp_recv) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    for (int p = 0; p < c->cfg.tp_size; p++) {
+        if (p == c->cfg.tp_rank) {
+            c->tp_peer[p] = c->tp_recv;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char *)handles + (size_t)p * sizeof(h), sizeof(h));
+        void *ptr = NULL;
+        CK(c, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        c->tp_peer[p] = (unsigned long long *)ptr;
+    }
+    c->tp_connected = 1;
     return 0;
 }
 
@@ -602,6 +648,7 @@ static int enqueue_stack(fomoe_b200_ctx_t *c, int l0, int l1, int load_store) {
 static int stack_kernel_usable(fomoe_b200_ctx_t *c) {
     fb_args_t a;
     if (c->variant != 2) return 0;
+    if (c->cfg.tp_size > 1 && !c->tp_connected) return 0;
     fill_args(c, 0, &a);
     return fb_stack_supported(&a, c->n_sm);
 }
@@ -629,15 +676,22 @@ static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int count) {
     k.tok_ctr = c->tok_ctr;
     k.bar = c->d_bar;
     k.bar_base = c->bar_count;
+    k.ll_dots = c->d_ll_dots;
+    k.gen_base = c->gen_count;
     k.abort_flag = c->d_abort;
     k.status = c->status;
+    k.tp_rank = c->cfg.tp_rank;
+    k.tp_size = c->cfg.tp_size;
+    k.tp_recv = c->tp_recv;
+    for (int p = 0; p < FB_MAX_TP; p++) k.tp_peer[p] = c->tp_peer[p];
     k.trace = c->d_trace;
     k.trace_cap = c->d_trace ? c->trace_cap : 0;
     k.trace_cta = c->trace_cta;
     CK(c, cudaMemsetAsync(c->d_abort, 0, sizeof(int), c->stream));
     CKL(c, fb_launch_stack(&k, c->n_sm, c->stream));
-    /* three grid barriers per layer per token, every block arrives once at each */
-    c->bar_count += 3ull * (unsigned long long)(l1 - l0) * (unsigned long long)count * (unsigned long long)c->n_sm;
+    /* three grid barriers per layer-token, every block arrives once at each */
+    c->bar_count += 3ull * (unsigned long long)((l1 - l0) * count) * (unsigned long long)c->n_sm;
+    c->gen_count += (unsigned)((l1 - l0) * count);
     return 0;
 }
 
@@ -720,8 +774,8 @@ int fomoe_b200_moe_layer_routed(fomoe_b200_ctx_t *c, int layer, const float *h, 
 
 int fomoe_b200_stack_run(fomoe_b200_ctx_t *c, const float *x_in, int l0, int l1, float *x_out) {
     if (!c || !x_in || !x_out || l0 < 0 || l1 > c->cfg.n_layers || l0 >= l1) return -1;
-    if (c->cfg.tp_size > 1) {
-        set_err(c, "stack_run on a tensor-parallel rank needs the all-reduce hook; use the per-layer calls");
+    if (c->cfg.tp_size > 1 && !stack_kernel_usable(c)) {
+        set_err(c, "stack_run on a tensor-parallel rank needs fomoe_b200_tp_connect first");
         return -1;
     }
     CK(c, cudaSetDevice(c->cfg.device));
@@ -789,8 +843,8 @@ static int build_graph(fomoe_b200_ctx_t *c) {
 
 int fomoe_b200_tokens_run(fomoe_b200_ctx_t *c, int first, int count, float *elapsed_ms) {
     if (!c || first < 0 || count < 1 || first + count > c->max_tokens) return -1;
-    if (c->cfg.tp_size > 1) {
-        set_err(c, "tokens_run on a tensor-parallel rank needs the all-reduce hook");
+    if (c->cfg.tp_size > 1 && !stack_kernel_usable(c)) {
+        set_err(c, "tokens_run on a tensor-parallel rank needs fomoe_b200_tp_connect first");
         return -1;
     }
     CK(c, cudaSetDevice(c->cfg.device));
@@ -878,8 +932,8 @@ int fomoe_b200_tokens_profile(fomoe_b200_ctx_t *c, int first, int count, float *
 
 int fomoe_b200_decode_token(fomoe_b200_ctx_t *c, const float *x_in, float *x_out) {
     if (!c || !x_in || !x_out) return -1;
-    if (c->cfg.tp_size > 1) {
-        set_err(c, "decode_token on a tensor-parallel rank needs the all-reduce hook");
+    if (c->cfg.tp_size > 1 && !stack_kernel_usable(c)) {
+        set_err(c, "decode_token on a tensor-parallel rank needs fomoe_b200_tp_connect first");
         return -1;
     }
     CK(c, cudaSetDevice(c->cfg.device));

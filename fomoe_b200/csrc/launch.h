@@ -32,6 +32,8 @@ typedef struct {
 #define FB_ST_BAD_ID 1      /* router produced an expert id outside the table */
 #define FB_ST_WAIT_TIMEOUT 2 /* a bounded wait ran out */
 
+#define FB_MAX_TP 8 /* tensor-parallel ranks */
+
 /* Argument block passed by value to every hot-path kernel. */
 typedef struct {
     /* shapes */
@@ -103,10 +105,18 @@ typedef struct {
     const float *tok_in;
     float *tok_out;
     unsigned *tok_ctr;
-    unsigned long long *bar; /* grid barrier arrival counter */
-    unsigned long long bar_base; /* its value when this launch starts (the host keeps count) */
+    unsigned long long *bar; /* grid barrier: [0] arrival counter, [16] generation of the last completed barrier */
+    unsigned long long bar_base; /* arrivals before this launch (the host keeps count) */
+    unsigned long long *ll_dots; /* [FB_MAX_SLOTS][n_embd] {generation, value} words: row groups split between blocks */
+    unsigned gen_base;       /* layer-tokens run by earlier launches */
     int *abort_flag;         /* raised by a block that gave up a wait; cleared by the host before a launch */
     int *status;
+    /* tensor parallelism: the combine step stores this rank's partial block output into slot tp_rank of every
+     * rank's receive buffer ([tp_size][n_embd] {generation, value} words); tp_peer[p] is rank p's buffer as mapped
+     * into this process (tp_peer[tp_rank] == tp_recv, this GPU's own) */
+    int tp_rank, tp_size;
+    unsigned long long *tp_recv;
+    unsigned long long *tp_peer[FB_MAX_TP];
     unsigned long long *trace; /* optional phase stamps of one block (profiling), or NULL */
     int trace_cap, trace_cta;
 } fb_stack_args_t;

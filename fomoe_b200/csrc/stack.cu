@@ -21,7 +21,7 @@
  *   --- grid barrier (moe_out), joined at the top of the next layer after its router rows
  *       have been requested ---
  *
- * Grid barriers are a monotonically increasing 64-bit arrival counter in global memory; every
+ * Grid barriers are an arrival counter plus a generation word in global memory; every
  * spin is bounded and, when a limit runs out, the block raises an abort flag that releases all
  * other blocks, records FB_ST_WAIT_TIMEOUT and returns.  The kernel needs all blocks co-resident:
  * it is launched cooperatively with one block per SM.
@@ -63,19 +63,13 @@ struct sk_smem_t {
 };
 
 struct sk_bar_t {
-    unsigned long long *ctr;
+    unsigned long long *ctr;  /* [0] arrivals, [16] generation of the last completed barrier */
     int *abort_flag;
     int *status;
     unsigned grid;
-    unsigned long long base; /* arrivals before this launch */
-    unsigned epoch;          /* barriers this block has arrived at */
+    unsigned long long base;  /* arrivals before this launch */
+    unsigned epoch;           /* barriers this block has arrived at in this launch */
 };
-
-__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
 
 __device__ __forceinline__ int ld_volatile_s32(const int *p) {
     int v;
@@ -83,10 +77,18 @@ __device__ __forceinline__ int ld_volatile_s32(const int *p) {
     return v;
 }
 
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
 /* Grid barrier.  Arrivals are counted on one cache line (an atomic that returns the count, so the last block
  * knows it is last); the last block then publishes the barrier's generation number on ANOTHER line, which is the
- * only one the waiting blocks poll.  Keeping the polls off the arrival line matters: 148 pollers on the line the
- * atomics land on made every barrier cost several microseconds.  Both words only ever grow; the host tells the
+ * only one the waiting blocks poll, one thread per block.  Measured alternatives were slower: a counter that all
+ * blocks poll (3-5 us per barrier), per-block flag words polled by a warp of every block (4-6 us), and exchanging
+ * the data itself as {generation, value} words polled by their consumers (5 us for the 512 logits): on this chip
+ * many pollers on few L2 lines delay the very stores they wait for.  Both words only ever grow; the host tells the
  * kernel where they stand when a launch starts. */
 __device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S) {
     __syncthreads();
@@ -122,6 +124,60 @@ __device__ __forceinline__ bool sk_wait(const sk_bar_t &B, sk_smem_t *S) {
     return S->ok != 0;
 }
 
+/* {generation, fp32 value} in one 8-byte word: data and flag cannot be seen apart, so a hand-over needs no fence */
+typedef unsigned long long sk_word_t;
+
+__device__ __forceinline__ void sk_put(sk_word_t *p, float v, uint32_t gen) {
+    const sk_word_t w = ((sk_word_t)gen << 32) | (sk_word_t)__float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+
+__device__ __forceinline__ sk_word_t sk_get1(const sk_word_t *p) {
+    sk_word_t a;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+    return a;
+}
+
+/* system scope: the word is written by, or meant for, another GPU; 16 bytes = two words in one load */
+__device__ __forceinline__ void sk_get2_sys(const sk_word_t *p, sk_word_t &a, sk_word_t &b) {
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+
+__device__ __forceinline__ void sk_put_sys(sk_word_t *p, float v, uint32_t gen) {
+    const sk_word_t w = ((sk_word_t)gen << 32) | (sk_word_t)__float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+
+/* Tensor-parallel output exchange, receiving side.  Every rank's combine step has stored its partial block output
+ * into slot `src` of EVERY rank's receive buffer ([tp_size][n_embd] words, in this GPU's own memory).  A thread
+ * polls its 8 elements of every slot until all carry `gen`, then adds the partials in rank order, so all ranks
+ * form bit-identical sums (the reference's tp_allreduce_sum, src/tp.hip:85-124, has the same meaning: out = p_0 +
+ * p_1 on both ranks).  false = gave up. */
+__device__ __forceinline__ bool sk_gather8(const sk_word_t *recv, int tp, int n, int e0, uint32_t gen, float (&v)[8],
+                                           const int *abort_flag) {
+#pragma unroll
+    for (int k = 0; k < 8; k++) v[k] = 0.0f;
+    for (int src = 0; src < tp; src++) {
+        const sk_word_t *p = recv + (size_t)src * n + e0;
+        bool got = false;
+        for (unsigned nsp = 0; nsp < SK_SPIN_LIMIT && !got; nsp++) {
+            sk_word_t w[8];
+#pragma unroll
+            for (int k = 0; k < 4; k++) sk_get2_sys(p + 2 * k, w[2 * k], w[2 * k + 1]);
+            got = true;
+#pragma unroll
+            for (int k = 0; k < 8; k++) got = got && ((uint32_t)(w[k] >> 32) == gen);
+            if (got) {
+#pragma unroll
+                for (int k = 0; k < 8; k++) v[k] = __fadd_rn(v[k], __uint_as_float((uint32_t)w[k]));
+            } else if ((nsp & 255u) == 255u && ld_volatile_s32(abort_flag))
+                break;
+        }
+        if (!got) return false;
+    }
+    return true;
+}
+
 __device__ __forceinline__ unsigned long long sk_now() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -137,6 +193,7 @@ __device__ __forceinline__ unsigned long long sk_now() {
                 ((unsigned long long)(idx) << 56) | (sk_now() & 0x00ffffffffffffffULL);      \
     } while (0)
 
+template <bool TP>
 __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
     extern __shared__ __align__(128) uint8_t dsm[];
     uint8_t *ring = dsm;
@@ -198,8 +255,22 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 w1 = __ldg(wp + 1);
             }
             SK_STAMP(0);
-            /* ---- join the barrier that publishes the previous layer's moe_out */
-            if (pending_join) {
+            /* ---- the previous layer's block output: one GPU joins the barrier that publishes moe_out; tensor-parallel
+             *      ranks gather the partial outputs of all ranks from their receive slots (that wait is the sync) */
+            const uint32_t gen = K.gen_base + (uint32_t)(tk * K.n_layers + l) + 1u; /* this layer-token's generation */
+            float mo[8];
+            if (TP) {
+                bool got = true;
+                if (l > 0 && own) got = sk_gather8(K.tp_recv, K.tp_size, n, e0, gen - 1u, mo, K.abort_flag);
+                if (!__syncthreads_and(got ? 1 : 0)) {
+                    if (tid == 0) {
+                        atomicExch(B.abort_flag, 1);
+                        atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
+                    }
+                    alive = false;
+                    break;
+                }
+            } else if (pending_join) {
                 alive = sk_wait(B, S);
                 pending_join = false;
                 if (!alive) break;
@@ -215,10 +286,14 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     v0 = p[0];
                     v1 = p[1];
                 } else {
-                    const float4 *m = reinterpret_cast<const float4 *>(A.moe_out + e0);
-                    const float4 m0 = __ldcg(m), m1 = __ldcg(m + 1);
-                    v0 = make_float4(__fadd_rn(x[0], m0.x), __fadd_rn(x[1], m0.y), __fadd_rn(x[2], m0.z), __fadd_rn(x[3], m0.w));
-                    v1 = make_float4(__fadd_rn(x[4], m1.x), __fadd_rn(x[5], m1.y), __fadd_rn(x[6], m1.z), __fadd_rn(x[7], m1.w));
+                    if (!TP) {
+                        const float4 *m = reinterpret_cast<const float4 *>(A.moe_out + e0);
+                        const float4 m0 = __ldcg(m), m1 = __ldcg(m + 1);
+                        mo[0] = m0.x; mo[1] = m0.y; mo[2] = m0.z; mo[3] = m0.w;
+                        mo[4] = m1.x; mo[5] = m1.y; mo[6] = m1.z; mo[7] = m1.w;
+                    }
+                    v0 = make_float4(__fadd_rn(x[0], mo[0]), __fadd_rn(x[1], mo[1]), __fadd_rn(x[2], mo[2]), __fadd_rn(x[3], mo[3]));
+                    v1 = make_float4(__fadd_rn(x[4], mo[4]), __fadd_rn(x[5], mo[5]), __fadd_rn(x[6], mo[6]), __fadd_rn(x[7], mo[7]));
                 }
                 x[0] = __fadd_rn(v0.x, r0.x); x[1] = __fadd_rn(v0.y, r0.y); x[2] = __fadd_rn(v0.z, r0.z); x[3] = __fadd_rn(v0.w, r0.w);
                 x[4] = __fadd_rn(v1.x, r1.x); x[5] = __fadd_rn(v1.y, r1.y); x[6] = __fadd_rn(v1.z, r1.z); x[7] = __fadd_rn(v1.w, r1.w);
@@ -378,7 +453,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             const int n_tail = (d1 > d0 && d1 % ns != 0) ? min(d1 - d0, d1 % ns) : 0;
             const int rg_first = d0 / ns;
             const int n_own_rg = (d1 > d0) ? (d1 / ns - rg_first) : 0;
-            unsigned *cnt_rg = A.counters + FB_CNT_WIN + FB_MAX_SLOTS * 32;
+            const uint32_t hand_gen = gen; /* tags this layer-token's hand-over words */
             auto dtask = [&](int j) { return j < n_tail ? d1 - n_tail + j : d0 + (j - n_tail); };
             const uint32_t dring_u = fb_smem_u32(ring) + warp * 2 * FB_Q6K_GROUP;
             auto dissue = [&](int t, int s) {
@@ -453,9 +528,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         /* a row group that continues in the next block: hand this slot's rows over through global
                          * memory right away (the owner combines at the end of its own run) */
                         const int r = rg * drpg + lane / dbpr;
-                        if (lane % dbpr == 0 && r < n) A.dots[slot * n + r] = f;
-                        __syncwarp();
-                        if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(cnt_rg + rg), "r"(1u) : "memory");
+                        if (lane % dbpr == 0 && r < n) sk_put(K.ll_dots + slot * n + r, f, hand_gen);
                     } else if (lane % dbpr == 0) {
                         S->dots[rg - rg_first][slot][lane / dbpr] = f;
                     }
@@ -477,19 +550,24 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 const int s_lo = max(d0, rg * ns) - rg * ns; /* slots below s_lo ran elsewhere */
                 const int r = rg * drpg + lane;
                 const bool row_ok = lane < drpg && r < n;
+                float pre[SK_DOWN_WARPS]; /* slots below s_lo: handed over by the previous block(s) */
                 if (s_lo > 0) {
-                    int ok = 1;
-                    if (lane == 0) {
-                        unsigned nspin = 0;
-                        unsigned seen;
-                        do {
-                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt_rg + rg) : "memory");
-                        } while (seen < (unsigned)s_lo && ++nspin < SK_SPIN_LIMIT);
-                        ok = seen >= (unsigned)s_lo;
-                        cnt_rg[rg] = 0;
+                    bool ok = true;
+                    if (row_ok) {
+                        for (int s = 0; s < s_lo; s++) {
+                            bool got = false;
+                            for (unsigned nsp = 0; nsp < SK_SPIN_LIMIT && !got; nsp++) {
+                                const sk_word_t w = sk_get1(K.ll_dots + s * n + r);
+                                if ((uint32_t)(w >> 32) == hand_gen) {
+                                    pre[s] = __uint_as_float((uint32_t)w);
+                                    got = true;
+                                } else if ((nsp & 255u) == 255u && ld_volatile_s32(K.abort_flag))
+                                    break;
+                            }
+                            ok = ok && got;
+                        }
                     }
-                    ok = __shfl_sync(FULL, ok, 0);
-                    if (!ok) {
+                    if (!__all_sync(FULL, ok)) {
                         if (lane == 0) {
                             atomicExch(B.abort_flag, 1);
                             atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
@@ -500,39 +578,64 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 if (row_ok) {
                     float acc = 0.0f;
                     for (int s = 0; s < A.top_k; s++) {
-                        const float dv = (s < s_lo) ? __ldcg(A.dots + s * n + r) : S->dots[q][s][lane];
+                        const float dv = (s < s_lo) ? pre[s] : S->dots[q][s][lane];
                         acc = __fmaf_rn(S->scores[s], dv, acc);
                     }
-                    if (A.has_shared) acc = __fadd_rn(acc, (A.top_k < s_lo) ? __ldcg(A.dots + A.top_k * n + r) : S->dots[q][A.top_k][lane]);
-                    A.moe_out[r] = acc;
+                    if (A.has_shared) acc = __fadd_rn(acc, (A.top_k < s_lo) ? pre[A.top_k] : S->dots[q][A.top_k][lane]);
+                    if (TP) {
+                        /* fused all-reduce, sending side: the partial goes straight into slot tp_rank of every
+                         * rank's receive buffer over NVLink (plain peer stores of {generation, value} words) */
+                        for (int p = 0; p < K.tp_size; p++) sk_put_sys(K.tp_peer[p] + (size_t)K.tp_rank * n + r, acc, gen);
+                    } else {
+                        A.moe_out[r] = acc;
+                    }
                 }
             }
             SK_STAMP(8);
-            sk_arrive(B, S);
-            pending_join = true;
+            if (!TP) {
+                sk_arrive(B, S);
+                pending_join = true;
+            }
         } /* layers */
         if (!alive) break;
-        /* ---- end of token: join the last barrier, x += moe_out, publish */
-        alive = sk_wait(B, S);
-        pending_join = false;
-        if (!alive) break;
-        if (leader) {
+        /* ---- end of token: the last layer's block output, x += moe_out, publish */
+        float mo[8];
+        {
             const fb_args_t &A = S->A;
             const int e0 = 8 * tid;
-            if (e0 < A.n_embd) {
-                const float4 *m = reinterpret_cast<const float4 *>(A.moe_out + e0);
-                const float4 m0 = __ldcg(m), m1 = __ldcg(m + 1);
+            if (TP) {
+                bool got = true;
+                if (leader && e0 < A.n_embd)
+                    got = sk_gather8(K.tp_recv, K.tp_size, A.n_embd, e0, K.gen_base + (uint32_t)((tk + 1) * K.n_layers), mo, K.abort_flag);
+                if (!__syncthreads_and(got ? 1 : 0)) {
+                    if (tid == 0) {
+                        atomicExch(B.abort_flag, 1);
+                        atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
+                    }
+                    alive = false;
+                    break;
+                }
+            } else {
+                alive = sk_wait(B, S);
+                pending_join = false;
+                if (!alive) break;
+                if (leader && e0 < A.n_embd) {
+                    const float4 *m = reinterpret_cast<const float4 *>(A.moe_out + e0);
+                    const float4 m0 = __ldcg(m), m1 = __ldcg(m + 1);
+                    mo[0] = m0.x; mo[1] = m0.y; mo[2] = m0.z; mo[3] = m0.w;
+                    mo[4] = m1.x; mo[5] = m1.y; mo[6] = m1.z; mo[7] = m1.w;
+                }
+            }
+            if (leader && e0 < A.n_embd) {
                 float4 *o = reinterpret_cast<float4 *>(K.tok_out + (size_t)tok * A.n_embd + e0);
-                o[0] = make_float4(__fadd_rn(x[0], m0.x), __fadd_rn(x[1], m0.y), __fadd_rn(x[2], m0.z), __fadd_rn(x[3], m0.w));
-                o[1] = make_float4(__fadd_rn(x[4], m1.x), __fadd_rn(x[5], m1.y), __fadd_rn(x[6], m1.z), __fadd_rn(x[7], m1.w));
+                o[0] = make_float4(__fadd_rn(x[0], mo[0]), __fadd_rn(x[1], mo[1]), __fadd_rn(x[2], mo[2]), __fadd_rn(x[3], mo[3]));
+                o[1] = make_float4(__fadd_rn(x[4], mo[4]), __fadd_rn(x[5], mo[5]), __fadd_rn(x[6], mo[6]), __fadd_rn(x[7], mo[7]));
                 float4 *xo = reinterpret_cast<float4 *>(A.x + e0);
                 xo[0] = o[0];
                 xo[1] = o[1];
             }
         }
         __syncthreads(); /* S->A is rewritten at the top of the next token */
-        /* the next token's P0 overwrites nothing another block still reads before its own first
-         * barrier, except moe_out, which is only rewritten after two more barriers */
     }
     if (leader && tid == 0 && alive) *K.tok_ctr = tok_first + (unsigned)K.tok_count;
 }
@@ -544,19 +647,20 @@ extern "C" int fb_stack_supported(const fb_args_t *a, int grid) {
     const int run = (dtotal + grid - 1) / grid;                       /* longest run of down tasks of one block */
     const int max_rg = (run + a->n_slots - 2) / a->n_slots + 2;       /* row groups such a run can touch */
     return a->n_embd <= 4096 && a->n_slots <= SK_DOWN_WARPS && a->n_slots * a->down_bpr <= SK_MAX_Q8A &&
-           a->n_embd / FB_QK <= 16 && a->tp_size == 1 && max_rg <= SK_MAX_RG;
+           a->n_embd / FB_QK <= 16 && a->tp_size <= FB_MAX_TP && a->inter_local % FB_QK == 0 && max_rg <= SK_MAX_RG;
 }
 
 extern "C" int fb_launch_stack(const fb_stack_args_t *k, int grid, void *stream) {
     static int configured = 0;
     const int sm = fb_stack_smem_bytes();
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_stack, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
+        cudaError_t e = cudaFuncSetAttribute(k_stack<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(k_stack<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
         if (e != cudaSuccess) return (int)e;
         configured = 1;
     }
     fb_stack_args_t kk = *k;
     void *params[] = {&kk};
-    return (int)cudaLaunchCooperativeKernel((const void *)k_stack, dim3(grid), dim3(SK_THREADS), params, (size_t)sm,
-                                            (cudaStream_t)stream);
+    const void *fn = kk.tp_size > 1 ? (const void *)k_stack<true> : (const void *)k_stack<false>;
+    return (int)cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(SK_THREADS), params, (size_t)sm, (cudaStream_t)stream);
 }

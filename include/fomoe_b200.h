@@ -167,6 +167,14 @@ int fomoe_b200_get_routing(fomoe_b200_ctx_t *ctx, int layer, int *ids, float *sc
 /* Counters since creation: CAR substitutions, kernels launched by this library. */
 uint64_t fomoe_b200_substitutions(fomoe_b200_ctx_t *ctx);
 uint64_t fomoe_b200_kernel_launches(fomoe_b200_ctx_t *ctx);
+/* Tensor parallelism over the expert intermediate dimension, one process per GPU (tp_rank / tp_size of the
+ * configuration).  Each rank exports a 64-byte handle of its receive buffer, the caller gathers the handles of all
+ * ranks (rank order) and gives them to every rank; after that stack_run / tokens_run / decode_token run on all ranks
+ * together, each call made by every rank with the same arguments, and return the full (summed) result on every
+ * rank.  Replaces the reference's host-staged tp_allreduce_sum (include/tp.h:53-79) by stores into the peers'
+ * memory from inside the kernel. */
+int fomoe_b200_tp_export(fomoe_b200_ctx_t *ctx, void *handle64);
+int fomoe_b200_tp_connect(fomoe_b200_ctx_t *ctx, const void *handles /* tp_size x 64 bytes */);
 /* Profiling aid for the persistent stack kernel: record up to `cap` %globaltimer stamps of block `cta` at its
  * phase boundaries during the following runs (cap 0 = off; cta < 0 = every block, `cap` stamps each, block-major);
  * trace_read copies the first n out.  Each word is
