@@ -689,8 +689,9 @@ static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int count) {
     k.trace_cta = c->trace_cta;
     CK(c, cudaMemsetAsync(c->d_abort, 0, sizeof(int), c->stream));
     CKL(c, fb_launch_stack(&k, c->n_sm, c->stream));
-    /* three grid barriers per layer-token, every block arrives once at each */
-    c->bar_count += 3ull * (unsigned long long)((l1 - l0) * count) * (unsigned long long)c->n_sm;
+    /* grid barriers per layer-token: logits, activations and (one GPU only; tensor-parallel ranks exchange the
+     * block output through their receive buffers instead) the block output; every block arrives once at each */
+    c->bar_count += (c->cfg.tp_size > 1 ? 2ull : 3ull) * (unsigned long long)((l1 - l0) * count) * (unsigned long long)c->n_sm;
     c->gen_count += (unsigned)((l1 - l0) * count);
     return 0;
 }
