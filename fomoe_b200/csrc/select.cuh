@@ -3,8 +3,8 @@
  *
  * Same result as route.cuh's single-warp routine, built for latency:
  *   1. every warp sorts its 32 (logit, expert) pairs with a shuffle bitonic network, best first;
- *   2. the 16 sorted heads are merged pairwise in a 4-level tree (bitonic merge of two 16-entry lists per
- *      warp) to the best 16 of the block;
+ *   2. the best 16 of each warp (256 candidates) are merged by rank: every candidate counts, by binary search in
+ *      the other 15 sorted lists, how many entries beat it; ranks 0..15 are the block's best 16;
  *   3. near-ties among the best k+1 are recomputed in the CPU's summation order (src/tensor.c:104-113) and the
  *      ranking repeated, so the selected ids match the CPU's top_k (src/tensor.c:226-252) index for index;
  *   4. softmax over all experts (src/tensor.c:186-200), renormalised top-k weights (src/inference.c:496-502);
@@ -54,12 +54,6 @@ __device__ __forceinline__ void fb_sort32(float &v, int &i, int lane) {
     }
 }
 
-/* lanes hold a bitonic sequence (best-first run, then worst-first run): sort it best first */
-__device__ __forceinline__ void fb_merge32(float &v, int &i, int lane) {
-#pragma unroll
-    for (int j = 16; j > 0; j >>= 1) fb_cmpx(v, i, j, (lane & j) == 0);
-}
-
 /* Must be called by all 512 threads of the block.  Outputs (shared memory): ids[n_slots], scores[n_slots],
  * ids_orig[top_k], slot_rec[n_slots], all_scores[n_experts].  `leader` updates the global counters. */
 __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const float *h_smem, float *all_scores, int *ids,
@@ -77,32 +71,40 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
             W->li[0][warp][lane] = id;
         }
         __syncthreads();
-        int src = 0;
-        for (int n = 8; n >= 1; n >>= 1) {
-            if (warp < n) {
-                const int L = 2 * warp + (lane >> 4), pos = lane < 16 ? lane : 31 - lane;
-                v = W->lv[src][L][pos];
-                id = W->li[src][L][pos];
-                fb_merge32(v, id, lane);
-                if (lane < 16) {
-                    W->lv[src ^ 1][warp][lane] = v;
-                    W->li[src ^ 1][warp][lane] = id;
-                }
+        /* merge by rank: candidate p of warp list w has p better entries in its own list; a 5-step binary search
+         * in each of the other 15 sorted lists counts the rest.  Ranks below 16 are the block's best 16, in order. */
+        if (tid < 256) {
+            const int w = tid >> 4, p = tid & 15;
+            const float mv = W->lv[0][w][p];
+            const int mi = W->li[0][w][p];
+            int rank = p;
+#pragma unroll
+            for (int o = 1; o < 16; o++) {
+                const int w2 = (w + o) & 15;
+                int pos = 0;
+#pragma unroll
+                for (int st = 8; st > 0; st >>= 1)
+                    if (fb_better(W->lv[0][w2][pos + st - 1], W->li[0][w2][pos + st - 1], mv, mi)) pos += st;
+                if (fb_better(W->lv[0][w2][pos], W->li[0][w2][pos], mv, mi)) pos++;
+                rank += pos;
             }
-            __syncthreads();
-            src ^= 1;
+            if (rank < 16) {
+                W->lv[1][0][rank] = mv;
+                W->li[1][0][rank] = mi;
+            }
         }
-        /* best 16 now in lv[0][0][*] (four levels: src is back to 0) */
+        __syncthreads();
+        /* best 16 now in lv[1][0][*] */
         if (pass == 1) break;
         uint32_t flag = 0;
         for (int r = 0; r + 1 < kk; r++) {
-            const float a = W->lv[0][0][r], b = W->lv[0][0][r + 1];
+            const float a = W->lv[1][0][r], b = W->lv[1][0][r + 1];
             if (a - b <= FB_TIE_TOL * fmaxf(1.0f, fabsf(a))) flag |= (1u << r) | (1u << (r + 1));
         }
         if (!flag) break;
         bool mine = false;
         for (int r = 0; r < kk; r++)
-            if (((flag >> r) & 1u) && W->li[0][0][r] == tid) mine = true;
+            if (((flag >> r) & 1u) && W->li[1][0][r] == tid) mine = true;
         if (mine) { /* this thread's expert is in a near tie: the CPU's order, sequential multiply-then-add */
             const float4 *w = reinterpret_cast<const float4 *>(A.router_w + (size_t)tid * A.n_embd);
             const float4 *hh = reinterpret_cast<const float4 *>(h_smem);
@@ -126,13 +128,13 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
     }
 
     /* softmax: the maximum is the best candidate's logit */
-    const float mx = W->lv[0][0][0];
+    const float mx = W->lv[1][0][0];
     float p = (tid < nE) ? expf(lg - mx) : 0.0f;
     float ps = p;
     for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(FULL, ps, o);
     if (lane == 0) W->psum[warp] = ps;
     if (tid < 16) {
-        W->ci[tid] = W->li[0][0][tid];
+        W->ci[tid] = W->li[1][0][tid];
     }
     __syncthreads();
     float sum = 0.0f;
