@@ -157,7 +157,7 @@ __device__ __forceinline__ bool sk_gather8(const sk_word_t *recv, int tp, int n,
                                            const int *abort_flag) {
 #pragma unroll
     for (int k = 0; k < 8; k++) v[k] = 0.0f;
-    for (int src = 0; src < tp; src++) {
+    for (int src = 0; src < tp; src++) { /* rank order: every rank forms the same sum */
         const sk_word_t *p = recv + (size_t)src * n + e0;
         bool got = false;
         for (unsigned nsp = 0; nsp < SK_SPIN_LIMIT && !got; nsp++) {
