@@ -207,7 +207,13 @@ __device__ __forceinline__ float fb_dot_q4k_sm(const uint4 &hdr, const uint4 (&q
 
 __device__ __forceinline__ float fb_dot_q6k_sm(const uint4 (&ql)[8], const uint4 (&qh)[4], const uint4 &sc,
                                                uint32_t d16, uint32_t a_u) {
-    int total = 0;
+    /* The 6-bit weight is never assembled: its low nibble and its two high bits are multiplied with the
+     * activations separately, each where it sits in its byte (masks only, no shifts), and the power of two that
+     * its position carries is applied to the 16-weight sums: v = lo + 16*hb, so with L = dot(field & mask) and
+     * H = dot(high-bit field & mask):   groups from low nibbles   d = L + {16, 4} * H          (totA, scale 1)
+     *                                   groups from high nibbles  16 d = L + {16, 4} * H       (totB, scale 16)
+     * All sums are exact integers; totB is a multiple of 16. */
+    int totA = 0, totB = 0;
 #pragma unroll
     for (int h = 0; h < 2; h++) {
 #pragma unroll
@@ -215,29 +221,29 @@ __device__ __forceinline__ float fb_dot_q6k_sm(const uint4 (&ql)[8], const uint4
             const uint4 A = ql[4 * h + tq], B = ql[4 * h + 2 + tq], H = qh[2 * h + tq];
             const uint4 a0 = fb_lds128_a(a_u + 16 * (8 * h + 0 + tq)), a1 = fb_lds128_a(a_u + 16 * (8 * h + 2 + tq));
             const uint4 a2 = fb_lds128_a(a_u + 16 * (8 * h + 4 + tq)), a3 = fb_lds128_a(a_u + 16 * (8 * h + 6 + tq));
-            int d0 = 0, d1 = 0, d2 = 0, d3 = 0;
+            int l0 = 0, l1 = 0, l2 = 0, l3 = 0, h0 = 0, h1 = 0, h2 = 0, h3 = 0;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const uint32_t qa = fb_u4c(A, i), qb = fb_u4c(B, i), hh = fb_u4c(H, i);
-                const uint32_t v0 = (qa & 0x0f0f0f0fu) | ((hh << 4) & 0x30303030u);
-                const uint32_t v1 = (qb & 0x0f0f0f0fu) | ((hh << 2) & 0x30303030u);
-                const uint32_t v2 = ((qa >> 4) & 0x0f0f0f0fu) | (hh & 0x30303030u);
-                const uint32_t v3 = ((qb >> 4) & 0x0f0f0f0fu) | ((hh >> 2) & 0x30303030u);
-                d0 = fb_dp4a(v0, fb_u4c(a0, i), d0);
-                d1 = fb_dp4a(v1, fb_u4c(a1, i), d1);
-                d2 = fb_dp4a(v2, fb_u4c(a2, i), d2);
-                d3 = fb_dp4a(v3, fb_u4c(a3, i), d3);
+                const uint32_t x0 = fb_u4c(a0, i), x1 = fb_u4c(a1, i), x2 = fb_u4c(a2, i), x3 = fb_u4c(a3, i);
+                l0 = fb_dp4a_us(qa & 0x0f0f0f0fu, x0, l0);
+                h0 = fb_dp4a_us(hh & 0x03030303u, x0, h0);
+                l1 = fb_dp4a_us(qb & 0x0f0f0f0fu, x1, l1);
+                h1 = fb_dp4a_us(hh & 0x0c0c0c0cu, x1, h1);
+                l2 = fb_dp4a_us(qa & 0xf0f0f0f0u, x2, l2);
+                h2 = fb_dp4a_us(hh & 0x30303030u, x2, h2);
+                l3 = fb_dp4a_us(qb & 0xf0f0f0f0u, x3, l3);
+                h3 = fb_dp4a_us(hh & 0xc0c0c0c0u, x3, h3);
             }
-            /* groups g = 8h + 2i + tq */
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int g = 8 * h + 2 * i + tq;
-                const int scv = (int)(signed char)((fb_u4c(sc, g >> 2) >> (8 * (g & 3))) & 0xff);
-                const int dv = i == 0 ? d0 : i == 1 ? d1 : i == 2 ? d2 : d3;
-                total += scv * dv;
-            }
+            /* groups g = 8h + 2i + tq, i = 0..3 */
+            const uint32_t scw0 = fb_u4c(sc, 2 * h), scw1 = fb_u4c(sc, 2 * h + 1);
+            const int s0 = (int)(signed char)((scw0 >> (8 * tq)) & 0xff), s1 = (int)(signed char)((scw0 >> (8 * (2 + tq))) & 0xff);
+            const int s2 = (int)(signed char)((scw1 >> (8 * tq)) & 0xff), s3 = (int)(signed char)((scw1 >> (8 * (2 + tq))) & 0xff);
+            totA += s0 * (l0 + 16 * h0) + s1 * (l1 + 4 * h1);
+            totB += s2 * (l2 + 16 * h2) + s3 * (l3 + 4 * h3);
         }
     }
+    int total = totA + (totB >> 4);
     /* q6 = v - 32: subtract 32 * sum_g sc_g * bsum_g, two groups per instruction (int16 pair times int8 pair) */
     const uint4 b0 = fb_lds128_a(a_u + 256), b1 = fb_lds128_a(a_u + 272);
     int corr = 0;

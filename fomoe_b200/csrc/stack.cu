@@ -38,8 +38,9 @@
 
 #define SK_THREADS 512
 #define SK_WARPS 16
-#define SK_DOWN_WARPS 12                              /* expert slots the down phase can serve */
-#define SK_RING_BYTES (SK_DOWN_WARPS * 2 * FB_Q6K_GROUP) /* 161,280 B: 12 x 2 x 6720 or 16 x 2 x 4608 */
+#define SK_DOWN_WARPS 13                              /* warps that run down tasks: 38 tasks per block at the 397B shape = 3 rounds */
+#define SK_DN_SLOTS 12                                /* expert slots the down phase can serve */
+#define SK_RING_BYTES (SK_DOWN_WARPS * 2 * FB_Q6K_GROUP) /* 174,720 B: 13 x 2 x 6720; gate/up uses 16 x 2 x 4608 of it */
 #define SK_MAX_Q8A 48                                 /* n_slots * down blocks per row */
 #define SK_MAX_RG 8                                   /* row groups one block's run of down tasks can touch */
 #define SK_SPIN_LIMIT (1u << 22)
@@ -49,10 +50,9 @@ struct sk_smem_t {
     fb_args_t A;                         /* this layer's arguments */
     fb_q8_entry_t q8h[16];               /* quantised hidden state */
     fb_q8_entry_t q8a[SK_MAX_Q8A];       /* quantised activations of every slot */
-    float dots[SK_MAX_RG][SK_DOWN_WARPS][32]; /* per-expert down outputs of this block's row groups */
+    float dots[SK_MAX_RG][SK_DN_SLOTS][32]; /* per-expert down outputs of this block's row groups */
     float red[4][SK_WARPS];
     float all_scores[FB_MAX_EXPERTS];
-    float h[4096];                       /* normalised hidden state (the near-tie arbiter re-sums rows from it) */
     fb_sel_smem_t sel;
     int ids[FB_MAX_SLOTS], ids_orig[FB_MAX_SLOTS];
     float scores[FB_MAX_SLOTS];
@@ -198,6 +198,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
     extern __shared__ __align__(128) uint8_t dsm[];
     uint8_t *ring = dsm;
     sk_smem_t *S = reinterpret_cast<sk_smem_t *>(dsm + SK_RING_BYTES);
+    /* the normalised hidden state in fp32 (the near-tie arbiter re-sums router rows from it) lives in the first
+     * 16 KB of the ring: it is written in P0 and last read in SEL, the ring is filled from P2 to the end of P3 */
+    float *h_sm = reinterpret_cast<float *>(ring);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cta = blockIdx.x, G = gridDim.x;
     const bool leader = (cta == 0);
@@ -318,9 +321,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             }
             if (warp < n / FB_QK) fb_warp_quantize(h, &S->q8h[warp], lane);
             if (own) {
-                float4 *hp = reinterpret_cast<float4 *>(S->h + e0);
+                float4 *hp = reinterpret_cast<float4 *>(h_sm + e0);
                 hp[0] = make_float4(h[0], h[1], h[2], h[3]);
                 hp[1] = make_float4(h[4], h[5], h[6], h[7]);
+                /* these bytes are later overwritten by bulk copies (async proxy); block barriers follow before then */
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 if (leader) { /* kept in global memory as well, for inspection from the host */
                     float4 *gp = reinterpret_cast<float4 *>(A.h + e0);
                     gp[0] = hp[0];
@@ -372,7 +377,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             SK_STAMP(4);
 
             /* ---- SEL: routing, redundantly in every block (results identical by construction) */
-            fb_block_select(A, &S->sel, S->h, S->all_scores, S->ids, S->ids_orig, S->scores, S->slot_rec, leader);
+            fb_block_select(A, &S->sel, h_sm, S->all_scores, S->ids, S->ids_orig, S->scores, S->slot_rec, leader);
             if (leader) {
                 if (tid < A.n_slots) {
                     A.ids[tid] = S->ids[tid];
@@ -550,7 +555,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 const int s_lo = max(d0, rg * ns) - rg * ns; /* slots below s_lo ran elsewhere */
                 const int r = rg * drpg + lane;
                 const bool row_ok = lane < drpg && r < n;
-                float pre[SK_DOWN_WARPS]; /* slots below s_lo: handed over by the previous block(s) */
+                float pre[SK_DN_SLOTS]; /* slots below s_lo: handed over by the previous block(s) */
                 if (s_lo > 0) {
                     bool ok = true;
                     if (row_ok) {
@@ -646,7 +651,7 @@ extern "C" int fb_stack_supported(const fb_args_t *a, int grid) {
     const int dtotal = a->down_groups * a->n_slots;
     const int run = (dtotal + grid - 1) / grid;                       /* longest run of down tasks of one block */
     const int max_rg = (run + a->n_slots - 2) / a->n_slots + 2;       /* row groups such a run can touch */
-    return a->n_embd <= 4096 && a->n_slots <= SK_DOWN_WARPS && a->n_slots * a->down_bpr <= SK_MAX_Q8A &&
+    return a->n_embd <= 4096 && a->n_slots <= SK_DN_SLOTS && a->n_slots * a->down_bpr <= SK_MAX_Q8A &&
            a->n_embd / FB_QK <= 16 && a->tp_size <= FB_MAX_TP && a->inter_local % FB_QK == 0 && max_rg <= SK_MAX_RG;
 }
 
