@@ -555,22 +555,36 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 const int s_lo = max(d0, rg * ns) - rg * ns; /* slots below s_lo ran elsewhere */
                 const int r = rg * drpg + lane;
                 const bool row_ok = lane < drpg && r < n;
-                float pre[SK_DN_SLOTS]; /* slots below s_lo: handed over by the previous block(s) */
                 if (s_lo > 0) {
+                    /* slots below s_lo were run by the previous block(s): the warp fetches their s_lo x drpg words
+                     * with all lanes, four requests per lane in flight, and parks the values beside its own */
+                    const int nw = s_lo * drpg, dsh = __ffs(drpg) - 1;
                     bool ok = true;
-                    if (row_ok) {
-                        for (int s = 0; s < s_lo; s++) {
-                            bool got = false;
-                            for (unsigned nsp = 0; nsp < SK_SPIN_LIMIT && !got; nsp++) {
-                                const sk_word_t w = sk_get1(K.ll_dots + s * n + r);
-                                if ((uint32_t)(w >> 32) == hand_gen) {
-                                    pre[s] = __uint_as_float((uint32_t)w);
-                                    got = true;
-                                } else if ((nsp & 255u) == 255u && ld_volatile_s32(K.abort_flag))
-                                    break;
-                            }
-                            ok = ok && got;
+                    for (int base = 0; base < nw && ok; base += 128) {
+                        unsigned need = 0;
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int idx = base + 32 * u + lane;
+                            if (idx < nw && rg * drpg + (idx & (drpg - 1)) < n) need |= 1u << u;
                         }
+                        for (unsigned nsp = 0; nsp < SK_SPIN_LIMIT && need; nsp++) {
+                            sk_word_t w[4];
+#pragma unroll
+                            for (int u = 0; u < 4; u++) {
+                                const int idx = base + 32 * u + lane;
+                                if ((need >> u) & 1u) w[u] = sk_get1(K.ll_dots + (idx >> dsh) * n + rg * drpg + (idx & (drpg - 1)));
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; u++) {
+                                const int idx = base + 32 * u + lane;
+                                if (((need >> u) & 1u) && (uint32_t)(w[u] >> 32) == hand_gen) {
+                                    S->dots[q][idx >> dsh][idx & (drpg - 1)] = __uint_as_float((uint32_t)w[u]);
+                                    need &= ~(1u << u);
+                                }
+                            }
+                            if (need && (nsp & 255u) == 255u && ld_volatile_s32(K.abort_flag)) break;
+                        }
+                        ok = need == 0u;
                     }
                     if (!__all_sync(FULL, ok)) {
                         if (lane == 0) {
@@ -579,14 +593,12 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         }
                         break; /* the grid barrier that follows sees the abort flag */
                     }
+                    __syncwarp();
                 }
                 if (row_ok) {
                     float acc = 0.0f;
-                    for (int s = 0; s < A.top_k; s++) {
-                        const float dv = (s < s_lo) ? pre[s] : S->dots[q][s][lane];
-                        acc = __fmaf_rn(S->scores[s], dv, acc);
-                    }
-                    if (A.has_shared) acc = __fadd_rn(acc, (A.top_k < s_lo) ? pre[A.top_k] : S->dots[q][A.top_k][lane]);
+                    for (int s = 0; s < A.top_k; s++) acc = __fmaf_rn(S->scores[s], S->dots[q][s][lane], acc);
+                    if (A.has_shared) acc = __fadd_rn(acc, S->dots[q][A.top_k][lane]);
                     if (TP) {
                         /* fused all-reduce, sending side: the partial goes straight into slot tp_rank of every
                          * rank's receive buffer over NVLink (plain peer stores of {generation, value} words) */
