@@ -269,7 +269,7 @@ __device__ __forceinline__ float fb_span_sum(float v, int span) {
 }
 
 /* One warp quantises 256 floats (lane holds src[8*lane .. 8*lane+7]) into one entry. */
-__device__ __forceinline__ void fb_warp_quantize(const float (&x)[8], fb_q8_entry_t *dst, int lane) {
+__device__ __forceinline__ void fb_warp_quantize(const float (&x)[8], fb_q8_entry_t *dst, int lane, bool store = true) {
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(x[i]));
@@ -293,6 +293,7 @@ __device__ __forceinline__ void fb_warp_quantize(const float (&x)[8], fb_q8_entr
         dout = __fdiv_rn(1.0f, iscale);
     }
     bs += __shfl_xor_sync(0xffffffffu, bs, 1); /* groups of 16 values = lane pairs */
+    if (!store) return; /* callers that run several windows side by side keep the arithmetic unconditional */
     reinterpret_cast<uint2 *>(dst->qs)[lane] = make_uint2(w0, w1);
     if ((lane & 1) == 0) dst->bsums[lane >> 1] = (int16_t)bs;
     if (lane == 0) {

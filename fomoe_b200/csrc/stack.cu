@@ -257,6 +257,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 w0 = __ldg(wp);
                 w1 = __ldg(wp + 1);
             }
+            if (A.has_shared && lane == 0) {
+                /* the shared expert runs in every layer: its gate and up shards (the first bytes HBM has to deliver
+                 * once the routing is known) are pulled into L2 now, while the chip waits on exchanges; 16 x 148
+                 * slices, one per warp */
+                const uint64_t tot = A.down_off; /* gate + up bytes of a record */
+                const uint64_t csz = ((tot + (uint64_t)G * SK_WARPS - 1) / ((uint64_t)G * SK_WARPS) + 15ull) & ~15ull;
+                const uint64_t off = ((uint64_t)cta * SK_WARPS + warp) * csz;
+                if (off < tot)
+                    fb_prefetch_l2(A.table_layer + (uint64_t)A.n_experts * A.rec_bytes + off, (uint32_t)min(csz, tot - off));
+            }
             SK_STAMP(0);
             /* ---- the previous layer's block output: one GPU joins the barrier that publishes moe_out; tensor-parallel
              *      ranks gather the partial outputs of all ranks from their receive slots (that wait is the sync) */
@@ -484,12 +494,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         const float4 p0 = __ldcg(src), p1 = __ldcg(src + 1);
                         v[u][0] = p0.x; v[u][1] = p0.y; v[u][2] = p0.z; v[u][3] = p0.w;
                         v[u][4] = p1.x; v[u][5] = p1.y; v[u][6] = p1.z; v[u][7] = p1.w;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) v[u][i] = 0.0f;
                     }
                 }
+                /* the three windows' shuffle chains are independent: run them unconditionally so they interleave */
 #pragma unroll
                 for (int u = 0; u < 3; u++) {
                     const int wd = warp + u * SK_WARPS;
-                    if (wd < ns * dbpr) fb_warp_quantize(v[u], &S->q8a[wd], lane);
+                    fb_warp_quantize(v[u], &S->q8a[min(wd, SK_MAX_Q8A - 1)], lane, wd < ns * dbpr);
                 }
             }
             __syncthreads();

@@ -65,6 +65,11 @@ __device__ __forceinline__ void fb_bulk_g2s(uint32_t dst, const void *src, uint3
                  : "memory");
 }
 
+/* Ask for `bytes` (a multiple of 16, source 16-byte aligned) to be brought into L2; nothing waits for it. */
+__device__ __forceinline__ void fb_prefetch_l2(const void *src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ uint4 fb_lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
