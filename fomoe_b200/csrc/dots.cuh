@@ -205,6 +205,64 @@ __device__ __forceinline__ float fb_dot_q4k_sm(const uint4 &hdr, const uint4 (&q
     return __fmaf_rn(d, (float)isum, -__fmul_rn(dmin, (float)msum));
 }
 
+/* Gate and up rows of one expert against the SAME activation entry: both weight groups stay in their ring stages
+ * (sg_u / su_u = this lane's 16-byte column of the stage: header at +0, quant piece k at +512*(k+1)) and every
+ * activation piece is read once for the two of them, which takes a third off the shared-memory reads of the
+ * gate/up phase.  Same integer arithmetic as fb_dot_q4k_sm. */
+__device__ __forceinline__ void fb_dot2_q4k_sm(uint32_t sg_u, uint32_t su_u, uint32_t a_u, float &fg, float &fu) {
+    const uint4 hg = fb_lds128_a(sg_u), hu = fb_lds128_a(su_u);
+    const uint32_t g_sc_lo = hg.y & 0x3f3f3f3fu, g_sc_hi = (hg.w & 0x0f0f0f0fu) | (((hg.y >> 6) & 0x03030303u) << 4);
+    const uint32_t u_sc_lo = hu.y & 0x3f3f3f3fu, u_sc_hi = (hu.w & 0x0f0f0f0fu) | (((hu.y >> 6) & 0x03030303u) << 4);
+    int isg = 0, isu = 0;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        int lg = 0, hg16 = 0, lu = 0, hu16 = 0;
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            const uint4 wg = fb_lds128_a(sg_u + 512 * (2 * c + kk + 1));
+            const uint4 wu = fb_lds128_a(su_u + 512 * (2 * c + kk + 1));
+            const uint4 al = fb_lds128_a(a_u + 16 * (4 * c + kk));
+            const uint4 ah = fb_lds128_a(a_u + 16 * (4 * c + 2 + kk));
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t g = fb_u4c(wg, i), u = fb_u4c(wu, i), xl = fb_u4c(al, i), xh = fb_u4c(ah, i);
+                lg = fb_dp4a(g & 0x0f0f0f0fu, xl, lg);
+                lu = fb_dp4a(u & 0x0f0f0f0fu, xl, lu);
+                hg16 = fb_dp4a_us(g & 0xf0f0f0f0u, xh, hg16);
+                hu16 = fb_dp4a_us(u & 0xf0f0f0f0u, xh, hu16);
+            }
+        }
+        const uint32_t gw = (c < 2) ? g_sc_lo : g_sc_hi, uw = (c < 2) ? u_sc_lo : u_sc_hi;
+        const int sh = 16 * (c & 1);
+        isg += (int)((gw >> sh) & 0xff) * lg + (int)((gw >> (sh + 8)) & 0xff) * (hg16 >> 4);
+        isu += (int)((uw >> sh) & 0xff) * lu + (int)((uw >> (sh + 8)) & 0xff) * (hu16 >> 4);
+    }
+    const uint4 b0 = fb_lds128_a(a_u + 256), b1 = fb_lds128_a(a_u + 272);
+    int msg = 0, msu = 0;
+    {
+        const uint32_t g_m_lo = hg.z & 0x3f3f3f3fu, g_m_hi = ((hg.w >> 4) & 0x0f0f0f0fu) | (((hg.z >> 6) & 0x03030303u) << 4);
+        const uint32_t u_m_lo = hu.z & 0x3f3f3f3fu, u_m_hi = ((hu.w >> 4) & 0x0f0f0f0fu) | (((hu.z >> 6) & 0x03030303u) << 4);
+        const uint32_t g01 = __byte_perm(g_m_lo, 0, 0x1100), g23 = __byte_perm(g_m_lo, 0, 0x3322);
+        const uint32_t g45 = __byte_perm(g_m_hi, 0, 0x1100), g67 = __byte_perm(g_m_hi, 0, 0x3322);
+        const uint32_t u01 = __byte_perm(u_m_lo, 0, 0x1100), u23 = __byte_perm(u_m_lo, 0, 0x3322);
+        const uint32_t u45 = __byte_perm(u_m_hi, 0, 0x1100), u67 = __byte_perm(u_m_hi, 0, 0x3322);
+        msg = fb_dp2a_lo_su(b0.x, g01, msg); msu = fb_dp2a_lo_su(b0.x, u01, msu);
+        msg = fb_dp2a_hi_su(b0.y, g01, msg); msu = fb_dp2a_hi_su(b0.y, u01, msu);
+        msg = fb_dp2a_lo_su(b0.z, g23, msg); msu = fb_dp2a_lo_su(b0.z, u23, msu);
+        msg = fb_dp2a_hi_su(b0.w, g23, msg); msu = fb_dp2a_hi_su(b0.w, u23, msu);
+        msg = fb_dp2a_lo_su(b1.x, g45, msg); msu = fb_dp2a_lo_su(b1.x, u45, msu);
+        msg = fb_dp2a_hi_su(b1.y, g45, msg); msu = fb_dp2a_hi_su(b1.y, u45, msu);
+        msg = fb_dp2a_lo_su(b1.z, g67, msg); msu = fb_dp2a_lo_su(b1.z, u67, msu);
+        msg = fb_dp2a_hi_su(b1.w, g67, msg); msu = fb_dp2a_hi_su(b1.w, u67, msu);
+    }
+    float yd;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(yd) : "r"(a_u + 288));
+    fg = __fmaf_rn(__fmul_rn(yd, fb_half_bits_to_float(hg.x & 0xffff)), (float)isg,
+                   -__fmul_rn(__fmul_rn(yd, fb_half_bits_to_float(hg.x >> 16)), (float)msg));
+    fu = __fmaf_rn(__fmul_rn(yd, fb_half_bits_to_float(hu.x & 0xffff)), (float)isu,
+                   -__fmul_rn(__fmul_rn(yd, fb_half_bits_to_float(hu.x >> 16)), (float)msu));
+}
+
 __device__ __forceinline__ float fb_dot_q6k_sm(const uint4 (&ql)[8], const uint4 (&qh)[4], const uint4 &sc,
                                                uint32_t d16, uint32_t a_u) {
     /* The 6-bit weight is never assembled: its low nibble and its two high bits are multiplied with the

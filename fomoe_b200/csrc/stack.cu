@@ -419,23 +419,19 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 const uint32_t a_u = fb_smem_u32(&S->q8h[lane % bpr]);
                 for (int t = t0 + warp; t < t1 && alive; t += SK_WARPS) {
                     float f[2];
-#pragma unroll
-                    for (int which = 0; which < 2; which++) {
-                        if (!fb_mbar_wait(full_u + 8 * which, full_uses[which] & 1)) {
-                            alive = false;
-                            break;
-                        }
-                        full_uses[which]++;
-                        const uint32_t st = ring_u + which * FB_Q4K_GROUP + 16 * lane;
-                        const uint4 hd = fb_lds128(st);
-                        uint4 q[8];
-#pragma unroll
-                        for (int k = 0; k < 8; k++) q[k] = fb_lds128(st + 512 * (k + 1));
-                        __syncwarp();
-                        if (lane == 0 && t + SK_WARPS < t1) issue(t + SK_WARPS, which);
-                        f[which] = fb_dot_q4k_sm(hd, q, a_u);
+                    if (!fb_mbar_wait(full_u, full_uses[0] & 1) || !fb_mbar_wait(full_u + 8, full_uses[1] & 1)) {
+                        alive = false;
+                        break;
                     }
-                    if (!alive) break;
+                    full_uses[0]++;
+                    full_uses[1]++;
+                    /* both groups are read where they lie, sharing every activation load between gate and up */
+                    fb_dot2_q4k_sm(ring_u + 16 * lane, ring_u + FB_Q4K_GROUP + 16 * lane, a_u, f[0], f[1]);
+                    __syncwarp();
+                    if (lane == 0 && t + SK_WARPS < t1) {
+                        issue(t + SK_WARPS, 0);
+                        issue(t + SK_WARPS, 1);
+                    }
                     const float fg = fb_span_sum(f[0], bpr), fu = fb_span_sum(f[1], bpr);
                     const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
                     const int row = g * rpg + lane / bpr;
