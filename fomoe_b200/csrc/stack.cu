@@ -472,9 +472,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 fb_mbar_expect_tx(full_u + 8 * s, GB);
                 fb_bulk_g2s(dring_u + s * FB_Q6K_GROUP, S->slot_rec[slot] + A.down_off + (uint64_t)rg * GB, GB, full_u + 8 * s);
             };
-            if (warp < SK_DOWN_WARPS && lane == 0)
-                for (int i = 0; i < 2; i++)
-                    if (warp + i * SK_DOWN_WARPS < d1 - d0) dissue(dtask(warp + i * SK_DOWN_WARPS), i);
+            /* one group per warp now; the second follows the barrier and the (small, latency-critical) activation
+             * loads, which would otherwise queue behind 175 KB of weights on their way into this SM */
+            if (warp < SK_DOWN_WARPS && lane == 0 && warp < d1 - d0) dissue(dtask(warp), 0);
             alive = sk_wait(B, S);
             if (!alive) break;
             SK_STAMP(7);
@@ -495,6 +495,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         for (int i = 0; i < 8; i++) v[u][i] = 0.0f;
                     }
                 }
+                if (warp < SK_DOWN_WARPS && lane == 0 && warp + SK_DOWN_WARPS < d1 - d0) dissue(dtask(warp + SK_DOWN_WARPS), 1);
                 /* the three windows' shuffle chains are independent: run them unconditionally so they interleave */
 #pragma unroll
                 for (int u = 0; u < 3; u++) {
