@@ -400,8 +400,9 @@ class GpuOperator:
                    down_type):
         """Returns (rc, ffn_out); rc == -1 means "fall back to the CPU path" as in the reference."""
         h, scores = _f32(h), _f32(scores)
-        keep = [np.ascontiguousarray(e).view(np.uint8).reshape(-1) for e in expert_buffers]
-        ptrs = (C.c_void_p * len(keep))(*[e.ctypes.data for e in keep])
+        # an int is taken as a raw address (e.g. a record already in device memory), anything else as host bytes
+        keep = [e if isinstance(e, int) else np.ascontiguousarray(e).view(np.uint8).reshape(-1) for e in expert_buffers]
+        ptrs = (C.c_void_p * len(keep))(*[e if isinstance(e, int) else e.ctypes.data for e in keep])
         out = np.zeros(n_embd, dtype=np.float32)
         rc = self._l.gpu_expert_ffn(self._h, _fp(h), ptrs, _fp(scores), len(keep), n_embd, inter, gate_size, up_size,
                                     stride, gate_type, up_type, down_type, _fp(out))

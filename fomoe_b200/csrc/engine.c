@@ -454,10 +454,20 @@ static int upload_record(fomoe_b200_ctx_t *c, int layer, int expert, const void 
     const uint64_t gb = ggml_matrix_bytes(c->cfg.gate_type, c->cfg.n_inter, c->cfg.n_embd);
     const uint64_t rb = fomoe_b200_record_bytes(c, layer);
     uint8_t *dst = L->table + (uint64_t)expert * L->rec_bytes;
-    CK(c, cudaMemcpyAsync(c->stage, record, rb, cudaMemcpyHostToDevice, c->stream));
-    CKL(c, fb_launch_repack(dst, c->stage, geom_gate(c), c->stream));
-    CKL(c, fb_launch_repack(dst + c->gate_bytes, c->stage + gb, geom_gate(c), c->stream));
-    CKL(c, fb_launch_repack(dst + 2 * c->gate_bytes, c->stage + 2 * gb, geom_down(c, L->down_type), c->stream));
+    /* `record` may be a host pointer (the reference's callers, src/inference.c:538-549: staged through a device
+     * buffer) or memory of this GPU (an expert that a caller already keeps in device memory: repacked where it lies) */
+    const uint8_t *src = c->stage;
+    struct cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, record) == cudaSuccess && at.type == cudaMemoryTypeDevice &&
+        at.device == c->cfg.device) {
+        src = (const uint8_t *)record;
+    } else {
+        cudaGetLastError(); /* an unregistered host pointer is not an error */
+        CK(c, cudaMemcpyAsync(c->stage, record, rb, cudaMemcpyDefault, c->stream));
+    }
+    CKL(c, fb_launch_repack(dst, src, geom_gate(c), c->stream));
+    CKL(c, fb_launch_repack(dst + c->gate_bytes, src + gb, geom_gate(c), c->stream));
+    CKL(c, fb_launch_repack(dst + 2 * c->gate_bytes, src + 2 * gb, geom_down(c, L->down_type), c->stream));
     return 0;
 }
 

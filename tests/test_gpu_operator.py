@@ -27,6 +27,24 @@ def test_gpu_expert_ffn_matches_cpu_expert(fb, oracle, down_type, n):
     op.close()
 
 
+def test_gpu_expert_ffn_takes_records_in_device_memory(fb):
+    """Expert pointers may be host memory (the reference's callers) or memory of the GPU: same bits either way."""
+    import torch
+    n_embd, inter, seed, n = 2048, 512, 67, 5
+    op = fb.GpuOperator()
+    ex = _experts(fb, seed, n, H.Q6, n_embd, inter)
+    h = H.hidden(fb, seed, 0, n_embd)
+    sc = np.random.default_rng(2).dirichlet(np.ones(n)).astype(np.float32)
+    gs = fb.matrix_bytes(H.Q4, inter, n_embd)
+    rc, host = op.expert_ffn(h, ex, sc, n_embd, inter, gs, gs, ex[0].size, H.Q4, H.Q4, H.Q6)
+    assert rc == 0
+    dev = [torch.from_numpy(e.copy()).cuda() for e in ex]
+    mixed = [dev[i].data_ptr() if i % 2 == 0 else ex[i] for i in range(n)]   # device and host records in one call
+    rc, got = op.expert_ffn(h, mixed, sc, n_embd, inter, gs, gs, ex[0].size, H.Q4, H.Q4, H.Q6)
+    assert rc == 0 and (H.bits(got) == H.bits(host)).all()
+    op.close()
+
+
 def test_gpu_expert_ffn_rejects_like_the_reference(fb):
     """-1 = "fall back to CPU" for the reference's limits (src/gpu_kernels.hip:8393-8403)."""
     n_embd, inter, seed = 512, 256, 3
