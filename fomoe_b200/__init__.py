@@ -159,6 +159,30 @@ def synth_f32(seed, layer, stream_id, mean, std, n):
     return out
 
 
+# ---- the seeded synthetic inputs of the benchmark configurations, as the table generator on the device makes them
+def synth_hidden(seed, token, n_embd):
+    """Input hidden state of token `token`: N(0, 1)."""
+    return synth_f32(seed, token, STREAM_HIDDEN, 0.0, 1.0, n_embd)
+
+
+def synth_router(seed, layer, n_experts, n_embd):
+    """fp32 router of a layer: N(0, 0.02), [n_experts, n_embd]."""
+    return synth_f32(seed, layer, STREAM_ROUTER, 0.0, ROUTER_STD, n_experts * n_embd).reshape(n_experts, n_embd)
+
+
+def synth_glue(seed, layer, n_embd):
+    """(residual vector, RMSNorm weight) of a layer of the decode stack."""
+    return (synth_f32(seed, layer, STREAM_RESID, 0.0, RESID_STD, n_embd),
+            synth_f32(seed, layer, STREAM_NORMW, NORMW_MEAN, NORMW_STD, n_embd))
+
+
+def synth_expert_record(seed, layer, expert, down_type, n_embd, inter):
+    """One expert in the reference's record order (include/expert_store.h:9-40): gate | up | down, ggml bytes."""
+    return np.concatenate([synth_matrix(seed, layer, expert, M_GATE, TYPE_Q4_K, inter, n_embd),
+                           synth_matrix(seed, layer, expert, M_UP, TYPE_Q4_K, inter, n_embd),
+                           synth_matrix(seed, layer, expert, M_DOWN, down_type, n_embd, inter)])
+
+
 class MoeDecoder:
     """Resident expert table + router/CAR + SwiGLU experts + decode stack on one GPU (one TP rank)."""
 

@@ -16,24 +16,19 @@ def bits(a):
 
 def expert_record(fb, seed, layer, expert, down_type, n_embd, inter):
     """One expert in the reference's record order: gate | up | down, ggml bytes."""
-    g = fb.synth_matrix(seed, layer, expert, fb.M_GATE, Q4, inter, n_embd)
-    u = fb.synth_matrix(seed, layer, expert, fb.M_UP, Q4, inter, n_embd)
-    d = fb.synth_matrix(seed, layer, expert, fb.M_DOWN, down_type, n_embd, inter)
-    return np.concatenate([g, u, d])
+    return fb.synth_expert_record(seed, layer, expert, down_type, n_embd, inter)
 
 
 def router_weights(fb, seed, layer, n_experts, n_embd):
-    return fb.synth_f32(seed, layer, fb.STREAM_ROUTER, 0.0, fb.ROUTER_STD, n_experts * n_embd).reshape(n_experts, n_embd)
+    return fb.synth_router(seed, layer, n_experts, n_embd)
 
 
 def hidden(fb, seed, token, n_embd):
-    return fb.synth_f32(seed, token, fb.STREAM_HIDDEN, 0.0, 1.0, n_embd)
+    return fb.synth_hidden(seed, token, n_embd)
 
 
 def glue(fb, seed, layer, n_embd):
-    r = fb.synth_f32(seed, layer, fb.STREAM_RESID, 0.0, fb.RESID_STD, n_embd)
-    w = fb.synth_f32(seed, layer, fb.STREAM_NORMW, fb.NORMW_MEAN, fb.NORMW_STD, n_embd)
-    return r, w
+    return fb.synth_glue(seed, layer, n_embd)
 
 
 def zipf_resident_mask(seed, layer, n_experts, frac=0.4, s=1.1):
