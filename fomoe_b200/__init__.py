@@ -23,7 +23,7 @@ TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K = 12, 13, 14
 STREAM_ROUTER, STREAM_RESID, STREAM_NORMW, STREAM_HIDDEN = 3, 4, 5, 6
 M_GATE, M_UP, M_DOWN = 0, 1, 2
 ROUTER_STD, RESID_STD, NORMW_MEAN, NORMW_STD = 0.02, 1.0, 1.0, 0.1
-BLOCK_BYTES = {TYPE_Q4_K: 144, TYPE_Q6_K: 210}
+BLOCK_BYTES = {TYPE_Q4_K: 144, TYPE_Q5_K: 176, TYPE_Q6_K: 210}
 
 _f32p = C.POINTER(C.c_float)
 _i32p = C.POINTER(C.c_int)

@@ -5,6 +5,8 @@
  * Arithmetic follows the reference's Q8_K-activation path:
  *   Q4_K: src/quant.c:405-476   sum_j sc_j * dot32(q4_j, q8_j) as int32, times (y.d * d), minus
  *                               (y.d * dmin) * sum_j m_j * (bsum_2j + bsum_2j+1)
+ *   Q5_K: src/quant.c:609-621   the reference dequantises the block and sums tmp*y.d*q8 in fp32; here the same
+ *                               value is formed like Q4_K's, with q5 = nibble + 16*bit, in exact integers
  *   Q6_K: src/quant.c:478-607   sum_g sc_g * dot16(q6_g, q8_g) as int32, times (y.d * d)
  *   Q8_K: src/quant.c:343-375   amax, iscale = 127/amax, roundf, clamp, bsums, d = 1/iscale
  * All integer sums are exact, so dp4a may associate them freely; only the fp32 sum over
@@ -88,6 +90,54 @@ __device__ __forceinline__ float fb_dot_q4k(const uint4 &hdr, const uint4 (&qs)[
         isum += s0 * lo + s1 * hi;
     }
     /* mins: bsums are int16 pairs; bs32_j = bsums[2j] + bsums[2j+1] */
+    const uint4 b0 = a[16], b1 = a[17];
+    int msum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const uint32_t pr = fb_u4c(j < 4 ? b0 : b1, j & 3);
+        const int bs = (int)(short)(pr & 0xffff) + (int)(short)(pr >> 16);
+        const uint32_t mw = (j < 4) ? m_lo : m_hi;
+        msum += (int)((mw >> (8 * (j & 3))) & 0xff) * bs;
+    }
+    const float yd = __uint_as_float(a[18].x);
+    const float d = __fmul_rn(yd, fb_half_bits_to_float(hdr.x & 0xffff));
+    const float dmin = __fmul_rn(yd, fb_half_bits_to_float(hdr.x >> 16));
+    return __fmaf_rn(d, (float)isum, -__fmul_rn(dmin, (float)msum));
+}
+
+/* Q5_K: header and quant pieces as Q4_K; h0,h1 = the 32 bytes of fifth bits (byte l: bit j belongs to weight l of
+ * 32-weight sub-block j).  The bits are multiplied where they stand (mask 0x01010101 << j) and scaled back after. */
+__device__ __forceinline__ float fb_dot_q5k(const uint4 &hdr, const uint4 &h0, const uint4 &h1, const uint4 (&qs)[8],
+                                            const uint4 *a) {
+    const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+    const uint32_t sc_lo = u0 & 0x3f3f3f3fu;
+    const uint32_t sc_hi = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
+    const uint32_t m_lo = u1 & 0x3f3f3f3fu;
+    const uint32_t m_hi = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
+    int isum = 0;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        int lo = 0, hi16 = 0, blo = 0, bhi = 0; /* blo = 2^(2c) * sum(bit * q8), bhi = 2^(2c+1) * ... */
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            const uint4 w = qs[2 * c + kk];
+            const uint4 hb = kk ? h1 : h0;
+            const uint4 al = a[4 * c + kk];
+            const uint4 ah = a[4 * c + 2 + kk];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t q = fb_u4c(w, i), h = fb_u4c(hb, i), xl = fb_u4c(al, i), xh = fb_u4c(ah, i);
+                lo = fb_dp4a(q & 0x0f0f0f0fu, xl, lo);
+                hi16 = fb_dp4a_us(q & 0xf0f0f0f0u, xh, hi16);
+                blo = fb_dp4a_us(h & (0x01010101u << (2 * c)), xl, blo);
+                bhi = fb_dp4a_us(h & (0x01010101u << (2 * c + 1)), xh, bhi);
+            }
+        }
+        const uint32_t scw = (c < 2) ? sc_lo : sc_hi;
+        const int s0 = (scw >> (16 * (c & 1))) & 0xff, s1 = (scw >> (16 * (c & 1) + 8)) & 0xff;
+        /* exact: the masked sums are multiples of the power of two they carry */
+        isum += s0 * (lo + 16 * (blo >> (2 * c))) + s1 * ((hi16 >> 4) + 16 * (bhi >> (2 * c + 1)));
+    }
     const uint4 b0 = a[16], b1 = a[17];
     int msum = 0;
 #pragma unroll
@@ -261,6 +311,58 @@ __device__ __forceinline__ void fb_dot2_q4k_sm(uint32_t sg_u, uint32_t su_u, uin
                    -__fmul_rn(__fmul_rn(yd, fb_half_bits_to_float(hg.x >> 16)), (float)msg));
     fu = __fmaf_rn(__fmul_rn(yd, fb_half_bits_to_float(hu.x & 0xffff)), (float)isu,
                    -__fmul_rn(__fmul_rn(yd, fb_half_bits_to_float(hu.x >> 16)), (float)msu));
+}
+
+/* Q5_K with the activation entry in shared memory (see fb_dot_q5k for the arithmetic). */
+__device__ __forceinline__ float fb_dot_q5k_sm(const uint4 &hdr, const uint4 &h0, const uint4 &h1, const uint4 (&qs)[8],
+                                               uint32_t a_u) {
+    const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+    const uint32_t sc_lo = u0 & 0x3f3f3f3fu;
+    const uint32_t sc_hi = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
+    const uint32_t m_lo = u1 & 0x3f3f3f3fu;
+    const uint32_t m_hi = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
+    int isum = 0;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        int lo = 0, hi16 = 0, blo = 0, bhi = 0;
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            const uint4 w = qs[2 * c + kk];
+            const uint4 hb = kk ? h1 : h0;
+            const uint4 al = fb_lds128_a(a_u + 16 * (4 * c + kk));
+            const uint4 ah = fb_lds128_a(a_u + 16 * (4 * c + 2 + kk));
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t q = fb_u4c(w, i), h = fb_u4c(hb, i), xl = fb_u4c(al, i), xh = fb_u4c(ah, i);
+                lo = fb_dp4a(q & 0x0f0f0f0fu, xl, lo);
+                hi16 = fb_dp4a_us(q & 0xf0f0f0f0u, xh, hi16);
+                blo = fb_dp4a_us(h & (0x01010101u << (2 * c)), xl, blo);
+                bhi = fb_dp4a_us(h & (0x01010101u << (2 * c + 1)), xh, bhi);
+            }
+        }
+        const uint32_t scw = (c < 2) ? sc_lo : sc_hi;
+        const int s0 = (scw >> (16 * (c & 1))) & 0xff, s1 = (scw >> (16 * (c & 1) + 8)) & 0xff;
+        isum += s0 * (lo + 16 * (blo >> (2 * c))) + s1 * ((hi16 >> 4) + 16 * (bhi >> (2 * c + 1)));
+    }
+    const uint4 b0 = fb_lds128_a(a_u + 256), b1 = fb_lds128_a(a_u + 272);
+    int msum = 0;
+    {
+        const uint32_t d01 = __byte_perm(m_lo, 0, 0x1100), d23 = __byte_perm(m_lo, 0, 0x3322);
+        const uint32_t d45 = __byte_perm(m_hi, 0, 0x1100), d67 = __byte_perm(m_hi, 0, 0x3322);
+        msum = fb_dp2a_lo_su(b0.x, d01, msum);
+        msum = fb_dp2a_hi_su(b0.y, d01, msum);
+        msum = fb_dp2a_lo_su(b0.z, d23, msum);
+        msum = fb_dp2a_hi_su(b0.w, d23, msum);
+        msum = fb_dp2a_lo_su(b1.x, d45, msum);
+        msum = fb_dp2a_hi_su(b1.y, d45, msum);
+        msum = fb_dp2a_lo_su(b1.z, d67, msum);
+        msum = fb_dp2a_hi_su(b1.w, d67, msum);
+    }
+    float yd;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(yd) : "r"(a_u + 288));
+    const float d = __fmul_rn(yd, fb_half_bits_to_float(hdr.x & 0xffff));
+    const float dmin = __fmul_rn(yd, fb_half_bits_to_float(hdr.x >> 16));
+    return __fmaf_rn(d, (float)isum, -__fmul_rn(dmin, (float)msum));
 }
 
 __device__ __forceinline__ float fb_dot_q6k_sm(const uint4 (&ql)[8], const uint4 (&qh)[4], const uint4 &sc,

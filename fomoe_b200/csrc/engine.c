@@ -228,7 +228,7 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
     c->down_types = (int *)malloc(sizeof(int) * (size_t)cfg->n_layers);
     for (int l = 0; l < cfg->n_layers; l++) {
         c->down_types[l] = cfg->down_types ? cfg->down_types[l] : FB_TYPE_Q6_K;
-        if (c->down_types[l] != FB_TYPE_Q4_K && c->down_types[l] != FB_TYPE_Q6_K) {
+        if (c->down_types[l] != FB_TYPE_Q4_K && c->down_types[l] != FB_TYPE_Q5_K && c->down_types[l] != FB_TYPE_Q6_K) {
             set_err(c, "layer %d: down type %d unsupported", l, c->down_types[l]);
             free(c->down_types);
             free(c);
@@ -1009,7 +1009,7 @@ int fomoe_b200_peek(fomoe_b200_ctx_t *c, int what, void *out, uint64_t bytes) {
 int fomoe_b200_matvec(fomoe_b200_ctx_t *c, int type, const void *w, int rows, int cols, const float *x, float *y) {
     if (!c || !w || !x || !y || rows < 1 || cols % FB_QK || cols < FB_QK) return -1;
     const int bpr = cols / FB_QK;
-    if ((type != FB_TYPE_Q4_K && type != FB_TYPE_Q6_K) || !is_pow2(bpr) || bpr > 32) {
+    if ((type != FB_TYPE_Q4_K && type != FB_TYPE_Q5_K && type != FB_TYPE_Q6_K) || !is_pow2(bpr) || bpr > 32) {
         set_err(c, "matvec: unsupported type %d / cols %d", type, cols);
         return -1;
     }
@@ -1080,6 +1080,10 @@ void fomoe_b200_synth_matrix(uint64_t seed, int layer, int expert, int matrix, i
             uint32_t w[36];
             fsyn_q4k_block(key, b, w);
             memcpy(o + b * FB_Q4K_BLOCK, w, FB_Q4K_BLOCK);
+        } else if (type == FB_TYPE_Q5_K) {
+            uint32_t w[44];
+            fsyn_q5k_block(key, b, w);
+            memcpy(o + b * FB_Q5K_BLOCK, w, FB_Q5K_BLOCK);
         } else {
             uint32_t ql[32], qh[16], sc[4];
             uint16_t d;
@@ -1220,7 +1224,7 @@ void gpu_get_pingpong_relay_stats(gpu_ctx_t *ctx, uint64_t *handoffs, uint64_t *
 
 static int op_types_ok(int gate_type, int up_type, int down_type) {
     return gate_type == FB_TYPE_Q4_K && up_type == FB_TYPE_Q4_K &&
-           (down_type == FB_TYPE_Q4_K || down_type == FB_TYPE_Q6_K);
+           (down_type == FB_TYPE_Q4_K || down_type == FB_TYPE_Q5_K || down_type == FB_TYPE_Q6_K);
 }
 
 int gpu_expert_ffn(gpu_ctx_t *ctx, const float *h, void **expert_buffers, const float *expert_scores, int n_experts,

@@ -6,7 +6,7 @@
  *                softmax, ordered top-k, renormalise and CAR substitute-and-dampen in one warp
  *   k_gate_up    Q4_K gate and up dequant-matvec of every selected expert + the shared expert,
  *                SwiGLU in the epilogue; the last warp to finish a 256-row window quantises it
- *   k_down       Q4_K / Q6_K down dequant-matvec per expert; the last warp to finish a row group
+ *   k_down       Q4_K / Q5_K / Q6_K down dequant-matvec per expert; the last warp to finish a row group
  *                combines the experts with their routing weights in list order
  *
  * Reference counterparts: src/gpu_kernels.hip:2127 (router matvec), 2668 (softmax), 2745 (top-k),
@@ -238,6 +238,13 @@ __global__ void __launch_bounds__(256) k_down(fb_args_t A) {
 #pragma unroll
             for (int i = 0; i < 8; i++) q[i] = ldg_stream(p + 32 * (i + 1));
             f = fb_dot_q4k(hd, q, a);
+        } else if (TYPE == FB_TYPE_Q5_K) {
+            const uint4 *p = reinterpret_cast<const uint4 *>(rec + (uint64_t)rg * FB_Q5K_GROUP) + lane;
+            const uint4 hd = ldg_stream(p), h0 = ldg_stream(p + 32), h1 = ldg_stream(p + 64);
+            uint4 q[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) q[i] = ldg_stream(p + 32 * (i + 3));
+            f = fb_dot_q5k(hd, h0, h1, q, a);
         } else {
             const uint8_t *gb = rec + (uint64_t)rg * FB_Q6K_GROUP;
             const uint4 *p = reinterpret_cast<const uint4 *>(gb) + lane;
@@ -519,6 +526,7 @@ extern "C" int fb_launch_gate_up_ring(const fb_args_t *a, int grid, void *stream
 }
 
 extern "C" int fb_launch_down_ring(const fb_args_t *a, int grid, void *stream) {
+    if (a->down_type == FB_TYPE_Q5_K) return fb_launch_down(a, grid, stream); /* no ring variant for Q5_K */
     const int ns = a->n_slots;
     const size_t sm = (size_t)ns * DN_STAGES * DN_STAGE_BYTES + sizeof(float) * 2 * ns * 32 + 8 * (ns * DN_STAGES + 4);
     static int configured = 0;
@@ -541,6 +549,8 @@ extern "C" int fb_launch_down(const fb_args_t *a, int grid, void *stream) {
     const size_t sm = (size_t)a->n_slots * a->down_bpr * sizeof(fb_q8_entry_t);
     if (a->down_type == FB_TYPE_Q4_K)
         k_down<FB_TYPE_Q4_K><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
+    else if (a->down_type == FB_TYPE_Q5_K)
+        k_down<FB_TYPE_Q5_K><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
     else
         k_down<FB_TYPE_Q6_K><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
     return (int)cudaGetLastError();

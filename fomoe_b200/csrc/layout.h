@@ -1,19 +1,22 @@
 /*
  * layout.h -- how expert weights lie in HBM ("lane-striped groups").
  *
- * The ggml block formats (Q4_K 144 B, Q6_K 210 B; the reference's include/quant_types.h:17-41)
+ * The ggml block formats (Q4_K 144 B, Q5_K 176 B, Q6_K 210 B; the reference's include/quant_types.h:17-41)
  * are kept bit for bit, but the bytes of every 32 consecutive blocks of a matrix shard are
  * regrouped so that lane L of a warp owns block L of the group and every 16-byte piece a
  * lane needs sits next to the same piece of its 31 neighbours:
  *
  *   Q4_K group (4608 B):  uint4 hdr[32]      hdr[L] = {d | dmin<<16, scales[0..11]}
  *                         uint4 qs[8][32]    qs[k][L] = bytes 16k..16k+15 of block L's qs
+ *   Q5_K group (5632 B):  uint4 hdr[32]      as Q4_K
+ *                         uint4 qh[2][32]    qh[k][L] = bytes 16k..16k+15 of block L's qh (the fifth bits)
+ *                         uint4 qs[8][32]    as Q4_K
  *   Q6_K group (6720 B):  uint4 ql[8][32]    ql[k][L] = bytes 16k..16k+15 of block L's ql
  *                         uint4 qh[4][32]    qh[k][L] = bytes 16k..16k+15 of block L's qh
  *                         uint4 sc[32]       sc[L]    = the 16 int8 scales
  *                         uint16 d[32]
  *
- * A warp therefore fetches a whole group with 9 (Q4_K) or 14 (Q6_K) fully coalesced
+ * A warp therefore fetches a whole group with 9 (Q4_K), 11 (Q5_K) or 14 (Q6_K) fully coalesced
  * 512-byte requests, all independent, and no byte is padded: a shard occupies exactly
  * its ggml size.  Blocks of a shard are numbered row-major over the rows and the
  * 256-column blocks this rank owns (tensor parallelism splits gate/up by rows and down
@@ -27,12 +30,15 @@
 #include <stdint.h>
 
 #define FB_TYPE_Q4_K 12
+#define FB_TYPE_Q5_K 13
 #define FB_TYPE_Q6_K 14
 #define FB_QK 256
 #define FB_Q4K_BLOCK 144u
+#define FB_Q5K_BLOCK 176u
 #define FB_Q6K_BLOCK 210u
 #define FB_GROUP 32u
 #define FB_Q4K_GROUP (FB_Q4K_BLOCK * FB_GROUP) /* 4608 */
+#define FB_Q5K_GROUP (FB_Q5K_BLOCK * FB_GROUP) /* 5632 */
 #define FB_Q6K_GROUP (FB_Q6K_BLOCK * FB_GROUP) /* 6720 */
 #define FB_Q6K_OFF_QH 4096u
 #define FB_Q6K_OFF_SC 6144u
@@ -49,7 +55,7 @@
 #endif
 
 FB_HD uint64_t fb_block_bytes(int type) {
-    return type == FB_TYPE_Q4_K ? FB_Q4K_BLOCK : type == FB_TYPE_Q6_K ? FB_Q6K_BLOCK : 0;
+    return type == FB_TYPE_Q4_K ? FB_Q4K_BLOCK : type == FB_TYPE_Q5_K ? FB_Q5K_BLOCK : type == FB_TYPE_Q6_K ? FB_Q6K_BLOCK : 0;
 }
 FB_HD uint64_t fb_group_bytes(int type) { return fb_block_bytes(type) * FB_GROUP; }
 FB_HD uint64_t fb_n_groups(uint64_t n_blocks) { return (n_blocks + FB_GROUP - 1) / FB_GROUP; }

@@ -456,7 +456,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
              *      long run per block dealt round-robin to 12 warps (two ring stages of one group each). */
             sk_arrive(B, S);
             const int ns = A.n_slots, dbpr = A.down_bpr, drpg = 32 / dbpr;
-            const uint32_t GB = (A.down_type == FB_TYPE_Q4_K) ? FB_Q4K_GROUP : FB_Q6K_GROUP;
+            const uint32_t GB = (A.down_type == FB_TYPE_Q4_K) ? FB_Q4K_GROUP : (A.down_type == FB_TYPE_Q5_K) ? FB_Q5K_GROUP : FB_Q6K_GROUP;
             const int dtotal = A.down_groups * ns;
             const int d0 = (int)(((long long)cta * dtotal) / G), d1 = (int)(((long long)(cta + 1) * dtotal) / G);
             /* the run [d0, d1): its last row group continues in the next block when d1 is not a multiple of ns;
@@ -526,6 +526,14 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         __syncwarp();
                         if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
                         f = fb_dot_q4k_sm(hd, q, a_u);
+                    } else if (A.down_type == FB_TYPE_Q5_K) {
+                        const uint4 hd = fb_lds128(st), h0 = fb_lds128(st + 512), h1 = fb_lds128(st + 1024);
+                        uint4 q[8];
+#pragma unroll
+                        for (int k = 0; k < 8; k++) q[k] = fb_lds128(st + 512 * (k + 3));
+                        __syncwarp();
+                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        f = fb_dot_q5k_sm(hd, h0, h1, q, a_u);
                     } else {
                         uint4 ql[8], qh[4];
 #pragma unroll

@@ -10,6 +10,7 @@
  * Distributions follow the benchmark's synthetic-input description:
  *   Q4_K block: d, dmin = fp16(|z| * 1e-3); the 12 scale bytes and 128 nibble bytes are raw
  *               hash bytes (uniform 6-bit scales/mins, uniform nibbles).
+ *   Q5_K block: as Q4_K, the 32 bytes of fifth bits raw hash bytes as well.
  *   Q6_K block: ql, qh raw hash bytes; scales = (byte & 63) - 32; d = fp16(|z| * 1e-3).
  *   fp32 streams (router, hidden, residual, norm weight): mean + std * z.
  * z is an 8-term Irwin-Hall variate (sum of eight 16-bit uniforms, centred and scaled to
@@ -97,6 +98,7 @@ FSYN_HD uint16_t fsyn_scale_f16(uint64_t key, uint64_t widx) {
  * (0-15 ql, 16-23 qh, 24-25 scales, 26-27 d). */
 #define FSYN_Q4K_WORDS 22u
 #define FSYN_Q6K_WORDS 28u
+#define FSYN_Q5K_WORDS 26u /* 0-3 d/dmin, 4-5 scales, 6-9 qh, 10-25 qs */
 
 /* Writes block `blk` of the stream `key` in ggml Q4_K byte order (144 B) as 36 u32. */
 FSYN_HD void fsyn_q4k_block(uint64_t key, uint64_t blk, uint32_t out[36]) {
@@ -108,6 +110,22 @@ FSYN_HD void fsyn_q4k_block(uint64_t key, uint64_t blk, uint32_t out[36]) {
     out[2] = (uint32_t)(s0 >> 32);
     out[3] = (uint32_t)s1;
     for (int i = 0; i < 16; i++) {
+        uint64_t w = fsyn_word(key, base + 6 + i);
+        out[4 + 2 * i] = (uint32_t)w;
+        out[5 + 2 * i] = (uint32_t)(w >> 32);
+    }
+}
+
+/* Writes block `blk` in ggml Q5_K byte order (176 B) as 44 u32: d|dmin, scales[12], qh[32], qs[128]. */
+FSYN_HD void fsyn_q5k_block(uint64_t key, uint64_t blk, uint32_t out[44]) {
+    uint64_t base = blk * FSYN_Q5K_WORDS;
+    uint32_t d = fsyn_scale_f16(key, base + 0), dmin = fsyn_scale_f16(key, base + 2);
+    out[0] = d | (dmin << 16);
+    uint64_t s0 = fsyn_word(key, base + 4), s1 = fsyn_word(key, base + 5);
+    out[1] = (uint32_t)s0;
+    out[2] = (uint32_t)(s0 >> 32);
+    out[3] = (uint32_t)s1;
+    for (int i = 0; i < 20; i++) {
         uint64_t w = fsyn_word(key, base + 6 + i);
         out[4 + 2 * i] = (uint32_t)w;
         out[5 + 2 * i] = (uint32_t)(w >> 32);

@@ -31,6 +31,12 @@ __device__ __forceinline__ void store_q4k(uint8_t *shard, int lb, const uint32_t
     for (int k = 0; k < 9; k++) grp[32 * k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
 }
 
+__device__ __forceinline__ void store_q5k(uint8_t *shard, int lb, const uint32_t w[44]) {
+    uint4 *grp = reinterpret_cast<uint4 *>(shard + (uint64_t)(lb >> 5) * FB_Q5K_GROUP) + (lb & 31);
+#pragma unroll
+    for (int k = 0; k < 11; k++) grp[32 * k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+}
+
 __device__ __forceinline__ void store_q6k(uint8_t *shard, int lb, const uint32_t ql[32], const uint32_t qh[16],
                                           const uint32_t sc[4], uint16_t d) {
     uint8_t *gb = shard + (uint64_t)(lb >> 5) * FB_Q6K_GROUP;
@@ -58,6 +64,12 @@ __global__ void k_gen_shards(uint8_t *dst0, uint64_t rec_stride, uint64_t seed, 
             else
                 for (int i = 0; i < 36; i++) w[i] = 0;
             store_q4k(shard, lb, w);
+        } else if (g.type == FB_TYPE_Q5_K) {
+            uint32_t w[44];
+            if (lb < n_local) fsyn_q5k_block(key, full_block_index(g, lb), w);
+            else
+                for (int i = 0; i < 44; i++) w[i] = 0;
+            store_q5k(shard, lb, w);
         } else {
             uint32_t ql[32], qh[16], sc[4];
             uint16_t d = 0;
@@ -77,7 +89,7 @@ __global__ void k_gen_f32(float *dst, uint64_t n, uint64_t key, float mean, floa
         dst[i] = fsyn_f32(key, i, mean, std);
 }
 
-/* ggml bytes of the full matrix -> shard.  Q4_K blocks are 16-byte aligned in ggml order;
+/* ggml bytes of the full matrix -> shard.  Q4_K and Q5_K blocks are 16-byte aligned in ggml order;
  * Q6_K blocks (210 B) are only 2-byte aligned, so they are read as 16-bit pieces. */
 __global__ void k_repack(uint8_t *shard, const uint8_t *src, fb_shard_geom_t g) {
     const int n_local = g.rows_local * g.bpr_local;
@@ -91,6 +103,14 @@ __global__ void k_repack(uint8_t *shard, const uint8_t *src, fb_shard_geom_t g) 
             } else
                 for (int i = 0; i < 36; i++) w[i] = 0;
             store_q4k(shard, lb, w);
+        } else if (g.type == FB_TYPE_Q5_K) {
+            uint32_t w[44];
+            if (lb < n_local) {
+                const uint32_t *s = reinterpret_cast<const uint32_t *>(src + full_block_index(g, lb) * FB_Q5K_BLOCK);
+                for (int i = 0; i < 44; i++) w[i] = s[i];
+            } else
+                for (int i = 0; i < 44; i++) w[i] = 0;
+            store_q5k(shard, lb, w);
         } else {
             uint32_t w[52];
             uint16_t d = 0;
@@ -113,6 +133,10 @@ __global__ void k_export_ggml(uint8_t *dst, const uint8_t *shard, fb_shard_geom_
             const uint4 *grp = reinterpret_cast<const uint4 *>(shard + (uint64_t)(lb >> 5) * FB_Q4K_GROUP) + (lb & 31);
             uint4 *o = reinterpret_cast<uint4 *>(dst + (uint64_t)lb * FB_Q4K_BLOCK);
             for (int k = 0; k < 9; k++) o[k] = grp[32 * k];
+        } else if (g.type == FB_TYPE_Q5_K) {
+            const uint4 *grp = reinterpret_cast<const uint4 *>(shard + (uint64_t)(lb >> 5) * FB_Q5K_GROUP) + (lb & 31);
+            uint4 *o = reinterpret_cast<uint4 *>(dst + (uint64_t)lb * FB_Q5K_BLOCK);
+            for (int k = 0; k < 11; k++) o[k] = grp[32 * k];
         } else {
             const uint8_t *gb = shard + (uint64_t)(lb >> 5) * FB_Q6K_GROUP;
             const uint4 *grp = reinterpret_cast<const uint4 *>(gb) + (lb & 31);
@@ -155,6 +179,35 @@ __global__ void k_dequant(float *dst, const uint8_t *shard, fb_shard_geom_t g) {
                         const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xff;
                         y[64 * c + 16 * kk + i] = __fsub_rn(__fmul_rn(d1, (float)(byte & 0xf)), m1);
                         y[64 * c + 32 + 16 * kk + i] = __fsub_rn(__fmul_rn(d2, (float)(byte >> 4)), m2);
+                    }
+                }
+            }
+        } else if (g.type == FB_TYPE_Q5_K) { /* src/quant.c:216-247: the nibble plus 16 where the fifth bit is set */
+            const uint4 *grp = reinterpret_cast<const uint4 *>(shard + (uint64_t)(lb >> 5) * FB_Q5K_GROUP) + (lb & 31);
+            const uint4 hdr = grp[0];
+            const float d = fb_half_bits_to_float(hdr.x & 0xffff), mn = fb_half_bits_to_float(hdr.x >> 16);
+            const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+            const uint32_t sc_lo = u0 & 0x3f3f3f3fu, sc_hi = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
+            const uint32_t m_lo = u1 & 0x3f3f3f3fu, m_hi = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
+            const uint4 h0 = grp[32], h1 = grp[64];
+            const uint32_t hb[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w}; /* qh bytes 0..31 */
+            for (int c = 0; c < 4; c++) {
+                const uint32_t scw = c < 2 ? sc_lo : sc_hi, mw = c < 2 ? m_lo : m_hi;
+                const float d1 = __fmul_rn(d, (float)((scw >> (16 * (c & 1))) & 0xff));
+                const float d2 = __fmul_rn(d, (float)((scw >> (16 * (c & 1) + 8)) & 0xff));
+                const float m1 = __fmul_rn(mn, (float)((mw >> (16 * (c & 1))) & 0xff));
+                const float m2 = __fmul_rn(mn, (float)((mw >> (16 * (c & 1) + 8)) & 0xff));
+                for (int kk = 0; kk < 2; kk++) {
+                    const uint4 v = grp[32 * (3 + 2 * c + kk)];
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                    for (int i = 0; i < 16; i++) {
+                        const int l = 16 * kk + i; /* byte l of this chunk's 32 quant bytes and of qh */
+                        const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xff;
+                        const uint32_t hbyte = (hb[l >> 2] >> (8 * (l & 3))) & 0xff;
+                        const uint32_t q1 = (byte & 0xf) + (((hbyte >> (2 * c)) & 1) ? 16 : 0);
+                        const uint32_t q2 = (byte >> 4) + (((hbyte >> (2 * c + 1)) & 1) ? 16 : 0);
+                        y[64 * c + l] = __fsub_rn(__fmul_rn(d1, (float)q1), m1);
+                        y[64 * c + 32 + l] = __fsub_rn(__fmul_rn(d2, (float)q2), m2);
                     }
                 }
             }
@@ -215,6 +268,13 @@ __global__ void __launch_bounds__(256) k_matvec(float *out, const uint8_t *shard
 #pragma unroll
             for (int i = 0; i < 8; i++) q[i] = p[32 * (i + 1)];
             f = fb_dot_q4k(hd, q, a);
+        } else if (TYPE == FB_TYPE_Q5_K) {
+            const uint4 *p = reinterpret_cast<const uint4 *>(shard + (uint64_t)gi * FB_Q5K_GROUP) + lane;
+            const uint4 hd = p[0], h0 = p[32], h1 = p[64];
+            uint4 q[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) q[i] = p[32 * (i + 3)];
+            f = fb_dot_q5k(hd, h0, h1, q, a);
         } else {
             const uint8_t *gb = shard + (uint64_t)gi * FB_Q6K_GROUP;
             const uint4 *p = reinterpret_cast<const uint4 *>(gb) + lane;
@@ -285,6 +345,8 @@ extern "C" int fb_launch_matvec(float *out, const uint8_t *shard, fb_shard_geom_
     const size_t sm = (size_t)g.bpr_local * sizeof(fb_q8_entry_t);
     if (g.type == FB_TYPE_Q4_K)
         k_matvec<FB_TYPE_Q4_K><<<grid, 256, sm, (cudaStream_t)stream>>>(out, shard, g, q8);
+    else if (g.type == FB_TYPE_Q5_K)
+        k_matvec<FB_TYPE_Q5_K><<<grid, 256, sm, (cudaStream_t)stream>>>(out, shard, g, q8);
     else
         k_matvec<FB_TYPE_Q6_K><<<grid, 256, sm, (cudaStream_t)stream>>>(out, shard, g, q8);
     return (int)cudaGetLastError();
@@ -327,7 +389,8 @@ extern "C" int fomoe_b200_matvec_noalloc(int type, const void *w_ggml_dev, int r
         return -1;
     }
     const int bpr = cols / FB_QK;
-    if ((type != FB_TYPE_Q4_K && type != FB_TYPE_Q6_K) || (bpr & (bpr - 1)) || bpr > FB_NOALLOC_Q8_ENTRIES) {
+    if ((type != FB_TYPE_Q4_K && type != FB_TYPE_Q5_K && type != FB_TYPE_Q6_K) || (bpr & (bpr - 1)) ||
+        bpr > FB_NOALLOC_Q8_ENTRIES) {
         fprintf(stderr, "fomoe_b200_matvec_noalloc: unsupported type %d or column count %d (a power-of-two number of "
                         "256-column blocks, at most %d columns)\n", type, cols, FB_NOALLOC_Q8_ENTRIES * FB_QK);
         return -1;

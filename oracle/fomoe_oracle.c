@@ -40,6 +40,7 @@ float orc_fp16_to_fp32(uint16_t h) {
 
 uint64_t orc_row_bytes(int type, int k) {
     if (type == ORC_TYPE_Q4_K) return (uint64_t)(k / ORC_QK_K) * sizeof(orc_block_q4_K);
+    if (type == ORC_TYPE_Q5_K) return (uint64_t)(k / ORC_QK_K) * sizeof(orc_block_q5_K);
     if (type == ORC_TYPE_Q6_K) return (uint64_t)(k / ORC_QK_K) * sizeof(orc_block_q6_K);
     return 0;
 }
@@ -75,6 +76,58 @@ void orc_dequantize_row_q4_K(const void *xv, float *y, int64_t k) {
             q += 32;
         }
     }
+}
+
+/* ---- Q5_K dequant : src/quant.c:216-247.  The nibble plus 16 where the fifth bit (qh, bit 2c / 2c+1 for the two
+ * halves of 64-chunk c) is set.  d*sc*q has at most 22 significant bits, so contraction cannot change the result. ---- */
+void orc_dequantize_row_q5_K(const void *xv, float *y, int64_t k) {
+    const orc_block_q5_K *x = (const orc_block_q5_K *)xv;
+    int64_t nb = k / ORC_QK_K;
+    for (int64_t i = 0; i < nb; i++) {
+        float d = orc_fp16_to_fp32(x[i].d);
+        float mn = orc_fp16_to_fp32(x[i].dmin);
+        const uint8_t *q = x[i].qs;
+        const uint8_t *qh = x[i].qh;
+        for (int c = 0; c < 4; c++) {
+            uint8_t sc1, m1, sc2, m2;
+            scale_min_k4(2 * c, x[i].scales, &sc1, &m1);
+            scale_min_k4(2 * c + 1, x[i].scales, &sc2, &m2);
+            float d1 = d * (float)sc1, mm1 = mn * (float)m1;
+            float d2 = d * (float)sc2, mm2 = mn * (float)m2;
+            for (int l = 0; l < 32; l++) y[l] = d1 * (float)((q[l] & 0xF) + (((qh[l] >> (2 * c)) & 1) ? 16 : 0)) - mm1;
+            for (int l = 0; l < 32; l++)
+                y[32 + l] = d2 * (float)((q[l] >> 4) + (((qh[l] >> (2 * c + 1)) & 1) ? 16 : 0)) - mm2;
+            y += 64;
+            q += 32;
+        }
+    }
+}
+
+/* ---- Q5_K x Q8_K : src/quant.c:609-621, a scalar loop in the reference: dequantise the block, then
+ * sum += (tmp[j] * y.d) * q8[j] sequentially, one block sum added to the row sum.  The reference build computes
+ * the products separately (vectorised) and adds them in order, i.e. no fused multiply-add; ORC_Q5_FMA = 0 is that
+ * form and is pinned bit for bit against the compiled reference. ---- */
+#ifndef ORC_Q5_FMA
+#define ORC_Q5_FMA 0
+#endif
+float orc_vec_dot_q5_K_q8_K(const void *xv, const void *yv, int nb) {
+    const orc_block_q5_K *x = (const orc_block_q5_K *)xv;
+    const orc_block_q8_K *y = (const orc_block_q8_K *)yv;
+    float sumf = 0.0f;
+    float tmp[ORC_QK_K];
+    for (int i = 0; i < nb; i++) {
+        orc_dequantize_row_q5_K(&x[i], tmp, ORC_QK_K);
+        float sum = 0.0f;
+        for (int j = 0; j < ORC_QK_K; j++) {
+#if ORC_Q5_FMA
+            sum = fmaf(tmp[j] * y[i].d, (float)y[i].qs[j], sum);
+#else
+            sum = sum + tmp[j] * y[i].d * (float)y[i].qs[j];
+#endif
+        }
+        sumf = sumf + sum;
+    }
+    return sumf;
 }
 
 /* ---- Q6_K dequant : src/quant.c:147-175.  y = (d*sc)*q, left to right. ---- */
@@ -223,6 +276,7 @@ void orc_matvec_q8(float *out, const void *mat, int type, const void *q8, int M,
     const uint8_t *m = (const uint8_t *)mat;
     for (int i = 0; i < M; i++) {
         if (type == ORC_TYPE_Q4_K) out[i] = orc_vec_dot_q4_K_q8_K(m + (uint64_t)i * rb, q8, nb);
+        else if (type == ORC_TYPE_Q5_K) out[i] = orc_vec_dot_q5_K_q8_K(m + (uint64_t)i * rb, q8, nb);
         else out[i] = orc_vec_dot_q6_K_q8_K(m + (uint64_t)i * rb, q8, nb);
     }
 }

@@ -20,6 +20,7 @@ extern "C" {
 
 #define ORC_QK_K 256
 #define ORC_TYPE_Q4_K 12 /* include/quant_types.h:56-64 */
+#define ORC_TYPE_Q5_K 13
 #define ORC_TYPE_Q6_K 14
 
 /* Block layouts, include/quant_types.h:17-41 and include/quant.h:94-98. */
@@ -28,6 +29,13 @@ typedef struct {
     uint8_t scales[12];
     uint8_t qs[128];
 } orc_block_q4_K; /* 144 B */
+
+typedef struct {
+    uint16_t d, dmin;
+    uint8_t scales[12];
+    uint8_t qh[32];
+    uint8_t qs[128];
+} orc_block_q5_K; /* 176 B */
 
 #pragma pack(push, 1)
 typedef struct {
@@ -46,9 +54,11 @@ typedef struct {
 
 float orc_fp16_to_fp32(uint16_t h);                                        /* src/quant.c:30-47 */
 void orc_dequantize_row_q4_K(const void *x, float *y, int64_t k);          /* src/quant.c:82-105 */
+void orc_dequantize_row_q5_K(const void *x, float *y, int64_t k);          /* src/quant.c:216-247 */
 void orc_dequantize_row_q6_K(const void *x, float *y, int64_t k);          /* src/quant.c:147-175 */
 void orc_quantize_row_q8_K(const float *x, void *y, int64_t k);            /* src/quant.c:343-375 */
 float orc_vec_dot_q4_K_q8_K(const void *x, const void *y, int nb);         /* src/quant.c:405-476 */
+float orc_vec_dot_q5_K_q8_K(const void *x, const void *y, int nb);         /* src/quant.c:609-621 */
 float orc_vec_dot_q6_K_q8_K(const void *x, const void *y, int nb);         /* src/quant.c:478-607 */
 uint64_t orc_row_bytes(int type, int k);                                   /* include/quant_types.h:93-97 */
 

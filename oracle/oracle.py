@@ -19,9 +19,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(_HERE, "libfomoe_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libfomoe_ref.so")
 
-TYPE_F32, TYPE_Q4_K, TYPE_Q6_K = 0, 12, 14
+TYPE_F32, TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K = 0, 12, 13, 14
 QK_K = 256
-Q4K_BLOCK, Q6K_BLOCK, Q8K_BLOCK = 144, 210, 292
+Q4K_BLOCK, Q5K_BLOCK, Q6K_BLOCK, Q8K_BLOCK = 144, 176, 210, 292
 
 _f32p = C.POINTER(C.c_float)
 _i32p = C.POINTER(C.c_int)
@@ -37,7 +37,7 @@ def build(force=False):
 
 
 def row_bytes(qtype, k):
-    return (k // QK_K) * {TYPE_Q4_K: Q4K_BLOCK, TYPE_Q6_K: Q6K_BLOCK}[qtype]
+    return (k // QK_K) * {TYPE_Q4_K: Q4K_BLOCK, TYPE_Q5_K: Q5K_BLOCK, TYPE_Q6_K: Q6K_BLOCK}[qtype]
 
 
 def _fp(a):
@@ -68,6 +68,10 @@ class _Common:
         g("dq4").restype = None
         g("dq6").argtypes = [C.c_void_p, _f32p, C.c_int64]
         g("dq6").restype = None
+        g("dq5").argtypes = [C.c_void_p, _f32p, C.c_int64]
+        g("dq5").restype = None
+        g("dot5").argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        g("dot5").restype = C.c_float
         g("q8").argtypes = [_f32p, C.c_void_p, C.c_int64]
         g("q8").restype = None
         g("dot4").argtypes = [C.c_void_p, C.c_void_p, C.c_int]
@@ -100,7 +104,7 @@ class _Common:
         b = _u8(blocks)
         assert b.size == row_bytes(qtype, k)
         y = np.empty(k, dtype=np.float32)
-        self._f("dq4" if qtype == TYPE_Q4_K else "dq6")(_vp(b), _fp(y), k)
+        self._f({TYPE_Q4_K: "dq4", TYPE_Q5_K: "dq5", TYPE_Q6_K: "dq6"}[qtype])(_vp(b), _fp(y), k)
         return y
 
     def quantize_q8k(self, x):
@@ -113,7 +117,7 @@ class _Common:
     def vec_dot(self, row_blocks, qtype, q8, nb):
         b = _u8(row_blocks)
         q = _u8(q8)
-        return np.float32(self._f("dot4" if qtype == TYPE_Q4_K else "dot6")(_vp(b), _vp(q), nb))
+        return np.float32(self._f({TYPE_Q4_K: "dot4", TYPE_Q5_K: "dot5", TYPE_Q6_K: "dot6"}[qtype])(_vp(b), _vp(q), nb))
 
     def matvec_q8(self, mat, qtype, x, M, K):
         """out[M] = mat[M x K] (quantised rows) . Q8_K(x)."""
@@ -176,6 +180,7 @@ class Oracle(_Common):
         build()
         lib = C.CDLL(ORACLE_SO)
         super().__init__(lib, dict(dq4="orc_dequantize_row_q4_K", dq6="orc_dequantize_row_q6_K",
+                                   dq5="orc_dequantize_row_q5_K", dot5="orc_vec_dot_q5_K_q8_K",
                                    q8="orc_quantize_row_q8_K", dot4="orc_vec_dot_q4_K_q8_K",
                                    dot6="orc_vec_dot_q6_K_q8_K", fp16="orc_fp16_to_fp32",
                                    softmax="orc_softmax", topk="orc_top_k", rms="orc_rms_norm",
@@ -224,6 +229,7 @@ class Ref(_Common):
         build()
         lib = C.CDLL(REF_SO)
         super().__init__(lib, dict(dq4="dequantize_row_q4_K", dq6="dequantize_row_q6_K",
+                                   dq5="dequantize_row_q5_K", dot5="vec_dot_q5_K_q8_K",
                                    q8="quantize_row_q8_K", dot4="vec_dot_q4_K_q8_K",
                                    dot6="vec_dot_q6_K_q8_K", fp16="fp16_to_fp32", softmax="softmax",
                                    topk="top_k", rms="rms_norm", route="refdrv_route",

@@ -1,7 +1,7 @@
 """Shared builders for the parity tests: seeded synthetic experts and comparison metrics."""
 import numpy as np
 
-Q4, Q6 = 12, 14
+Q4, Q5, Q6 = 12, 13, 14
 
 
 def rel_l2(a, b):

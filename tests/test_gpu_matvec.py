@@ -30,15 +30,20 @@ def test_quantize_q8k_bit_exact(fb, dec, oracle, n):
 
 
 @pytest.mark.parametrize("qtype,rows,cols", [(H.Q4, 1024, 4096), (H.Q6, 4096, 1024), (H.Q4, 4096, 1024),
-                                             (H.Q4, 64, 256), (H.Q6, 40, 512), (H.Q6, 8, 8192), (H.Q4, 3, 2048)])
+                                             (H.Q4, 64, 256), (H.Q6, 40, 512), (H.Q6, 8, 8192), (H.Q4, 3, 2048),
+                                             (H.Q5, 4096, 1024), (H.Q5, 24, 512)])
 def test_matvec_vs_oracle(fb, dec, oracle, qtype, rows, cols):
     w = fb.synth_matrix(9, 0, 1, fb.M_GATE, qtype, rows, cols)
     x = H.hidden(fb, 9, rows, cols)
     got = dec.matvec(qtype, w, rows, cols, x)
     want = oracle.matvec_q8(w, qtype, x, rows, cols)
-    assert H.rel_l2(got, want) < TOL
+    # Q4_K / Q6_K: both sides form exact integer block sums, only the fp32 sum over blocks is reassociated.
+    # Q5_K: the reference adds 256 rounded fp32 products per block (src/quant.c:609-621), the device sums exact
+    # integers, so the two differ by the reference's own rounding noise.
+    tol, peak = (TOL, 1e-5) if qtype != H.Q5 else (3e-5, 1e-4)
+    assert H.rel_l2(got, want) < tol
     scale = np.abs(want).max()
-    assert np.abs(got - want).max() <= 1e-5 * scale
+    assert np.abs(got - want).max() <= peak * scale
 
 
 def test_matvec_reference_patterns(fb, dec, oracle):

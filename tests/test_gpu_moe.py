@@ -15,7 +15,7 @@ OUT_TOL = 1e-3       # the stated bar
 OUT_EXPECT = 3e-4
 
 
-@pytest.mark.parametrize("down_type", [H.Q6, H.Q4])
+@pytest.mark.parametrize("down_type", [H.Q6, H.Q4, H.Q5])
 def test_config0_layer_full_shape(fb, oracle, down_type):
     """One routed-MoE block at the 397B shape: hidden 4096, 512 experts top-10 + shared, intermediate 1024."""
     seed = 101
@@ -50,7 +50,8 @@ def test_config0_layer_vs_compiled_reference(fb, ref):
 
 @pytest.mark.parametrize("n_embd,inter,n_experts,top_k,shared,down_type",
                          [(256, 256, 4, 1, False, H.Q4), (512, 256, 8, 2, True, H.Q6), (1024, 2048, 16, 4, True, H.Q6),
-                          (8192, 512, 16, 3, False, H.Q4), (2048, 512, 32, 15, True, H.Q6)])
+                          (8192, 512, 16, 3, False, H.Q4), (2048, 512, 32, 15, True, H.Q6),
+                          (1024, 1024, 16, 4, True, H.Q5)])
 def test_layer_shapes(fb, oracle, n_embd, inter, n_experts, top_k, shared, down_type):
     seed = 7 + n_embd
     d = fb.MoeDecoder(1, n_embd, inter, n_experts, top_k, shared, [down_type])
@@ -155,7 +156,7 @@ def test_stack_teacher_forced_and_free_running(fb, oracle):
     (teacher forcing: ids bit-exact, output within tolerance), then the free-running stack, the
     CUDA-graph token path and the plain-launch path are compared."""
     n_layers, n_embd, inter, n_experts, top_k, seed, eps = 4, 1024, 512, 64, 4, 77, 1e-6
-    dts = [H.Q6, H.Q4, H.Q6, H.Q4]
+    dts = [H.Q6, H.Q4, H.Q5, H.Q4]
     d = fb.MoeDecoder(n_layers, n_embd, inter, n_experts, top_k, True, dts, rms_eps=eps, max_tokens=4)
     d.generate(seed)
     toks = np.stack([H.hidden(fb, seed, t, n_embd) for t in range(4)])

@@ -12,7 +12,7 @@ def _experts(fb, seed, n, down_type, n_embd, inter):
     return [H.expert_record(fb, seed, 0, e, down_type, n_embd, inter) for e in range(n)]
 
 
-@pytest.mark.parametrize("down_type,n", [(H.Q6, 10), (H.Q4, 8), (H.Q6, 1)])
+@pytest.mark.parametrize("down_type,n", [(H.Q6, 10), (H.Q4, 8), (H.Q6, 1), (H.Q5, 6)])
 def test_gpu_expert_ffn_matches_cpu_expert(fb, oracle, down_type, n):
     n_embd, inter, seed = 4096, 1024, 61
     op = fb.GpuOperator()

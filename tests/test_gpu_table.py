@@ -1,5 +1,5 @@
 """Expert table: device generator == host generator, repack round trip, bit-exact dequant
-(reference src/quant.c:82-105, 147-175), tensor-parallel shard geometry."""
+(reference src/quant.c:82-105, 147-175, 216-247), tensor-parallel shard geometry."""
 import numpy as np
 import pytest
 
@@ -10,13 +10,13 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope="module")
 def small(fb):
-    d = fb.MoeDecoder(2, 512, 512, 8, 2, True, [H.Q6, H.Q4])
+    d = fb.MoeDecoder(3, 512, 512, 8, 2, True, [H.Q6, H.Q4, H.Q5])
     d.generate(11)
     yield d
     d.close()
 
 
-@pytest.mark.parametrize("layer", [0, 1])
+@pytest.mark.parametrize("layer", [0, 1, 2])
 @pytest.mark.parametrize("expert", [0, 5, 8])
 def test_generated_bytes_match_host_generator(fb, small, layer, expert):
     dt = small.down_types[layer]
@@ -27,7 +27,7 @@ def test_generated_bytes_match_host_generator(fb, small, layer, expert):
         assert (dev == host).all()
 
 
-@pytest.mark.parametrize("layer", [0, 1])
+@pytest.mark.parametrize("layer", [0, 1, 2])
 def test_dequant_bit_exact(fb, small, oracle, layer):
     dt = small.down_types[layer]
     for m, t in ((fb.M_GATE, H.Q4), (fb.M_DOWN, dt)):
@@ -41,7 +41,7 @@ def test_dequant_bit_exact(fb, small, oracle, layer):
 
 def test_upload_repack_round_trip(fb, small):
     rng = np.random.default_rng(5)
-    for layer in (0, 1):
+    for layer in (0, 1, 2):
         rec = rng.integers(0, 256, small.record_bytes(layer), dtype=np.uint8)
         small.upload_expert(layer, 2, rec)
         gb = fb.matrix_bytes(H.Q4, 512, 512)

@@ -30,6 +30,10 @@ def test_dequant_q8k_dots_golden(fb, oracle):
     assert (oracle.quantize_q8k(x1) == GOLD["q8_1024"]).all()
     assert (H.bits(oracle.matvec_q8(q4, H.Q4, x4, 8, 4096)) == H.bits(GOLD["dot4"])).all()
     assert (H.bits(oracle.matvec_q8(q6, H.Q6, x1, 8, 1024)) == H.bits(GOLD["dot6"])).all()
+    q5 = fb.synth_matrix(seed, 0, 1, fb.M_DOWN, H.Q5, 8, 1024)
+    for r in range(8):
+        assert (H.bits(oracle.dequantize(q5[r * 704:(r + 1) * 704], H.Q5, 1024)) == H.bits(GOLD["dq5"][r])).all()
+    assert (H.bits(oracle.matvec_q8(q5, H.Q5, x1, 8, 1024)) == H.bits(GOLD["dot5"])).all()
 
 
 def test_reference_matvec_pattern_dequant(oracle):
@@ -61,7 +65,7 @@ def test_topk_tie_order(oracle):
     assert list(ids) == list(GOLD["topk_tie_ids"]) == [1, 2, 4, 3]
 
 
-@pytest.mark.parametrize("tag,down_type", [("q6", H.Q6), ("q4", H.Q4)])
+@pytest.mark.parametrize("tag,down_type", [("q6", H.Q6), ("q4", H.Q4), ("q5", H.Q5)])
 def test_config0_layer_golden(fb, oracle, tag, down_type):
     seed = 2024
     h = H.hidden(fb, seed, 0, 4096)
@@ -99,7 +103,8 @@ def test_stack_golden(fb, oracle):
 # ---- direct comparison with the compiled reference (skipped where it was not built) ----
 def test_oracle_equals_compiled_reference(fb, oracle, ref):
     rng = np.random.default_rng(3)
-    for qt, m, rows, cols in ((H.Q4, fb.M_GATE, 6, 4096), (H.Q6, fb.M_DOWN, 6, 1024), (H.Q4, fb.M_DOWN, 6, 1024)):
+    for qt, m, rows, cols in ((H.Q4, fb.M_GATE, 6, 4096), (H.Q6, fb.M_DOWN, 6, 1024), (H.Q4, fb.M_DOWN, 6, 1024),
+                              (H.Q5, fb.M_DOWN, 6, 1024)):
         w = fb.synth_matrix(77, 1, 2, m, qt, rows, cols)
         rb = fb.matrix_bytes(qt, 1, cols)
         x = rng.normal(0, 2, cols).astype(np.float32)
