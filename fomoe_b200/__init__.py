@@ -81,6 +81,7 @@ _SIGS = {
     "fomoe_b200_router_upload": (C.c_int, [C.c_void_p, C.c_int, _f32p]),
     "fomoe_b200_glue_upload": (C.c_int, [C.c_void_p, C.c_int, _f32p, _f32p]),
     "fomoe_b200_set_resident_mask": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "fomoe_b200_shared_gate_upload": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "fomoe_b200_set_car": (C.c_int, [C.c_void_p, C.c_float, C.c_int]),
     "fomoe_b200_moe_layer": (C.c_int, [C.c_void_p, C.c_int, _f32p, _f32p, _i32p, _f32p, _i32p, _f32p]),
     "fomoe_b200_moe_layer_routed": (C.c_int, [C.c_void_p, C.c_int, _f32p, _i32p, _f32p, C.c_int, _f32p]),
@@ -256,6 +257,15 @@ class MoeDecoder:
         w = _f32(normw) if normw is not None else None
         self._ck(self._l.fomoe_b200_glue_upload(self._h, layer, _fp(r) if r is not None else None,
                                                 _fp(w) if w is not None else None), "glue_upload")
+
+    def set_shared_gate(self, layer, w):
+        """w: float32[n_embd] (the shared expert's output is scaled by sigmoid(h . w)) or None (no gate)."""
+        if w is None:
+            self._ck(self._l.fomoe_b200_shared_gate_upload(self._h, layer, None), "shared_gate_upload")
+            return
+        w = _f32(w)
+        assert w.size == self.n_embd
+        self._ck(self._l.fomoe_b200_shared_gate_upload(self._h, layer, w.ctypes.data), "shared_gate_upload")
 
     def set_resident_mask(self, layer, mask):
         if mask is None:

@@ -28,6 +28,7 @@ typedef struct {
     float *router_w, *resid, *normw;
     uint32_t *mask; /* device copy of the residency mask */
     int mask_set;
+    float *shared_gate_w; /* [n_embd] or NULL */
 } fb_layer_t;
 
 struct fomoe_b200_ctx {
@@ -47,6 +48,7 @@ struct fomoe_b200_ctx {
     const uint8_t **slot_rec;
     fb_q8_entry_t *q8h, *q8a;
     unsigned *counters, *tok_ctr;
+    float *shared_gate; /* scalar gate of the shared expert for the layer in flight */
     uint32_t *freq; /* [n_layers][n_experts] or NULL */
     float *tok_in, *tok_out;
     int max_tokens;
@@ -160,13 +162,14 @@ void fomoe_b200_destroy(fomoe_b200_ctx_t *c) {
             cudaFree(c->layers[l].resid);
             cudaFree(c->layers[l].normw);
             cudaFree(c->layers[l].mask);
+            cudaFree(c->layers[l].shared_gate_w);
         }
         free(c->layers);
     }
     cudaFree(c->x); cudaFree(c->h); cudaFree(c->moe_out); cudaFree(c->logits); cudaFree(c->all_scores);
     cudaFree(c->scores); cudaFree(c->act); cudaFree(c->dots); cudaFree(c->ids); cudaFree(c->ids_orig);
     cudaFree(c->status); cudaFree((void *)c->slot_rec); cudaFree(c->q8h); cudaFree(c->q8a);
-    cudaFree(c->counters); cudaFree(c->tok_ctr); cudaFree(c->freq); cudaFree(c->tok_in); cudaFree(c->tok_out);
+    cudaFree(c->counters); cudaFree(c->tok_ctr); cudaFree(c->shared_gate); cudaFree(c->freq); cudaFree(c->tok_in); cudaFree(c->tok_out);
     for (int p = 0; p < FB_MAX_TP; p++)
         if (c->tp_peer[p] && c->tp_peer[p] != c->tp_recv) cudaIpcCloseMemHandle(c->tp_peer[p]);
     cudaFree(c->tp_recv);
@@ -282,6 +285,7 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
         dev_alloc(c, (void **)&c->q8a, sizeof(fb_q8_entry_t) * FB_MAX_SLOTS * (c->inter_local / FB_QK)) ||
         dev_alloc(c, (void **)&c->counters, sizeof(unsigned) * (FB_CNT_WIN + FB_MAX_SLOTS * 32 + c->down_groups)) ||
         dev_alloc(c, (void **)&c->status, sizeof(int)) || dev_alloc(c, (void **)&c->tok_ctr, sizeof(unsigned)) ||
+        dev_alloc(c, (void **)&c->shared_gate, sizeof(float)) ||
         dev_alloc(c, (void **)&c->d_layer_args, sizeof(fb_args_t) * (uint64_t)nl) ||
         dev_alloc(c, (void **)&c->d_bar, 32 * sizeof(unsigned long long)) ||
         dev_alloc(c, (void **)&c->d_ll_dots, sizeof(unsigned long long) * FB_MAX_SLOTS * (uint64_t)ne) || dev_alloc(c, (void **)&c->d_abort, sizeof(int)) ||
@@ -543,6 +547,22 @@ int fomoe_b200_glue_upload(fomoe_b200_ctx_t *c, int layer, const float *resid, c
     return 0;
 }
 
+int fomoe_b200_shared_gate_upload(fomoe_b200_ctx_t *c, int layer, const float *w) {
+    if (!c || layer < 0 || layer >= c->cfg.n_layers || !c->cfg.has_shared) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    drop_graph(c);
+    fb_layer_t *L = &c->layers[layer];
+    if (!w) {
+        if (L->shared_gate_w) cudaFree(L->shared_gate_w);
+        L->shared_gate_w = NULL;
+        return 0;
+    }
+    if (!L->shared_gate_w && dev_alloc(c, (void **)&L->shared_gate_w, sizeof(float) * c->cfg.n_embd)) return -1;
+    CK(c, cudaMemcpyAsync(L->shared_gate_w, w, sizeof(float) * c->cfg.n_embd, cudaMemcpyHostToDevice, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
 int fomoe_b200_set_resident_mask(fomoe_b200_ctx_t *c, int layer, const uint32_t *mask) {
     if (!c || layer < 0 || layer >= c->cfg.n_layers) return -1;
     CK(c, cudaSetDevice(c->cfg.device));
@@ -592,6 +612,8 @@ static void fill_args(const fomoe_b200_ctx_t *c, int layer, fb_args_t *a) {
     a->resid = L->resid;
     a->normw = L->normw;
     a->resident = L->mask_set ? L->mask : NULL;
+    a->shared_gate_w = c->cfg.has_shared ? L->shared_gate_w : NULL;
+    a->shared_gate = c->shared_gate;
     a->freq = c->freq ? c->freq + (size_t)layer * c->cfg.n_experts : NULL;
     a->x = c->x;
     a->h = c->h;

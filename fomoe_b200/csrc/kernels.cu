@@ -82,6 +82,20 @@ __global__ void __launch_bounds__(1024) k_prologue(fb_args_t A, int flags) {
     } else {
         for (int i = tid; i < n; i += blockDim.x) A.h[i] = A.x[i];
     }
+    if (A.shared_gate_w) {
+        /* scalar gate of the shared expert: sigmoid(h . w) (src/inference.c:586-592) */
+        __syncthreads();
+        float p = 0.0f;
+        for (int i = tid; i < n; i += blockDim.x) p = __fmaf_rn(A.h[i], A.shared_gate_w[i], p);
+        for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(FULL, p, o);
+        if (lane == 0) red[warp] = p;
+        __syncthreads();
+        if (warp == 0) {
+            float t = (lane < (int)(blockDim.x >> 5)) ? red[lane] : 0.0f;
+            for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(FULL, t, o);
+            if (lane == 0) *A.shared_gate = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-t)));
+        }
+    }
     if (flags & FB_PRO_QUANT) {
         __syncthreads();
         for (int b = warp; b < n / FB_QK; b += (blockDim.x >> 5)) {
@@ -278,7 +292,10 @@ __global__ void __launch_bounds__(256) k_down(fb_args_t A) {
                 float acc = A.accumulate ? A.moe_out[r] : 0.0f;
                 for (int s = 0; s < A.top_k; s++)
                     acc = __fmaf_rn(__ldcg(A.scores + s), __ldcg(A.dots + s * A.n_embd + r), acc);
-                if (A.has_shared) acc = __fadd_rn(acc, __ldcg(A.dots + A.top_k * A.n_embd + r));
+                if (A.has_shared) {
+                    const float sh = __ldcg(A.dots + A.top_k * A.n_embd + r);
+                    acc = __fadd_rn(acc, A.shared_gate_w ? __fmul_rn(sh, __ldcg(A.scores + A.top_k)) : sh);
+                }
                 A.moe_out[r] = acc;
             }
             if (lane == 0) cnt_rg[rg] = 0;
@@ -482,7 +499,10 @@ __global__ void __launch_bounds__(512, 1) k_down_ring(fb_args_t A) {
             if (lane < rpg && r < A.n_embd) {
                 float acc = A.accumulate ? A.moe_out[r] : 0.0f;
                 for (int s = 0; s < A.top_k; s++) acc = __fmaf_rn(A.scores[s], dots[(buf * ns + s) * 32 + lane], acc);
-                if (A.has_shared) acc = __fadd_rn(acc, dots[(buf * ns + A.top_k) * 32 + lane]);
+                if (A.has_shared) {
+                    const float sh = dots[(buf * ns + A.top_k) * 32 + lane];
+                    acc = __fadd_rn(acc, A.shared_gate_w ? __fmul_rn(sh, __ldcg(A.scores + A.top_k)) : sh);
+                }
                 A.moe_out[r] = acc;
             }
             __syncwarp();

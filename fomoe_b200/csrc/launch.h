@@ -51,6 +51,8 @@ typedef struct {
     const float *router_w;    /* [n_experts][n_embd] */
     const float *resid;       /* [n_embd] or NULL */
     const float *normw;       /* [n_embd] or NULL */
+    const float *shared_gate_w; /* [n_embd] or NULL: the shared expert's output is scaled by sigmoid(h . w) */
+    float *shared_gate;         /* that scalar, written by the prologue kernel (per-phase path) */
     const uint32_t *resident; /* [16] residency bit mask or NULL */
     uint32_t *freq;           /* [n_experts] selection histogram for this layer or NULL */
     /* state */

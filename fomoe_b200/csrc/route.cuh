@@ -247,7 +247,7 @@ static __device__ void fb_route_select(const fb_args_t &A, int lane, bool leader
         }
         if (A.has_shared) {
             A.ids[k] = nE;
-            A.scores[k] = 1.0f;
+            A.scores[k] = A.shared_gate_w ? __ldcg(A.shared_gate) : 1.0f; /* weight 1, or its scalar gate */
             A.slot_rec[k] = A.table_layer + (uint64_t)nE * A.rec_bytes;
         }
         if (leader && n_subs) atomicAdd(A.counters + FB_CNT_SUBS, (unsigned)n_subs);

@@ -55,9 +55,11 @@ __device__ __forceinline__ void fb_sort32(float &v, int &i, int lane) {
 }
 
 /* Must be called by all 512 threads of the block.  Outputs (shared memory): ids[n_slots], scores[n_slots],
- * ids_orig[top_k], slot_rec[n_slots], all_scores[n_experts].  `leader` updates the global counters. */
+ * ids_orig[top_k], slot_rec[n_slots], all_scores[n_experts].  `leader` updates the global counters;
+ * `shared_score` is the weight of the shared expert's slot. */
 __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const float *h_smem, float *all_scores, int *ids,
-                                int *ids_orig, float *scores, const uint8_t **slot_rec, bool leader) {
+                                int *ids_orig, float *scores, const uint8_t **slot_rec, bool leader,
+                                float shared_score = 1.0f) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nE = A.n_experts, k = A.top_k, kk = min(k + 1, nE);
     float lg = (tid < nE) ? __ldcg(A.logits + tid) : -INFINITY;
@@ -276,7 +278,7 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
         if (lane == 0) {
             if (A.has_shared) {
                 ids[k] = nE;
-                scores[k] = 1.0f;
+                scores[k] = shared_score; /* 1, or the shared expert's scalar gate */
                 slot_rec[k] = A.table_layer + (uint64_t)nE * A.rec_bytes;
             }
             if (leader && n_subs) atomicAdd(A.counters + FB_CNT_SUBS, (unsigned)n_subs);

@@ -51,7 +51,8 @@ struct sk_smem_t {
     fb_q8_entry_t q8h[16];               /* quantised hidden state */
     fb_q8_entry_t q8a[SK_MAX_Q8A];       /* quantised activations of every slot */
     float dots[SK_MAX_RG][SK_DN_SLOTS][32]; /* per-expert down outputs of this block's row groups */
-    float red[4][SK_WARPS];
+    float red[5][SK_WARPS];             /* four router rows and the shared expert's gate vector */
+    float shared_gate;
     float all_scores[FB_MAX_EXPERTS];
     fb_sel_smem_t sel;
     int ids[FB_MAX_SLOTS], ids_orig[FB_MAX_SLOTS];
@@ -353,6 +354,17 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(FULL, p, o);
                 if (lane == 0) S->red[j][warp] = p;
             }
+            if (A.shared_gate_w) { /* scalar gate of the shared expert: sigmoid(h . w) (src/inference.c:586-592) */
+                float p = 0.0f;
+                if (own) {
+                    const float4 *q = reinterpret_cast<const float4 *>(A.shared_gate_w + e0);
+                    const float4 a0 = __ldg(q), a1 = __ldg(q + 1);
+                    p = fmaf(a0.x, h[0], p); p = fmaf(a0.y, h[1], p); p = fmaf(a0.z, h[2], p); p = fmaf(a0.w, h[3], p);
+                    p = fmaf(a1.x, h[4], p); p = fmaf(a1.y, h[5], p); p = fmaf(a1.z, h[6], p); p = fmaf(a1.w, h[7], p);
+                }
+                for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(FULL, p, o);
+                if (lane == 0) S->red[4][warp] = p;
+            }
             __syncthreads();
             if (tid < 4) {
                 const int row = cta + tid * G;
@@ -361,6 +373,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     for (int w = 0; w < SK_WARPS; w++) t += S->red[tid][w];
                     A.logits[row] = t;
                 }
+            } else if (tid == 32) {
+                float t = 0.0f;
+                if (A.shared_gate_w)
+                    for (int w = 0; w < SK_WARPS; w++) t += S->red[4][w];
+                S->shared_gate = A.shared_gate_w ? __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-t))) : 1.0f;
             }
             for (int row = cta + 4 * G; row < A.n_experts; row += G) { /* more than 4 rows per block: rare shapes */
                 float p = 0.0f;
@@ -387,7 +404,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             SK_STAMP(4);
 
             /* ---- SEL: routing, redundantly in every block (results identical by construction) */
-            fb_block_select(A, &S->sel, h_sm, S->all_scores, S->ids, S->ids_orig, S->scores, S->slot_rec, leader);
+            fb_block_select(A, &S->sel, h_sm, S->all_scores, S->ids, S->ids_orig, S->scores, S->slot_rec, leader,
+                            S->shared_gate);
             if (leader) {
                 if (tid < A.n_slots) {
                     A.ids[tid] = S->ids[tid];
@@ -617,7 +635,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 if (row_ok) {
                     float acc = 0.0f;
                     for (int s = 0; s < A.top_k; s++) acc = __fmaf_rn(S->scores[s], S->dots[q][s][lane], acc);
-                    if (A.has_shared) acc = __fadd_rn(acc, S->dots[q][A.top_k][lane]);
+                    if (A.has_shared) {
+                        const float sh = S->dots[q][A.top_k][lane];
+                        acc = __fadd_rn(acc, A.shared_gate_w ? __fmul_rn(sh, S->scores[A.top_k]) : sh);
+                    }
                     if (TP) {
                         /* fused all-reduce, sending side: the partial goes straight into slot tp_rank of every
                          * rank's receive buffer over NVLink (plain peer stores of {generation, value} words) */

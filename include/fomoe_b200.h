@@ -129,6 +129,10 @@ uint64_t fomoe_b200_table_bytes(fomoe_b200_ctx_t *ctx);
 int fomoe_b200_table_generate(fomoe_b200_ctx_t *ctx, uint64_t seed);
 /* Upload one expert record in ggml order (expert == n_experts addresses the shared expert). */
 int fomoe_b200_table_upload(fomoe_b200_ctx_t *ctx, int layer, int expert, const void *record);
+/* Optional scalar gate of the shared expert (src/inference.c:586-592, include/model.h shared_expert_gate): with a
+ * vector w[n_embd] uploaded, the shared expert's output is multiplied by sigmoid(h . w) before it is added to the
+ * routed sum; NULL removes the gate again (the default: weight 1). */
+int fomoe_b200_shared_gate_upload(fomoe_b200_ctx_t *ctx, int layer, const float *w);
 /* Read this rank's shard of one matrix (0 gate, 1 up, 2 down) back in ggml order / as fp32. */
 int fomoe_b200_table_export(fomoe_b200_ctx_t *ctx, int layer, int expert, int matrix, void *ggml_out);
 int fomoe_b200_table_dequant(fomoe_b200_ctx_t *ctx, int layer, int expert, int matrix, float *out);
@@ -202,7 +206,7 @@ int fomoe_b200_matvec(fomoe_b200_ctx_t *ctx, int type, const void *w_ggml, int r
 /* y[rows] = W[rows x cols] . Q8_K(x) with NO allocation of any kind.  (No counterpart in the reference: added for
  * callers that cannot call cudaMalloc while they run, such as a serving loop whose device memory was all handed out
  * at start-up or a latency-critical path that must not take cudaMalloc's device synchronisation.)
- * w_ggml_dev (ggml-ordered blocks, type Q4_K or Q6_K), x_dev and y_dev are DEVICE pointers supplied by the caller;
+ * w_ggml_dev (ggml-ordered blocks, type Q4_K, Q5_K or Q6_K), x_dev and y_dev are DEVICE pointers supplied by the caller;
  * the kernels are enqueued on `stream` (a cudaStream_t, NULL = default stream) of the current device and the call
  * does not synchronise.  The two temporaries fomoe_b200_matvec allocates per call live in a fixed array inside the
  * library instead, which limits the matrix to 4 MiB of quantised weights (e.g. 1024 x 4096 Q4_K, 4096 x 1024 Q6_K)

@@ -324,6 +324,14 @@ void orc_router_logits(float *logits, const float *w, const float *h, int n_expe
     }
 }
 
+/* ---- scalar gate of the shared expert: src/inference.c:586-590.  (inference.c is not among the reference files
+ * that compile on their own, so this one function is checked by reading, not against the compiled reference.) ---- */
+float orc_shared_gate(const float *h, const float *w, int n_embd) {
+    float dot = 0.0f;
+    for (int i = 0; i < n_embd; i++) dot = dot + h[i] * w[i];
+    return 1.0f / (1.0f + expf(-dot));
+}
+
 void orc_softmax(float *x, int64_t n) {
     float mx = x[0];
     for (int64_t i = 1; i < n; i++)

@@ -78,6 +78,7 @@ void orc_router_logits(float *logits, const float *w, const float *h, int n_expe
 void orc_softmax(float *x, int64_t n);
 void orc_top_k(const float *x, int64_t n, int k, int *indices, float *values); /* src/tensor.c:226-252 */
 void orc_renorm(float *scores, int k);                                        /* src/inference.c:496-502 */
+float orc_shared_gate(const float *h, const float *w, int n_embd);               /* src/inference.c:586-590 */
 void orc_rms_norm(float *out, const float *x, const float *w, int64_t n, float eps); /* src/tensor.c:175-184 */
 
 /* Cache-aware routing over a single residency tier given as a bit mask

@@ -189,9 +189,15 @@ class Oracle(_Common):
         lib.orc_car.restype = C.c_int
         lib.orc_router_logits.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int]
         lib.orc_router_logits.restype = None
+        lib.orc_shared_gate.argtypes = [_f32p, _f32p, C.c_int]
+        lib.orc_shared_gate.restype = C.c_float
         lib.orc_expert_ffn.argtypes = [_f32p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int, C.c_int,
                                        C.c_uint64, C.c_uint64, C.c_int, C.c_int, _f32p]
         lib.orc_expert_ffn.restype = None
+
+    def shared_gate(self, h, w):
+        h, w = _f32(h), _f32(w)
+        return np.float32(self.lib.orc_shared_gate(_fp(h), _fp(w), h.size))
 
     def router_logits(self, w, h):
         w, h = _f32(w), _f32(h)

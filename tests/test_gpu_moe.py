@@ -190,6 +190,40 @@ def test_stack_teacher_forced_and_free_running(fb, oracle):
     d.close()
 
 
+def test_shared_expert_gate(fb, oracle):
+    """Optional scalar gate sigmoid(h . w) on the shared expert (src/inference.c:582-596), per-phase kernels and the
+    persistent stack kernel; removing the gate restores the ungated bits."""
+    n_embd, inter, n_experts, top_k, seed = 2048, 512, 32, 4, 57
+    d = fb.MoeDecoder(2, n_embd, inter, n_experts, top_k, True, [H.Q6, H.Q4], rms_eps=1e-6)
+    d.generate(seed)
+    h = H.hidden(fb, seed, 0, n_embd)
+    plain = d.moe_layer(0, h)["out"]
+    gw = [(0.02 * H.hidden(fb, seed, 100 + l, n_embd)).astype(np.float32) for l in range(2)]
+    for l in range(2):
+        d.set_shared_gate(l, gw[l])
+    got = d.moe_layer(0, h)
+    want = H.oracle_layer(oracle, fb, seed, 0, h, n_embd, inter, n_experts, top_k, H.Q6, shared_gate_w=gw[0])
+    assert 0.05 < want["gate"] < 0.95
+    assert (got["ids"] == want["ids"]).all()
+    assert H.rel_l2(got["out"], want["out"]) < OUT_EXPECT
+    assert H.rel_l2(got["out"], plain) > 1e-2          # the gate matters
+    # the stack kernel, one layer at a time from the oracle's input
+    x = H.hidden(fb, seed, 1, n_embd)
+    for l, dt in enumerate([H.Q6, H.Q4]):
+        r, w = H.glue(fb, seed, l, n_embd)
+        xin = x.copy()
+        x = x + r
+        hh = oracle.rms_norm(x, w, 1e-6)
+        lay = H.oracle_layer(oracle, fb, seed, l, hh, n_embd, inter, n_experts, top_k, dt, shared_gate_w=gw[l])
+        x = x + lay["out"]
+        got = d.stack_run(xin, l, l + 1)
+        assert H.rel_l2(got, x) < 1e-5
+    d.set_shared_gate(0, None)
+    assert (H.bits(d.moe_layer(0, h)["out"]) == H.bits(plain)).all()
+    assert d.status() == 0
+    d.close()
+
+
 def test_stack_with_car(fb, oracle):
     """Config-3 style: CAR 0.35 with dampening over seeded Zipf residency masks, teacher forced."""
     n_layers, n_embd, inter, n_experts, top_k, seed, eps = 3, 1024, 256, 128, 6, 91, 1e-6

@@ -54,5 +54,5 @@ def test_noalloc_refuses_what_does_not_fit(fb):
     # 4096 x 4096 Q4_K = 9.4 MB of weights: beyond the 4 MiB array
     assert lib.fomoe_b200_matvec_noalloc(H.Q4, _dev(d), 4096, 4096, _dev(d), _dev(d), None) == -1
     assert lib.fomoe_b200_matvec_noalloc(H.Q4, _dev(d), 4, 16384, _dev(d), _dev(d), None) == -1   # > 8192 columns
-    assert lib.fomoe_b200_matvec_noalloc(13, _dev(d), 4, 256, _dev(d), _dev(d), None) == -1       # Q5_K
+    assert lib.fomoe_b200_matvec_noalloc(8, _dev(d), 4, 256, _dev(d), _dev(d), None) == -1        # Q8_0: not a type it takes
     assert lib.fomoe_b200_matvec_noalloc(H.Q4, None, 4, 256, _dev(d), _dev(d), None) == -1
