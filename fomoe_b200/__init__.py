@@ -82,6 +82,7 @@ _SIGS = {
     "fomoe_b200_glue_upload": (C.c_int, [C.c_void_p, C.c_int, _f32p, _f32p]),
     "fomoe_b200_set_resident_mask": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "fomoe_b200_shared_gate_upload": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "fomoe_b200_table_load_qmoe": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
     "fomoe_b200_set_car": (C.c_int, [C.c_void_p, C.c_float, C.c_int]),
     "fomoe_b200_moe_layer": (C.c_int, [C.c_void_p, C.c_int, _f32p, _f32p, _i32p, _f32p, _i32p, _f32p]),
     "fomoe_b200_moe_layer_routed": (C.c_int, [C.c_void_p, C.c_int, _f32p, _i32p, _f32p, C.c_int, _f32p]),
@@ -257,6 +258,12 @@ class MoeDecoder:
         w = _f32(normw) if normw is not None else None
         self._ck(self._l.fomoe_b200_glue_upload(self._h, layer, _fp(r) if r is not None else None,
                                                 _fp(w) if w is not None else None), "glue_upload")
+
+    def load_qmoe(self, path, first_store_layer=0):
+        """Fill the routed experts from an expert store file of the reference; returns the number loaded."""
+        n = self._l.fomoe_b200_table_load_qmoe(self._h, path.encode(), first_store_layer)
+        self._ck(0 if n >= 0 else -1, "table_load_qmoe")
+        return n
 
     def set_shared_gate(self, layer, w):
         """w: float32[n_embd] (the shared expert's output is scaled by sigmoid(h . w)) or None (no gate)."""

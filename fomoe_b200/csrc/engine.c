@@ -8,11 +8,14 @@
  * layer to classify and run car_evaluate (src/gpu_kernels.hip:6984, 7097-7187); here the
  * whole table is resident and routing stays on the device, so a token is one CUDA graph.
  */
+#define _POSIX_C_SOURCE 200809L /* fseeko */
+#define _FILE_OFFSET_BITS 64
 #include <cuda_runtime_api.h>
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/types.h>
 
 #include "../../include/fomoe_b200.h"
 #include "launch.h"
@@ -481,6 +484,77 @@ int fomoe_b200_table_upload(fomoe_b200_ctx_t *c, int layer, int expert, const vo
     if (upload_record(c, layer, expert, record)) return -1;
     CK(c, cudaStreamSynchronize(c->stream)); /* the staging buffer is reused by the next call */
     return 0;
+}
+
+/* ---- expert store files of the reference (".qmoe", include/expert_store.h:9-40): a 64-byte header, a table of
+ * 32-byte layer entries, then for each layer its experts at data_offset + e * stride, each expert gate | up | down in
+ * ggml order (tools/prepare_experts.c:262-291).  The routed experts of store layers first_store_layer ..
+ * first_store_layer + n_layers - 1 are read and repacked into the table; the shared expert is not part of such a
+ * file.  Returns the number of experts loaded, or -1. */
+typedef struct {
+    uint32_t magic, version, n_moe_layers, n_experts, quant_type, alignment;
+    uint64_t gate_size, up_size, down_size, stride;
+} qmoe_head_t;
+typedef struct {
+    uint64_t data_offset, stride, down_size;
+    uint32_t down_type, pad;
+} qmoe_layer_t;
+
+int fomoe_b200_table_load_qmoe(fomoe_b200_ctx_t *c, const char *path, int first_store_layer) {
+    if (!c || !path || first_store_layer < 0) return -1;
+    FILE *f = fopen(path, "rb");
+    if (!f) {
+        set_err(c, "cannot open expert store %s", path);
+        return -1;
+    }
+    int rc = -1, loaded = 0;
+    uint8_t *buf = NULL;
+    qmoe_layer_t *idx = NULL;
+    qmoe_head_t hd;
+    if (fread(&hd, sizeof(hd), 1, f) != 1 || hd.magic != 0x454F4D51u || hd.version < 2) {
+        set_err(c, "%s: not an expert store of version >= 2", path);
+        goto done;
+    }
+    const uint64_t gb = ggml_matrix_bytes(c->cfg.gate_type, c->cfg.n_inter, c->cfg.n_embd);
+    if ((int)hd.n_experts != c->cfg.n_experts || hd.gate_size != gb || hd.up_size != gb ||
+        (uint64_t)first_store_layer + (uint64_t)c->cfg.n_layers > hd.n_moe_layers) {
+        set_err(c, "%s: %u layers of %u experts, gate/up %llu/%llu bytes do not match the table (%d layers from %d, %d "
+                   "experts, %llu bytes)", path, hd.n_moe_layers, hd.n_experts, (unsigned long long)hd.gate_size,
+                (unsigned long long)hd.up_size, c->cfg.n_layers, first_store_layer, c->cfg.n_experts,
+                (unsigned long long)gb);
+        goto done;
+    }
+    idx = (qmoe_layer_t *)malloc(sizeof(qmoe_layer_t) * hd.n_moe_layers);
+    if (!idx || fseek(f, 64, SEEK_SET) || fread(idx, sizeof(qmoe_layer_t), hd.n_moe_layers, f) != hd.n_moe_layers) {
+        set_err(c, "%s: layer index unreadable", path);
+        goto done;
+    }
+    for (int l = 0; l < c->cfg.n_layers; l++) {
+        const qmoe_layer_t *e = &idx[first_store_layer + l];
+        const uint64_t stride = e->stride ? e->stride : hd.stride, rb = fomoe_b200_record_bytes(c, l);
+        if ((int)e->down_type != c->down_types[l] || e->down_size != rb - 2 * gb || stride < rb) {
+            set_err(c, "%s: store layer %d has down type %u / %llu bytes, the table expects type %d / %llu bytes", path,
+                    first_store_layer + l, e->down_type, (unsigned long long)e->down_size, c->down_types[l],
+                    (unsigned long long)(rb - 2 * gb));
+            goto done;
+        }
+        if (!buf) buf = (uint8_t *)malloc(c->stage_bytes);
+        if (!buf) goto done;
+        for (int x = 0; x < c->cfg.n_experts; x++) {
+            if (fseeko(f, (off_t)(e->data_offset + (uint64_t)x * stride), SEEK_SET) || fread(buf, 1, rb, f) != rb) {
+                set_err(c, "%s: short read at layer %d expert %d", path, first_store_layer + l, x);
+                goto done;
+            }
+            if (fomoe_b200_table_upload(c, l, x, buf)) goto done;
+            loaded++;
+        }
+    }
+    rc = loaded;
+done:
+    free(buf);
+    free(idx);
+    fclose(f);
+    return rc;
 }
 
 static int shard_of(fomoe_b200_ctx_t *c, int layer, int expert, int matrix, const uint8_t **shard,

@@ -133,6 +133,11 @@ int fomoe_b200_table_upload(fomoe_b200_ctx_t *ctx, int layer, int expert, const 
  * vector w[n_embd] uploaded, the shared expert's output is multiplied by sigmoid(h . w) before it is added to the
  * routed sum; NULL removes the gate again (the default: weight 1). */
 int fomoe_b200_shared_gate_upload(fomoe_b200_ctx_t *ctx, int layer, const float *w);
+/* Fill the routed experts of the table from an expert store file of the reference (".qmoe",
+ * include/expert_store.h:9-40, written by tools/prepare_experts.c): store layers first_store_layer ..
+ * first_store_layer + n_layers - 1.  Header and per-layer down types must match the configuration; the shared
+ * expert (not part of such files) is left alone.  Returns the number of experts loaded or -1. */
+int fomoe_b200_table_load_qmoe(fomoe_b200_ctx_t *ctx, const char *path, int first_store_layer);
 /* Read this rank's shard of one matrix (0 gate, 1 up, 2 down) back in ggml order / as fp32. */
 int fomoe_b200_table_export(fomoe_b200_ctx_t *ctx, int layer, int expert, int matrix, void *ggml_out);
 int fomoe_b200_table_dequant(fomoe_b200_ctx_t *ctx, int layer, int expert, int matrix, float *out);

@@ -250,6 +250,30 @@ class Ref(_Common):
         lib.fp32_to_fp16.argtypes = [C.c_float]
         lib.fp32_to_fp16.restype = C.c_uint16
 
+    def write_store(self, path, layers):
+        """Write an expert store (.qmoe) with the reference's own writer.  layers: list of (down_type, records),
+        records = list of uint8 arrays gate | up | down, gate and up of equal size."""
+        n_layers, n_experts = len(layers), len(layers[0][1])
+        keep = [_u8(r) for _, recs in layers for r in recs]
+        ptrs = (C.c_void_p * len(keep))(*[k.ctypes.data for k in keep])
+        down_types = (C.c_uint32 * n_layers)(*[int(t) for t, _ in layers])
+        gate = None
+        downs = []
+        for t, recs in layers:
+            blk = {TYPE_Q4_K: Q4K_BLOCK, TYPE_Q5_K: Q5K_BLOCK, TYPE_Q6_K: Q6K_BLOCK}[t]
+            # gate/up are Q4_K [inter x n_embd], down is [n_embd x inter]: same element count, other block size
+            n = _u8(recs[0]).size
+            g = n * Q4K_BLOCK // (2 * Q4K_BLOCK + blk)
+            gate = g
+            downs.append(n - 2 * g)
+        down_sizes = (C.c_uint64 * n_layers)(*downs)
+        self.lib.refdrv_write_store.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_uint64, C.c_uint64, C.c_void_p,
+                                                C.c_void_p, C.c_void_p]
+        self.lib.refdrv_write_store.restype = C.c_int
+        rc = self.lib.refdrv_write_store(path.encode(), n_layers, n_experts, gate, gate, down_sizes, down_types, ptrs)
+        if rc != 0:
+            raise RuntimeError("reference expert_store writer failed")
+
     def max_threads(self):
         return int(self.lib.refdrv_max_threads())
 

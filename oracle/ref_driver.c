@@ -128,3 +128,61 @@ void refdrv_moe_block(float *out, const float *h, const void *const *experts, co
         vec_add(out, out, cpu_expert_result(sctx), n_embd);
     }
 }
+
+/* ---- expert store files: written with the reference's own writer (src/expert_store.c:128-172) so that the
+ * loader under test reads exactly what tools/prepare_experts.c produces.  records[l][e] = gate | up | down bytes of
+ * expert e of layer l; every expert is padded to a 4096-aligned stride as prepare_experts.c does. ---- */
+#include <unistd.h>
+
+#include "expert_store.h"
+
+int refdrv_write_store(const char *path, int n_layers, int n_experts, uint64_t gate_size, uint64_t up_size,
+                       const uint64_t *down_sizes, const uint32_t *down_types, const void *const *records) {
+    uint64_t max_down = 0;
+    for (int l = 0; l < n_layers; l++)
+        if (down_sizes[l] > max_down) max_down = down_sizes[l];
+    const uint64_t stride = ALIGN_UP(gate_size + up_size + max_down, (uint64_t)QMOE_ALIGNMENT);
+    qmoe_header_t hd;
+    memset(&hd, 0, sizeof(hd));
+    hd.magic = QMOE_MAGIC;
+    hd.version = QMOE_VERSION;
+    hd.n_moe_layers = (uint32_t)n_layers;
+    hd.n_experts = (uint32_t)n_experts;
+    hd.quant_type = 12;
+    hd.alignment = QMOE_ALIGNMENT;
+    hd.expert_gate_size = gate_size;
+    hd.expert_up_size = up_size;
+    hd.expert_down_size = max_down;
+    hd.expert_stride = stride;
+    qmoe_layer_entry_t *layers = (qmoe_layer_entry_t *)calloc((size_t)n_layers, sizeof(qmoe_layer_entry_t));
+    uint64_t off = ALIGN_UP((uint64_t)64 + (uint64_t)n_layers * sizeof(qmoe_layer_entry_t), (uint64_t)QMOE_ALIGNMENT);
+    for (int l = 0; l < n_layers; l++) {
+        layers[l].data_offset = off;
+        layers[l].expert_stride = stride;
+        layers[l].down_size = down_sizes[l];
+        layers[l].down_type = down_types[l];
+        off += stride * (uint64_t)n_experts;
+    }
+    int fd = expert_store_create(path, &hd, layers);
+    if (fd < 0) {
+        free(layers);
+        return -1;
+    }
+    void *buf = NULL;
+    if (posix_memalign(&buf, QMOE_ALIGNMENT, stride)) {
+        close(fd);
+        free(layers);
+        return -1;
+    }
+    int rc = 0;
+    for (int l = 0; l < n_layers && !rc; l++)
+        for (int e = 0; e < n_experts && !rc; e++) {
+            memset(buf, 0, stride);
+            memcpy(buf, records[(size_t)l * n_experts + e], gate_size + up_size + down_sizes[l]);
+            if (!expert_store_write_expert(fd, &layers[l], e, stride, buf, stride)) rc = -1;
+        }
+    free(buf);
+    free(layers);
+    close(fd);
+    return rc;
+}

@@ -81,3 +81,34 @@ def test_full_shape_table_sample(fb, oracle):
                 want = oracle.dequantize(host[r * rb:(r + 1) * rb], t, cols)
                 assert (H.bits(got[r]) == H.bits(want)).all()
     d.close()
+
+
+def test_load_expert_store_written_by_the_reference(fb, ref, tmp_path):
+    """A .qmoe file written by the reference's own writer (src/expert_store.c:128-172, the layout of
+    tools/prepare_experts.c:262-291) is read into the table: bytes of every routed expert match, the shared expert
+    (not part of such files) is untouched, mismatching files are refused."""
+    n_embd, inter, n_experts = 512, 256, 8
+    dts = [H.Q6, H.Q5, H.Q4]
+    recs = [(dt, [H.expert_record(fb, 900, l, e, dt, n_embd, inter) for e in range(n_experts)])
+            for l, dt in enumerate(dts)]
+    path = str(tmp_path / "experts.qmoe")
+    ref.write_store(path, recs)
+    d = fb.MoeDecoder(2, n_embd, inter, n_experts, 2, True, dts[1:])       # store layers 1 and 2
+    d.generate(11)
+    assert d.load_qmoe(path, first_store_layer=1) == 2 * n_experts
+    gb = fb.matrix_bytes(H.Q4, inter, n_embd)
+    for l in range(2):
+        for e in (0, 3, n_experts - 1):
+            rec = recs[1 + l][1][e]
+            assert (d.export_shard(l, e, fb.M_GATE) == rec[:gb]).all()
+            assert (d.export_shard(l, e, fb.M_UP) == rec[gb:2 * gb]).all()
+            assert (d.export_shard(l, e, fb.M_DOWN) == rec[2 * gb:]).all()
+        shared = fb.synth_matrix(11, l, n_experts, fb.M_DOWN, dts[1 + l], n_embd, inter)
+        assert (d.export_shard(l, n_experts, fb.M_DOWN) == shared).all()
+    with pytest.raises(RuntimeError):
+        d.load_qmoe(path, first_store_layer=0)      # store layer 0 is Q6_K, the table's layer 0 is Q5_K
+    with pytest.raises(RuntimeError):
+        d.load_qmoe(path, first_store_layer=2)      # runs past the end of the file's layers
+    with pytest.raises(RuntimeError):
+        d.load_qmoe(str(tmp_path / "missing.qmoe"))
+    d.close()
