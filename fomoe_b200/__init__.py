@@ -83,6 +83,8 @@ _SIGS = {
     "fomoe_b200_set_resident_mask": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "fomoe_b200_shared_gate_upload": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "fomoe_b200_table_load_qmoe": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
+    "fomoe_b200_set_allreduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "fomoe_b200_stream": (C.c_void_p, [C.c_void_p]),
     "fomoe_b200_set_car": (C.c_int, [C.c_void_p, C.c_float, C.c_int]),
     "fomoe_b200_moe_layer": (C.c_int, [C.c_void_p, C.c_int, _f32p, _f32p, _i32p, _f32p, _i32p, _f32p]),
     "fomoe_b200_moe_layer_routed": (C.c_int, [C.c_void_p, C.c_int, _f32p, _i32p, _f32p, C.c_int, _f32p]),
@@ -374,6 +376,21 @@ class MoeDecoder:
     def n_blocks(self):
         import torch
         return torch.cuda.get_device_properties(0).multi_processor_count
+
+    def set_allreduce(self, fn):
+        """fn(device_pointer, n_floats, cuda_stream_handle) -> 0: the caller's in-place sum over the tensor-parallel
+        ranks, enqueued on that stream; used by the per-phase kernels (set_variant(0)).  None removes it."""
+        if fn is None:
+            self._allreduce_cb = None
+            self._ck(self._l.fomoe_b200_set_allreduce(self._h, None, None), "set_allreduce")
+            return
+        proto = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p)
+        self._allreduce_cb = proto(lambda user, ptr, n, stream: int(fn(ptr, n, stream) or 0))
+        self._ck(self._l.fomoe_b200_set_allreduce(self._h, C.cast(self._allreduce_cb, C.c_void_p), None),
+                 "set_allreduce")
+
+    def stream_handle(self):
+        return int(self._l.fomoe_b200_stream(self._h) or 0)
 
     def tp_export(self):
         """64-byte handle of this rank's receive buffer (bytes)."""

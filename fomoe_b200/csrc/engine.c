@@ -61,6 +61,8 @@ struct fomoe_b200_ctx {
     float *pin;           /* pinned host scratch, 4 * n_embd floats + routing scratch */
     /* graphs */
     int use_graphs;
+    fomoe_b200_allreduce_fn allreduce; /* caller's collective for the per-phase tensor-parallel path, or NULL */
+    void *allreduce_user;
     cudaGraphExec_t graph_exec;
     int graph_nodes;
     uint64_t launches;
@@ -407,6 +409,16 @@ int fomoe_b200_tp_connect(fomoe_b200_ctx_t *c, const void *handles) {
     return 0;
 }
 
+int fomoe_b200_set_allreduce(fomoe_b200_ctx_t *c, fomoe_b200_allreduce_fn fn, void *user) {
+    if (!c) return -1;
+    drop_graph(c);
+    c->allreduce = fn;
+    c->allreduce_user = user;
+    return 0;
+}
+
+void *fomoe_b200_stream(fomoe_b200_ctx_t *c) { return c ? (void *)c->stream : NULL; }
+
 int fomoe_b200_set_variant(fomoe_b200_ctx_t *c, int variant) {
     if (!c || variant < 0 || variant > 2) return -1;
     if (c->stream) cudaStreamSynchronize(c->stream);
@@ -745,11 +757,19 @@ static int enqueue_stack(fomoe_b200_ctx_t *c, int l0, int l1, int load_store) {
         CKL(c, fb_launch_prologue(&a, flags, c->stream));
         CKL(c, fb_launch_router(&a, grid_router(c), c->stream));
         if (enqueue_experts(c, &a)) return -1;
+        if (c->allreduce && c->cfg.tp_size > 1 &&
+            c->allreduce(c->allreduce_user, c->moe_out, c->cfg.n_embd, (void *)c->stream)) {
+            set_err(c, "the caller's all-reduce reported a failure at layer %d", l);
+            return -1;
+        }
     }
     fill_args(c, l1 - 1, &a);
     CKL(c, fb_launch_prologue(&a, FB_PRO_ADD_PREV | (load_store ? FB_PRO_STORE : 0), c->stream));
     return 0;
 }
+
+/* launches of the per-phase path are replayed from a CUDA graph unless the caller's collective sits between them */
+static int graphs_on(const fomoe_b200_ctx_t *c) { return c->use_graphs && !(c->allreduce && c->cfg.tp_size > 1); }
 
 static int stack_kernel_usable(fomoe_b200_ctx_t *c) {
     fb_args_t a;
@@ -881,8 +901,8 @@ int fomoe_b200_moe_layer_routed(fomoe_b200_ctx_t *c, int layer, const float *h, 
 
 int fomoe_b200_stack_run(fomoe_b200_ctx_t *c, const float *x_in, int l0, int l1, float *x_out) {
     if (!c || !x_in || !x_out || l0 < 0 || l1 > c->cfg.n_layers || l0 >= l1) return -1;
-    if (c->cfg.tp_size > 1 && !stack_kernel_usable(c)) {
-        set_err(c, "stack_run on a tensor-parallel rank needs fomoe_b200_tp_connect first");
+    if (c->cfg.tp_size > 1 && !stack_kernel_usable(c) && !c->allreduce) {
+        set_err(c, "stack_run on a tensor-parallel rank needs fomoe_b200_tp_connect (or an all-reduce hook) first");
         return -1;
     }
     CK(c, cudaSetDevice(c->cfg.device));
@@ -950,8 +970,8 @@ static int build_graph(fomoe_b200_ctx_t *c) {
 
 int fomoe_b200_tokens_run(fomoe_b200_ctx_t *c, int first, int count, float *elapsed_ms) {
     if (!c || first < 0 || count < 1 || first + count > c->max_tokens) return -1;
-    if (c->cfg.tp_size > 1 && !stack_kernel_usable(c)) {
-        set_err(c, "tokens_run on a tensor-parallel rank needs fomoe_b200_tp_connect first");
+    if (c->cfg.tp_size > 1 && !stack_kernel_usable(c) && !c->allreduce) {
+        set_err(c, "tokens_run on a tensor-parallel rank needs fomoe_b200_tp_connect (or an all-reduce hook) first");
         return -1;
     }
     CK(c, cudaSetDevice(c->cfg.device));
@@ -966,11 +986,11 @@ int fomoe_b200_tokens_run(fomoe_b200_ctx_t *c, int first, int count, float *elap
         if (elapsed_ms) CK(c, cudaEventElapsedTime(elapsed_ms, c->ev0, c->ev1));
         return 0;
     }
-    if (c->use_graphs && !c->graph_exec && build_graph(c)) return -1;
+    if (graphs_on(c) && !c->graph_exec && build_graph(c)) return -1;
     CK(c, cudaMemcpyAsync(c->tok_ctr, &f, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
     CK(c, cudaEventRecord(c->ev0, c->stream));
     for (int t = 0; t < count; t++) {
-        if (c->use_graphs) {
+        if (graphs_on(c)) {
             CK(c, cudaGraphLaunch(c->graph_exec, c->stream));
             c->launches += (uint64_t)c->graph_nodes;
         } else if (enqueue_stack(c, 0, c->cfg.n_layers, 1))
@@ -1039,13 +1059,13 @@ int fomoe_b200_tokens_profile(fomoe_b200_ctx_t *c, int first, int count, float *
 
 int fomoe_b200_decode_token(fomoe_b200_ctx_t *c, const float *x_in, float *x_out) {
     if (!c || !x_in || !x_out) return -1;
-    if (c->cfg.tp_size > 1 && !stack_kernel_usable(c)) {
-        set_err(c, "decode_token on a tensor-parallel rank needs fomoe_b200_tp_connect first");
+    if (c->cfg.tp_size > 1 && !stack_kernel_usable(c) && !c->allreduce) {
+        set_err(c, "decode_token on a tensor-parallel rank needs fomoe_b200_tp_connect (or an all-reduce hook) first");
         return -1;
     }
     CK(c, cudaSetDevice(c->cfg.device));
     const int use_kernel = stack_kernel_usable(c);
-    if (!use_kernel && c->use_graphs && !c->graph_exec && build_graph(c)) return -1;
+    if (!use_kernel && graphs_on(c) && !c->graph_exec && build_graph(c)) return -1;
     const size_t nb = sizeof(float) * c->cfg.n_embd;
     unsigned *slot = (unsigned *)(c->pin + 2 * c->cfg.n_embd); /* the spare slot past max_tokens */
     *slot = (unsigned)c->max_tokens;
@@ -1055,7 +1075,7 @@ int fomoe_b200_decode_token(fomoe_b200_ctx_t *c, const float *x_in, float *x_out
     CK(c, cudaMemcpyAsync(c->tok_ctr, slot, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
     if (use_kernel) {
         if (launch_stack_kernel(c, 0, c->cfg.n_layers, 1)) return -1;
-    } else if (c->use_graphs) {
+    } else if (graphs_on(c)) {
         CK(c, cudaGraphLaunch(c->graph_exec, c->stream));
         c->launches += (uint64_t)c->graph_nodes;
     } else if (enqueue_stack(c, 0, c->cfg.n_layers, 1))

@@ -176,6 +176,16 @@ int fomoe_b200_get_routing(fomoe_b200_ctx_t *ctx, int layer, int *ids, float *sc
 /* Counters since creation: CAR substitutions, kernels launched by this library. */
 uint64_t fomoe_b200_substitutions(fomoe_b200_ctx_t *ctx);
 uint64_t fomoe_b200_kernel_launches(fomoe_b200_ctx_t *ctx);
+/* Tensor parallelism with the CALLER's collective instead of the fused exchange (the reference's arrangement:
+ * kernels per phase and tp_allreduce_sum between them, include/tp.h:53-79).  With a hook installed and the per-phase
+ * kernels selected (fomoe_b200_set_variant 0 or 1), the hook is called once per layer, after the down projection
+ * has been enqueued, with this rank's partial block output (device memory, n floats) and the CUDA stream the
+ * library works on; it must enqueue an in-place sum over all ranks on that stream (e.g. ncclAllReduce) and return 0.
+ * CUDA-graph replay is off while a hook is installed.  The benchmark uses it for its NCCL comparison arm. */
+typedef int (*fomoe_b200_allreduce_fn)(void *user, float *partial_dev, int n, void *cuda_stream);
+int fomoe_b200_set_allreduce(fomoe_b200_ctx_t *ctx, fomoe_b200_allreduce_fn fn, void *user);
+/* The cudaStream_t every call of this context enqueues on. */
+void *fomoe_b200_stream(fomoe_b200_ctx_t *ctx);
 /* Tensor parallelism over the expert intermediate dimension, one process per GPU (tp_rank / tp_size of the
  * configuration).  Each rank exports a 64-byte handle of its receive buffer, the caller gathers the handles of all
  * ranks (rank order) and gives them to every rank; after that stack_run / tokens_run / decode_token run on all ranks

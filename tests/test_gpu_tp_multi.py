@@ -19,6 +19,14 @@ SEED = 19
 
 
 def _worker(rank, world, port, q):
+    try:
+        _run_rank(rank, world, port, q)
+    except Exception as e:      # report instead of leaving the parent waiting for its time-out
+        import traceback
+        q.put(("error", rank, repr(e), traceback.format_exc()))
+
+
+def _run_rank(rank, world, port, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -27,7 +35,7 @@ def _worker(rank, world, port, q):
     import torch
     import torch.distributed as dist
     import fomoe_b200 as fb
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
     torch.cuda.set_device(rank)
     dts = [H.Q6, H.Q4, H.Q6]
     d = fb.MoeDecoder(SHAPE["n_layers"], SHAPE["n_embd"], SHAPE["n_inter"], SHAPE["n_experts"], SHAPE["top_k"], True, dts,
@@ -43,9 +51,29 @@ def _worker(rank, world, port, q):
     out = d.tokens_download(0, 4)
     one = d.stack_run(toks[1])
     ids = [d.get_routing(l)[0] for l in range(SHAPE["n_layers"])]
+    # the same stack through the per-phase kernels with the CALLER's collective between them: NCCL on the
+    # library's own stream (the arrangement of the reference's tp_allreduce_sum, include/tp.h:53-79)
+    stream = torch.cuda.ExternalStream(d.stream_handle(), device=rank)
+
+    class _Dev:
+        def __init__(self, ptr, n):
+            self.__cuda_array_interface__ = dict(shape=(n,), typestr="<f4", data=(ptr, False), version=2)
+
+    def hook(ptr, n, _stream):
+        t = torch.as_tensor(_Dev(ptr, n), device=f"cuda:{rank}")
+        with torch.cuda.stream(stream):
+            dist.all_reduce(t)
+        return 0
+
+    d.set_variant(0)
+    d.set_allreduce(hook)
+    d.tokens_run(0, 4)
+    out_nccl = d.tokens_download(0, 4)
+    d.set_allreduce(None)
+    d.set_variant(2)
     st = d.status()
     dist.barrier()
-    q.put((rank, out, one, ids, st))
+    q.put((rank, out, one, ids, st, out_nccl))
     dist.barrier()
     d.close()
     dist.destroy_process_group()
@@ -63,7 +91,15 @@ def test_tensor_parallel_stack_across_gpus(fb, world):
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = sorted([q.get(timeout=600) for _ in range(world)], key=lambda t: t[0])
+    res = [q.get(timeout=240) for _ in range(world)]
+    errors = [r for r in res if r[0] == "error"]
+    if errors:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.terminate()
+        pytest.fail("rank %d: %s\n%s" % errors[0][1:])
+    res.sort(key=lambda t: t[0])
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
@@ -75,8 +111,9 @@ def test_tensor_parallel_stack_across_gpus(fb, world):
     single.tokens_upload(0, toks)
     single.tokens_run(0, 4)
     want = single.tokens_download(0, 4)
-    for rank, out, one, ids, st in res:
+    for rank, out, one, ids, st, out_nccl in res:
         assert st == 0
+        assert H.rel_l2(out_nccl, out) < 1e-5                   # NCCL between per-phase kernels == fused exchange
         assert (H.bits(out) == H.bits(res[0][1])).all()        # every rank holds the same bits
         assert (H.bits(one) == H.bits(out[1])).all()           # host-to-host call == resident run
         assert H.rel_l2(out, want) < 1e-4                       # == single GPU up to reassociation
