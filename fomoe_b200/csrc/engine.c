@@ -58,7 +58,8 @@ struct fomoe_b200_ctx {
     /* staging */
     uint8_t *stage;       /* device staging for uploads / exports */
     uint64_t stage_bytes;
-    float *pin;           /* pinned host scratch, 4 * n_embd floats + routing scratch */
+    float *pin;           /* pinned host scratch, 4 * n_embd floats + routing scratch (mapped into the device) */
+    float *pin_dev;       /* the same memory as the device sees it */
     /* graphs */
     int use_graphs;
     fomoe_b200_allreduce_fn allreduce; /* caller's collective for the per-phase tensor-parallel path, or NULL */
@@ -304,9 +305,10 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
     }
     c->stage_bytes = max_rec_ggml > sizeof(float) * (uint64_t)ne * 1024 ? max_rec_ggml : sizeof(float) * (uint64_t)ne * 1024;
     if (cudaMalloc((void **)&c->stage, c->stage_bytes) != cudaSuccess) goto fail;
-    if (cudaHostAlloc((void **)&c->pin, sizeof(float) * (4 * (size_t)ne + 4 * FB_MAX_EXPERTS), cudaHostAllocDefault) !=
+    if (cudaHostAlloc((void **)&c->pin, sizeof(float) * (4 * (size_t)ne + 4 * FB_MAX_EXPERTS), cudaHostAllocMapped) !=
         cudaSuccess)
         goto fail;
+    if (cudaHostGetDevicePointer((void **)&c->pin_dev, c->pin, 0) != cudaSuccess) goto fail;
     return c;
 fail:
     if (!c->err[0]) set_err(c, "CUDA setup failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -323,6 +325,7 @@ int fomoe_b200_status(fomoe_b200_ctx_t *c) {
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1;
     if (cudaMemcpy(&st, c->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     if (st == FB_ST_WAIT_TIMEOUT) { /* a stack launch gave up half way: its flags are in an unknown state, start over */
+        cudaMemset(c->d_abort, 0, sizeof(int));
         cudaMemset(c->d_bar, 0, 32 * sizeof(unsigned long long));
         cudaMemset(c->d_ll_dots, 0, sizeof(unsigned long long) * FB_MAX_SLOTS * (size_t)c->cfg.n_embd);
         c->bar_count = 0;
@@ -779,8 +782,9 @@ static int stack_kernel_usable(fomoe_b200_ctx_t *c) {
     return fb_stack_supported(&a, c->n_sm);
 }
 
-/* layers [l0, l1) of `count` tokens starting at the token index already stored in tok_ctr: one launch */
-static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int count) {
+/* layers [l0, l1) of `count` resident tokens starting at index `first`: one launch.  out_host: NULL, or where (mapped
+ * host memory) the last token's output goes instead of its slot in tok_out. */
+static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int first, int count, float *out_host) {
     if (!c->layer_args_valid) {
         fb_args_t *tmp = (fb_args_t *)malloc(sizeof(fb_args_t) * (size_t)c->cfg.n_layers);
         if (!tmp) return -1;
@@ -797,8 +801,10 @@ static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int count) {
     k.layers = c->d_layer_args + l0;
     k.n_layers = l1 - l0;
     k.tok_count = count;
+    k.tok_first = first;
     k.tok_in = c->tok_in;
     k.tok_out = c->tok_out;
+    k.out_host = out_host;
     k.tok_ctr = c->tok_ctr;
     k.bar = c->d_bar;
     k.bar_base = c->bar_count;
@@ -813,7 +819,7 @@ static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int count) {
     k.trace = c->d_trace;
     k.trace_cap = c->d_trace ? c->trace_cap : 0;
     k.trace_cta = c->trace_cta;
-    CK(c, cudaMemsetAsync(c->d_abort, 0, sizeof(int), c->stream));
+    /* the abort flag is zero unless an earlier launch gave up; fomoe_b200_status clears it again */
     CKL(c, fb_launch_stack(&k, c->n_sm, c->stream));
     /* grid barriers per layer-token: logits, activations and (one GPU only; tensor-parallel ranks exchange the
      * block output through their receive buffers instead) the block output; every block arrives once at each */
@@ -909,12 +915,8 @@ int fomoe_b200_stack_run(fomoe_b200_ctx_t *c, const float *x_in, int l0, int l1,
     const size_t nb = sizeof(float) * c->cfg.n_embd;
     memcpy(c->pin, x_in, nb);
     if (stack_kernel_usable(c)) { /* the spare token slot past max_tokens carries host-to-host calls */
-        unsigned *slot = (unsigned *)(c->pin + 2 * c->cfg.n_embd);
-        *slot = (unsigned)c->max_tokens;
         CK(c, cudaMemcpyAsync(c->tok_in + (size_t)c->max_tokens * c->cfg.n_embd, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
-        CK(c, cudaMemcpyAsync(c->tok_ctr, slot, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
-        if (launch_stack_kernel(c, l0, l1, 1)) return -1;
-        CK(c, cudaMemcpyAsync(c->pin + c->cfg.n_embd, c->tok_out + (size_t)c->max_tokens * c->cfg.n_embd, nb, cudaMemcpyDeviceToHost, c->stream));
+        if (launch_stack_kernel(c, l0, l1, c->max_tokens, 1, c->pin_dev + c->cfg.n_embd)) return -1;
         CK(c, cudaStreamSynchronize(c->stream));
         memcpy(x_out, c->pin + c->cfg.n_embd, nb);
         return 0;
@@ -977,10 +979,8 @@ int fomoe_b200_tokens_run(fomoe_b200_ctx_t *c, int first, int count, float *elap
     CK(c, cudaSetDevice(c->cfg.device));
     unsigned f = (unsigned)first;
     if (stack_kernel_usable(c)) {
-        CK(c, cudaMemcpyAsync(c->tok_ctr, &f, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
-        CK(c, cudaMemsetAsync(c->d_abort, 0, sizeof(int), c->stream));
         CK(c, cudaEventRecord(c->ev0, c->stream));
-        if (launch_stack_kernel(c, 0, c->cfg.n_layers, count)) return -1;
+        if (launch_stack_kernel(c, 0, c->cfg.n_layers, first, count, NULL)) return -1;
         CK(c, cudaEventRecord(c->ev1, c->stream));
         CK(c, cudaStreamSynchronize(c->stream));
         if (elapsed_ms) CK(c, cudaEventElapsedTime(elapsed_ms, c->ev0, c->ev1));
@@ -1072,10 +1072,15 @@ int fomoe_b200_decode_token(fomoe_b200_ctx_t *c, const float *x_in, float *x_out
     const size_t spare = (size_t)c->max_tokens * c->cfg.n_embd;
     memcpy(c->pin, x_in, nb);
     CK(c, cudaMemcpyAsync(c->tok_in + spare, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
-    CK(c, cudaMemcpyAsync(c->tok_ctr, slot, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
     if (use_kernel) {
-        if (launch_stack_kernel(c, 0, c->cfg.n_layers, 1)) return -1;
-    } else if (graphs_on(c)) {
+        /* one copy in, one launch, one synchronise: the kernel writes the result into the pinned buffer itself */
+        if (launch_stack_kernel(c, 0, c->cfg.n_layers, c->max_tokens, 1, c->pin_dev + c->cfg.n_embd)) return -1;
+        CK(c, cudaStreamSynchronize(c->stream));
+        memcpy(x_out, c->pin + c->cfg.n_embd, nb);
+        return 0;
+    }
+    CK(c, cudaMemcpyAsync(c->tok_ctr, slot, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
+    if (graphs_on(c)) {
         CK(c, cudaGraphLaunch(c->graph_exec, c->stream));
         c->launches += (uint64_t)c->graph_nodes;
     } else if (enqueue_stack(c, 0, c->cfg.n_layers, 1))

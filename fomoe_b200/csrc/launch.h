@@ -103,10 +103,12 @@ int fb_launch_down_ring(const fb_args_t *a, int grid, void *stream);
 typedef struct {
     const fb_args_t *layers; /* device array, one entry per layer of the range to run */
     int n_layers;
-    int tok_count;           /* tokens *tok_ctr .. *tok_ctr + tok_count - 1 */
+    int tok_count;           /* tokens tok_first .. tok_first + tok_count - 1 */
+    int tok_first;
     const float *tok_in;
     float *tok_out;
-    unsigned *tok_ctr;
+    float *out_host;         /* NULL, or mapped host memory that receives the LAST token's output instead of tok_out */
+    unsigned *tok_ctr;       /* left at tok_first + tok_count for the per-phase path */
     unsigned long long *bar; /* grid barrier: [0] arrival counter, [16] generation of the last completed barrier */
     unsigned long long bar_base; /* arrivals before this launch (the host keeps count) */
     unsigned long long *ll_dots; /* [FB_MAX_SLOTS][n_embd] {generation, value} words: row groups split between blocks */

@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
     __syncthreads();
     uint32_t full_uses[2] = {0, 0}; /* completed phases of this warp's two stage barriers */
 
-    const unsigned tok_first = *K.tok_ctr;
+    const unsigned tok_first = (unsigned)K.tok_first;
     int trace_n = 0;
     bool alive = true;
     bool pending_join = false; /* a barrier has been arrived at but not yet waited for */
@@ -684,7 +684,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 }
             }
             if (leader && e0 < A.n_embd) {
-                float4 *o = reinterpret_cast<float4 *>(K.tok_out + (size_t)tok * A.n_embd + e0);
+                /* a host-to-host call lets the last token's result go straight to the caller's pinned buffer */
+                float4 *o = (K.out_host && tk == K.tok_count - 1)
+                                ? reinterpret_cast<float4 *>(K.out_host + e0)
+                                : reinterpret_cast<float4 *>(K.tok_out + (size_t)tok * A.n_embd + e0);
                 o[0] = make_float4(__fadd_rn(x[0], mo[0]), __fadd_rn(x[1], mo[1]), __fadd_rn(x[2], mo[2]), __fadd_rn(x[3], mo[3]));
                 o[1] = make_float4(__fadd_rn(x[4], mo[4]), __fadd_rn(x[5], mo[5]), __fadd_rn(x[6], mo[6]), __fadd_rn(x[7], mo[7]));
                 float4 *xo = reinterpret_cast<float4 *>(A.x + e0);
