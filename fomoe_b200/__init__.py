@@ -327,7 +327,8 @@ class MoeDecoder:
         return float(ms.value)
 
     def decode_token(self, x):
-        """One token host -> host through every layer (H2D, graph launch, D2H, synchronise)."""
+        """One token host -> host through every layer: one pinned copy in, one launch of the stack kernel (which
+        writes the result into pinned host memory), one synchronise."""
         x = _f32(x)
         out = np.empty_like(x)
         self._ck(self._l.fomoe_b200_decode_token(self._h, _fp(x), _fp(out)), "decode_token")
