@@ -190,6 +190,33 @@ def test_stack_teacher_forced_and_free_running(fb, oracle):
     d.close()
 
 
+def test_config2_full_shape_stack(fb, oracle):
+    """The benchmark's own layer shape (hidden 4096, 512 experts, top-10 + shared, intermediate 1024, Q6_K / Q4_K down
+    alternating), four layers: every layer teacher-forced against the oracle (ids exact), the free-running token, and
+    the properties that do not need the oracle -- a batch of tokens in one launch equals the tokens one by one, bit
+    for bit, and a second run repeats the first."""
+    n_layers, n_embd, inter, n_experts, top_k, seed, eps = 4, 4096, 1024, 512, 10, 397, 1e-6
+    dts = [H.Q6, H.Q4, H.Q6, H.Q4]
+    d = fb.MoeDecoder(n_layers, n_embd, inter, n_experts, top_k, True, dts, rms_eps=eps, max_tokens=6)
+    d.generate(seed)
+    toks = np.stack([H.hidden(fb, seed, t, n_embd) for t in range(6)])
+    tr = _oracle_stack(oracle, fb, seed, toks[0], range(n_layers), n_embd, inter, n_experts, top_k, dts, eps)
+    for l in range(n_layers):
+        got = d.stack_run(tr[l]["x_in"], l, l + 1)
+        assert (d.get_routing(l)[0] == tr[l]["ids"]).all(), l
+        assert H.rel_l2(got, tr[l]["x_out"]) < OUT_EXPECT      # one int8 activation may move by 1, see OUT_EXPECT
+    assert H.rel_l2(d.stack_run(toks[0]), tr[-1]["x_out"]) < 1e-3
+    d.tokens_upload(0, toks)
+    d.tokens_run(0, 6)
+    batch = d.tokens_download(0, 6)
+    for t in range(6):
+        assert (H.bits(batch[t]) == H.bits(d.decode_token(toks[t]))).all(), t
+    d.tokens_run(0, 6)
+    assert (H.bits(batch) == H.bits(d.tokens_download(0, 6))).all()
+    assert np.isfinite(batch).all() and d.status() == 0
+    d.close()
+
+
 def test_shared_expert_gate(fb, oracle):
     """Optional scalar gate sigmoid(h . w) on the shared expert (src/inference.c:582-596), per-phase kernels and the
     persistent stack kernel; removing the gate restores the ungated bits."""
