@@ -54,6 +54,110 @@ __device__ __forceinline__ void fb_sort32(float &v, int &i, int lane) {
     }
 }
 
+/* One router row re-summed in the CPU's order: sequential multiply-then-add (src/tensor.c:104-113).  Rarely called
+ * and kept out of line so that its unrolled body does not sit in the instruction stream of every layer. */
+static __device__ __noinline__ float fb_exact_logit(const fb_args_t &A, const float *h_smem, int row) {
+    const float4 *w = reinterpret_cast<const float4 *>(A.router_w + (size_t)row * A.n_embd);
+    const float4 *hh = reinterpret_cast<const float4 *>(h_smem);
+    float exact = 0.0f;
+    for (int j0 = 0; j0 < A.n_embd / 4; j0 += 8) {
+        float4 wv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) wv[u] = __ldg(w + j0 + u);
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const float4 hv = hh[j0 + u];
+            exact = __fadd_rn(exact, __fmul_rn(wv[u].x, hv.x));
+            exact = __fadd_rn(exact, __fmul_rn(wv[u].y, hv.y));
+            exact = __fadd_rn(exact, __fmul_rn(wv[u].z, hv.z));
+            exact = __fadd_rn(exact, __fmul_rn(wv[u].w, hv.w));
+        }
+    }
+    return exact;
+}
+
+/* Cache-aware routing over one residency tier (src/car.c:36-264; classify as src/gpu_kernels.hip:7097-7149), run by
+ * one warp on the renormalised selection in W->ci / W->cv.  Returns the number of substitutions.  Out of line: it
+ * only runs when a residency mask and a threshold inside (0, 1) are set. */
+static __device__ __noinline__ int fb_select_car(const fb_args_t &A, fb_sel_smem_t *W, const float *all_scores, int lane) {
+    const int nE = A.n_experts, k = A.top_k;
+    int n_subs = 0;
+
+    uint32_t res = 0, sel = 0; /* bit j <-> expert j*32 + lane */
+#pragma unroll
+    for (int j = 0; j < FB_EPL; j++)
+        if ((__ldg(A.resident + j) >> lane) & 1u) res |= 1u << j;
+    for (int r = 0; r < k; r++) {
+        const int e = W->ci[r];
+        if ((e & 31) == lane) sel |= 1u << (e >> 5);
+    }
+    int c_idx[FB_MAX_TOPK], c_best[FB_MAX_TOPK];
+    float c_score[FB_MAX_TOPK], c_ratio[FB_MAX_TOPK];
+    int nc = 0;
+    for (int r = 0; r < k; r++) {
+        const int orig = W->ci[r];
+        if ((__ldg(A.resident + (orig >> 5)) >> (orig & 31)) & 1u) continue; /* cached: uniform */
+        float bv = 0.0f; /* strict improvement over 0: src/car.c:104-112 */
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < FB_EPL; j++) {
+            const int e = j * 32 + lane;
+            if (((res >> j) & 1u) && !((sel >> j) & 1u) && e < nE) {
+                const float pe = all_scores[e];
+                if (pe > 0.0f && fb_better(pe, e, bv, bi)) {
+                    bv = pe;
+                    bi = e;
+                }
+            }
+        }
+        fb_warp_best(bv, bi);
+        const float ov = all_scores[orig];
+        const float ratio = (ov > 0.0f) ? __fdiv_rn(bv, ov) : 0.0f;
+        if (bi != 0x7fffffff && ratio >= A.car_threshold) {
+            c_idx[nc] = r;
+            c_best[nc] = bi;
+            c_score[nc] = bv;
+            c_ratio[nc] = ratio;
+            nc++;
+            if ((bi & 31) == lane) sel |= 1u << (bi >> 5); /* reserved at once */
+        }
+    }
+    for (int a = 1; a < nc; a++) { /* stable insertion by ratio descending (src/car.c:168-176) */
+        const int ti = c_idx[a], tb = c_best[a];
+        const float ts = c_score[a], tr = c_ratio[a];
+        int b = a - 1;
+        while (b >= 0 && c_ratio[b] < tr) {
+            c_idx[b + 1] = c_idx[b];
+            c_best[b + 1] = c_best[b];
+            c_score[b + 1] = c_score[b];
+            c_ratio[b + 1] = c_ratio[b];
+            b--;
+        }
+        c_idx[b + 1] = ti;
+        c_best[b + 1] = tb;
+        c_score[b + 1] = ts;
+        c_ratio[b + 1] = tr;
+    }
+    if (lane == 0) {
+        for (int c = 0; c < nc; c++) {
+            const int r = c_idx[c];
+            W->ci[r] = c_best[c];
+            W->cv[r] = A.car_dampen ? __fmul_rn(W->cv[r], c_ratio[c]) : c_score[c];
+        }
+        if (nc > 0 && !A.car_dampen) {
+            float s2 = 0.0f;
+            for (int r = 0; r < k; r++) s2 = __fadd_rn(s2, W->cv[r]);
+            if (s2 > 0.0f) {
+                const float i2 = __fdiv_rn(1.0f, s2);
+                for (int r = 0; r < k; r++) W->cv[r] = __fmul_rn(W->cv[r], i2);
+            }
+        }
+    }
+    n_subs = nc;
+    __syncwarp();
+    return n_subs;
+}
+
 /* Must be called by all 512 threads of the block.  Outputs (shared memory): ids[n_slots], scores[n_slots],
  * ids_orig[top_k], slot_rec[n_slots], all_scores[n_experts].  `leader` updates the global counters;
  * `shared_score` is the weight of the shared expert's slot. */
@@ -80,7 +184,7 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
             const float mv = W->lv[0][w][p];
             const int mi = W->li[0][w][p];
             int rank = p;
-#pragma unroll
+#pragma unroll /* fully unrolled on purpose: the fifteen searches overlap; unrolled by three the selection took 0.4 us longer */
             for (int o = 1; o < 16; o++) {
                 const int w2 = (w + o) & 15;
                 int pos = 0;
@@ -107,25 +211,7 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
         bool mine = false;
         for (int r = 0; r < kk; r++)
             if (((flag >> r) & 1u) && W->li[1][0][r] == tid) mine = true;
-        if (mine) { /* this thread's expert is in a near tie: the CPU's order, sequential multiply-then-add */
-            const float4 *w = reinterpret_cast<const float4 *>(A.router_w + (size_t)tid * A.n_embd);
-            const float4 *hh = reinterpret_cast<const float4 *>(h_smem);
-            float exact = 0.0f;
-            for (int j0 = 0; j0 < A.n_embd / 4; j0 += 8) {
-                float4 wv[8];
-#pragma unroll
-                for (int u = 0; u < 8; u++) wv[u] = __ldg(w + j0 + u);
-#pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    const float4 hv = hh[j0 + u];
-                    exact = __fadd_rn(exact, __fmul_rn(wv[u].x, hv.x));
-                    exact = __fadd_rn(exact, __fmul_rn(wv[u].y, hv.y));
-                    exact = __fadd_rn(exact, __fmul_rn(wv[u].z, hv.z));
-                    exact = __fadd_rn(exact, __fmul_rn(wv[u].w, hv.w));
-                }
-            }
-            lg = exact;
-        }
+        if (mine) lg = fb_exact_logit(A, h_smem, tid);
         __syncthreads();
     }
 
@@ -191,80 +277,7 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
 
         /* ---- CAR ---- */
         int n_subs = 0;
-        if (A.resident && A.car_threshold > 0.0f && A.car_threshold < 1.0f) {
-            uint32_t res = 0, sel = 0; /* bit j <-> expert j*32 + lane */
-#pragma unroll
-            for (int j = 0; j < FB_EPL; j++)
-                if ((__ldg(A.resident + j) >> lane) & 1u) res |= 1u << j;
-            for (int r = 0; r < k; r++) {
-                const int e = W->ci[r];
-                if ((e & 31) == lane) sel |= 1u << (e >> 5);
-            }
-            int c_idx[FB_MAX_TOPK], c_best[FB_MAX_TOPK];
-            float c_score[FB_MAX_TOPK], c_ratio[FB_MAX_TOPK];
-            int nc = 0;
-            for (int r = 0; r < k; r++) {
-                const int orig = W->ci[r];
-                if ((__ldg(A.resident + (orig >> 5)) >> (orig & 31)) & 1u) continue; /* cached: uniform */
-                float bv = 0.0f; /* strict improvement over 0: src/car.c:104-112 */
-                int bi = 0x7fffffff;
-#pragma unroll
-                for (int j = 0; j < FB_EPL; j++) {
-                    const int e = j * 32 + lane;
-                    if (((res >> j) & 1u) && !((sel >> j) & 1u) && e < nE) {
-                        const float pe = all_scores[e];
-                        if (pe > 0.0f && fb_better(pe, e, bv, bi)) {
-                            bv = pe;
-                            bi = e;
-                        }
-                    }
-                }
-                fb_warp_best(bv, bi);
-                const float ov = all_scores[orig];
-                const float ratio = (ov > 0.0f) ? __fdiv_rn(bv, ov) : 0.0f;
-                if (bi != 0x7fffffff && ratio >= A.car_threshold) {
-                    c_idx[nc] = r;
-                    c_best[nc] = bi;
-                    c_score[nc] = bv;
-                    c_ratio[nc] = ratio;
-                    nc++;
-                    if ((bi & 31) == lane) sel |= 1u << (bi >> 5); /* reserved at once */
-                }
-            }
-            for (int a = 1; a < nc; a++) { /* stable insertion by ratio descending (src/car.c:168-176) */
-                const int ti = c_idx[a], tb = c_best[a];
-                const float ts = c_score[a], tr = c_ratio[a];
-                int b = a - 1;
-                while (b >= 0 && c_ratio[b] < tr) {
-                    c_idx[b + 1] = c_idx[b];
-                    c_best[b + 1] = c_best[b];
-                    c_score[b + 1] = c_score[b];
-                    c_ratio[b + 1] = c_ratio[b];
-                    b--;
-                }
-                c_idx[b + 1] = ti;
-                c_best[b + 1] = tb;
-                c_score[b + 1] = ts;
-                c_ratio[b + 1] = tr;
-            }
-            if (lane == 0) {
-                for (int c = 0; c < nc; c++) {
-                    const int r = c_idx[c];
-                    W->ci[r] = c_best[c];
-                    W->cv[r] = A.car_dampen ? __fmul_rn(W->cv[r], c_ratio[c]) : c_score[c];
-                }
-                if (nc > 0 && !A.car_dampen) {
-                    float s2 = 0.0f;
-                    for (int r = 0; r < k; r++) s2 = __fadd_rn(s2, W->cv[r]);
-                    if (s2 > 0.0f) {
-                        const float i2 = __fdiv_rn(1.0f, s2);
-                        for (int r = 0; r < k; r++) W->cv[r] = __fmul_rn(W->cv[r], i2);
-                    }
-                }
-            }
-            n_subs = nc;
-            __syncwarp();
-        }
+        if (A.resident && A.car_threshold > 0.0f && A.car_threshold < 1.0f) n_subs = fb_select_car(A, W, all_scores, lane);
         if (lane < k) {
             int e = W->ci[lane];
             if (e < 0 || e >= nE) {

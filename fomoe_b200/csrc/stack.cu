@@ -187,11 +187,10 @@ __device__ __forceinline__ unsigned long long sk_now() {
 
 /* phase stamps of block `trace_cta` (of every block when trace_cta < 0; trace_cap is then per block), in
  * nanoseconds of %globaltimer, 9 per layer, for profiling only */
-#define SK_STAMP(idx)                                                                        \
-    do {                                                                                     \
-        if (K.trace && (K.trace_cta < 0 || cta == K.trace_cta) && tid == 0 && trace_n < K.trace_cap) \
-            K.trace[(K.trace_cta < 0 ? (size_t)cta * K.trace_cap : 0) + trace_n++] =         \
-                ((unsigned long long)(idx) << 56) | (sk_now() & 0x00ffffffffffffffULL);      \
+#define SK_STAMP(idx)                                                                             \
+    do {                                                                                          \
+        if (trace_p && trace_n < K.trace_cap)                                                     \
+            trace_p[trace_n++] = ((unsigned long long)(idx) << 56) | (sk_now() & 0x00ffffffffffffffULL); \
     } while (0)
 
 template <bool TP>
@@ -218,6 +217,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
 
     const unsigned tok_first = (unsigned)K.tok_first;
     int trace_n = 0;
+    /* where this thread records its stamps: thread 0 of the traced block (of every block when trace_cta < 0) */
+    unsigned long long *trace_p = nullptr;
+    if (K.trace && tid == 0 && (K.trace_cta < 0 || cta == K.trace_cta))
+        trace_p = K.trace + (K.trace_cta < 0 ? (size_t)cta * K.trace_cap : 0);
     bool alive = true;
     bool pending_join = false; /* a barrier has been arrived at but not yet waited for */
 
