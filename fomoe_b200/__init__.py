@@ -84,6 +84,9 @@ _SIGS = {
     "fomoe_b200_shared_gate_upload": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "fomoe_b200_table_load_qmoe": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
     "fomoe_b200_set_allreduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "fomoe_b200_tp_recv_ptr": (C.c_void_p, [C.c_void_p]),
+    "fomoe_b200_tp_connect_ptrs": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "fomoe_b200_set_wait_limit": (C.c_int, [C.c_void_p, C.c_uint]),
     "fomoe_b200_stream": (C.c_void_p, [C.c_void_p]),
     "fomoe_b200_set_car": (C.c_int, [C.c_void_p, C.c_float, C.c_int]),
     "fomoe_b200_moe_layer": (C.c_int, [C.c_void_p, C.c_int, _f32p, _f32p, _i32p, _f32p, _i32p, _f32p]),
@@ -377,6 +380,17 @@ class MoeDecoder:
     def n_blocks(self):
         import torch
         return torch.cuda.get_device_properties(0).multi_processor_count
+
+    def tp_recv_ptr(self):
+        return int(self._l.fomoe_b200_tp_recv_ptr(self._h) or 0)
+
+    def tp_connect_ptrs(self, ptrs):
+        """ptrs: the receive buffers (device addresses) of all tp_size ranks of this process, rank order."""
+        arr = (C.c_void_p * len(ptrs))(*ptrs)
+        self._ck(self._l.fomoe_b200_tp_connect_ptrs(self._h, arr), "tp_connect_ptrs")
+
+    def set_wait_limit(self, polls):
+        self._ck(self._l.fomoe_b200_set_wait_limit(self._h, int(polls)), "set_wait_limit")
 
     def set_allreduce(self, fn):
         """fn(device_pointer, n_floats, cuda_stream_handle) -> 0: the caller's in-place sum over the tensor-parallel

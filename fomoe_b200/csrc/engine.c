@@ -86,6 +86,7 @@ struct fomoe_b200_ctx {
     unsigned gen_count;            /* layer-tokens of all finished stack launches */
     int trace_cap, trace_cta;
     int *d_abort;
+    unsigned spin_limit; /* polls after which the stack kernel gives a wait up */
     char err[256];
 };
 
@@ -177,7 +178,7 @@ void fomoe_b200_destroy(fomoe_b200_ctx_t *c) {
     cudaFree(c->status); cudaFree((void *)c->slot_rec); cudaFree(c->q8h); cudaFree(c->q8a);
     cudaFree(c->counters); cudaFree(c->tok_ctr); cudaFree(c->shared_gate); cudaFree(c->freq); cudaFree(c->tok_in); cudaFree(c->tok_out);
     for (int p = 0; p < FB_MAX_TP; p++)
-        if (c->tp_peer[p] && c->tp_peer[p] != c->tp_recv) cudaIpcCloseMemHandle(c->tp_peer[p]);
+        if (c->tp_connected == 1 && c->tp_peer[p] && c->tp_peer[p] != c->tp_recv) cudaIpcCloseMemHandle(c->tp_peer[p]);
     cudaFree(c->tp_recv);
     cudaFree(c->d_trace); cudaFree(c->stage); cudaFree(c->d_layer_args); cudaFree(c->d_bar); cudaFree(c->d_ll_dots); cudaFree(c->d_abort);
     if (c->pin) cudaFreeHost(c->pin);
@@ -208,6 +209,7 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
     if (!c) return NULL;
     c->cfg = *cfg;
     c->use_graphs = 1;
+    c->spin_limit = 1u << 22; /* seconds: far beyond any legitimate wait, still bounded */
     c->variant = getenv("FOMOE_B200_VARIANT") ? atoi(getenv("FOMOE_B200_VARIANT")) : 2;
     const int N = cfg->tp_size > 0 ? cfg->tp_size : 1;
     c->cfg.tp_size = N;
@@ -409,6 +411,24 @@ int fomoe_b200_tp_connect(fomoe_b200_ctx_t *c, const void *handles) {
         c->tp_peer[p] = (unsigned long long *)ptr;
     }
     c->tp_connected = 1;
+    return 0;
+}
+
+int fomoe_b200_tp_connect_ptrs(fomoe_b200_ctx_t *c, void *const *recv_ptrs) {
+    if (!c || !recv_ptrs || !c->tp_recv) return -1;
+    for (int p = 0; p < c->cfg.tp_size; p++) {
+        if (!recv_ptrs[p]) return -1;
+        c->tp_peer[p] = (p == c->cfg.tp_rank) ? c->tp_recv : (unsigned long long *)recv_ptrs[p];
+    }
+    c->tp_connected = 2; /* nothing to close on destroy */
+    return 0;
+}
+
+void *fomoe_b200_tp_recv_ptr(fomoe_b200_ctx_t *c) { return c ? (void *)c->tp_recv : NULL; }
+
+int fomoe_b200_set_wait_limit(fomoe_b200_ctx_t *c, unsigned polls) {
+    if (!c) return -1;
+    c->spin_limit = polls ? polls : 1u << 22;
     return 0;
 }
 
@@ -811,6 +831,7 @@ static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int first, i
     k.ll_dots = c->d_ll_dots;
     k.gen_base = c->gen_count;
     k.abort_flag = c->d_abort;
+    k.spin_limit = c->spin_limit;
     k.status = c->status;
     k.tp_rank = c->cfg.tp_rank;
     k.tp_size = c->cfg.tp_size;

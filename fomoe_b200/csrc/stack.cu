@@ -43,7 +43,6 @@
 #define SK_RING_BYTES (SK_DOWN_WARPS * 2 * FB_Q6K_GROUP) /* 174,720 B: 13 x 2 x 6720; gate/up uses 16 x 2 x 4608 of it */
 #define SK_MAX_Q8A 48                                 /* n_slots * down blocks per row */
 #define SK_MAX_RG 8                                   /* row groups one block's run of down tasks can touch */
-#define SK_SPIN_LIMIT (1u << 22)
 #define SK_BAR_THREAD (SK_THREADS - 32) /* lane 0 of the last warp runs the grid barrier; it issues no copies */
 
 struct sk_smem_t {
@@ -69,6 +68,7 @@ struct sk_bar_t {
     int *status;
     unsigned grid;
     unsigned long long base;  /* arrivals before this launch */
+    unsigned limit;           /* polls before a wait is given up */
     unsigned epoch;           /* barriers this block has arrived at in this launch */
 };
 
@@ -110,7 +110,7 @@ __device__ __forceinline__ bool sk_wait(const sk_bar_t &B, sk_smem_t *S) {
         int ok = 1;
         unsigned n = 0;
         while (ld_acquire_u64(B.ctr + 16) < gen) {
-            if (++n > SK_SPIN_LIMIT || ((n & 63u) == 0 && ld_volatile_s32(B.abort_flag))) {
+            if (++n > B.limit || ((n & 63u) == 0 && ld_volatile_s32(B.abort_flag))) {
                 ok = 0;
                 break;
             }
@@ -155,13 +155,13 @@ __device__ __forceinline__ void sk_put_sys(sk_word_t *p, float v, uint32_t gen) 
  * form bit-identical sums (the reference's tp_allreduce_sum, src/tp.hip:85-124, has the same meaning: out = p_0 +
  * p_1 on both ranks).  false = gave up. */
 __device__ __forceinline__ bool sk_gather8(const sk_word_t *recv, int tp, int n, int e0, uint32_t gen, float (&v)[8],
-                                           const int *abort_flag) {
+                                           const int *abort_flag, unsigned limit) {
 #pragma unroll
     for (int k = 0; k < 8; k++) v[k] = 0.0f;
     for (int src = 0; src < tp; src++) { /* rank order: every rank forms the same sum */
         const sk_word_t *p = recv + (size_t)src * n + e0;
         bool got = false;
-        for (unsigned nsp = 0; nsp < SK_SPIN_LIMIT && !got; nsp++) {
+        for (unsigned nsp = 0; nsp < limit && !got; nsp++) {
             sk_word_t w[8];
 #pragma unroll
             for (int k = 0; k < 4; k++) sk_get2_sys(p + 2 * k, w[2 * k], w[2 * k + 1]);
@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cta = blockIdx.x, G = gridDim.x;
     const bool leader = (cta == 0);
-    sk_bar_t B = {K.bar, K.abort_flag, K.status, (unsigned)G, K.bar_base, 0u};
+    sk_bar_t B = {K.bar, K.abort_flag, K.status, (unsigned)G, K.bar_base, K.spin_limit, 0u};
 
     const uint32_t full_u = fb_smem_u32(&S->full[warp][0]);
     if (tid == 0) {
@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             float mo[8];
             if (TP) {
                 bool got = true;
-                if (l > 0 && own) got = sk_gather8(K.tp_recv, K.tp_size, n, e0, gen - 1u, mo, K.abort_flag);
+                if (l > 0 && own) got = sk_gather8(K.tp_recv, K.tp_size, n, e0, gen - 1u, mo, K.abort_flag, K.spin_limit);
                 if (!__syncthreads_and(got ? 1 : 0)) {
                     if (tid == 0) {
                         atomicExch(B.abort_flag, 1);
@@ -607,7 +607,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                             const int idx = base + 32 * u + lane;
                             if (idx < nw && rg * drpg + (idx & (drpg - 1)) < n) need |= 1u << u;
                         }
-                        for (unsigned nsp = 0; nsp < SK_SPIN_LIMIT && need; nsp++) {
+                        for (unsigned nsp = 0; nsp < K.spin_limit && need; nsp++) {
                             sk_word_t w[4];
 #pragma unroll
                             for (int u = 0; u < 4; u++) {
@@ -666,7 +666,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             if (TP) {
                 bool got = true;
                 if (leader && e0 < A.n_embd)
-                    got = sk_gather8(K.tp_recv, K.tp_size, A.n_embd, e0, K.gen_base + (uint32_t)((tk + 1) * K.n_layers), mo, K.abort_flag);
+                    got = sk_gather8(K.tp_recv, K.tp_size, A.n_embd, e0, K.gen_base + (uint32_t)((tk + 1) * K.n_layers), mo, K.abort_flag, K.spin_limit);
                 if (!__syncthreads_and(got ? 1 : 0)) {
                     if (tid == 0) {
                         atomicExch(B.abort_flag, 1);

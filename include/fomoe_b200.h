@@ -176,6 +176,15 @@ int fomoe_b200_get_routing(fomoe_b200_ctx_t *ctx, int layer, int *ids, float *sc
 /* Counters since creation: CAR substitutions, kernels launched by this library. */
 uint64_t fomoe_b200_substitutions(fomoe_b200_ctx_t *ctx);
 uint64_t fomoe_b200_kernel_launches(fomoe_b200_ctx_t *ctx);
+/* The same for ranks that live in ONE process (one context per GPU, as the reference drives its two GPUs from one
+ * process, src/tp.hip): the receive buffers are exchanged as plain device pointers; the caller enables peer access
+ * between the devices (cudaDeviceEnablePeerAccess). */
+void *fomoe_b200_tp_recv_ptr(fomoe_b200_ctx_t *ctx);
+int fomoe_b200_tp_connect_ptrs(fomoe_b200_ctx_t *ctx, void *const *recv_ptrs /* tp_size pointers, rank order */);
+/* Every wait of the stack kernel on another block or rank gives up after `polls` polls (0 = the default, about
+ * four million: seconds), sets status 2 ("bounded wait ran out") and lets the kernel return; a rank whose peer
+ * has gone away therefore reports instead of hanging.  fomoe_b200_status re-arms the kernel's flags afterwards. */
+int fomoe_b200_set_wait_limit(fomoe_b200_ctx_t *ctx, unsigned polls);
 /* Tensor parallelism with the CALLER's collective instead of the fused exchange (the reference's arrangement:
  * kernels per phase and tp_allreduce_sum between them, include/tp.h:53-79).  With a hook installed and the per-phase
  * kernels selected (fomoe_b200_set_variant 0 or 1), the hook is called once per layer, after the down projection

@@ -297,3 +297,27 @@ def test_tensor_parallel_partials_sum_to_full(fb, oracle, tp):
     assert H.rel_l2(acc, want["out"]) < 1e-5
     o = H.oracle_layer(oracle, fb, seed, 0, h, n_embd, inter, n_experts, top_k, H.Q6)
     assert H.rel_l2(acc, o["out"]) < 2e-5
+
+
+def test_missing_peer_times_out_and_reports(fb):
+    """Failure detection without a fault: a tensor-parallel rank whose peer never delivers (its slot of the receive
+    buffer is a flag that nothing sets) gives the wait up after the configured number of polls, the kernel returns,
+    the status word says so, and the GPU goes on working."""
+    n_embd, inter, n_experts, top_k, seed = 1024, 512, 16, 2, 23
+    dts = [H.Q6, H.Q4]
+    d = fb.MoeDecoder(2, n_embd, inter, n_experts, top_k, True, dts, tp_rank=0, tp_size=2, rms_eps=1e-6, max_tokens=2)
+    d.generate(seed)
+    own = d.tp_recv_ptr()
+    d.tp_connect_ptrs([own, own])          # "rank 1" is nobody: its partial sums never arrive
+    d.set_wait_limit(20000)                # about 15 ms instead of seconds
+    d.tokens_upload(0, np.stack([H.hidden(fb, seed, t, n_embd) for t in range(2)]))
+    d.tokens_run(0, 2)                     # returns: the kernel gave up at layer 1's receive step
+    assert d.status() == 2                 # bounded wait ran out (and the flags are re-armed)
+    d.tokens_run(0, 1)
+    assert d.status() == 2                 # still nobody there: reported again, not hung
+    d.close()
+    ok = fb.MoeDecoder(2, n_embd, inter, n_experts, top_k, True, dts, rms_eps=1e-6, max_tokens=2)
+    ok.generate(seed)
+    x = H.hidden(fb, seed, 0, n_embd)
+    assert np.isfinite(ok.decode_token(x)).all() and ok.status() == 0
+    ok.close()
