@@ -87,6 +87,7 @@ _SIGS = {
     "fomoe_b200_tp_recv_ptr": (C.c_void_p, [C.c_void_p]),
     "fomoe_b200_tp_connect_ptrs": (C.c_int, [C.c_void_p, C.c_void_p]),
     "fomoe_b200_set_wait_limit": (C.c_int, [C.c_void_p, C.c_uint]),
+    "fomoe_b200_set_act_mode": (C.c_int, [C.c_void_p, C.c_int]),
     "fomoe_b200_stream": (C.c_void_p, [C.c_void_p]),
     "fomoe_b200_set_car": (C.c_int, [C.c_void_p, C.c_float, C.c_int]),
     "fomoe_b200_moe_layer": (C.c_int, [C.c_void_p, C.c_int, _f32p, _f32p, _i32p, _f32p, _i32p, _f32p]),
@@ -269,6 +270,11 @@ class MoeDecoder:
         n = self._l.fomoe_b200_table_load_qmoe(self._h, path.encode(), first_store_layer)
         self._ck(0 if n >= 0 else -1, "table_load_qmoe")
         return n
+
+    def set_act_mode(self, f32):
+        """False: Q8_K int8 activations (src/cpu_expert.c, default); True: fp32 activations (the reference's
+        forward pass without cpu_expert)."""
+        self._ck(self._l.fomoe_b200_set_act_mode(self._h, 1 if f32 else 0), "set_act_mode")
 
     def set_shared_gate(self, layer, w):
         """w: float32[n_embd] (the shared expert's output is scaled by sigmoid(h . w)) or None (no gate)."""

@@ -87,6 +87,7 @@ struct fomoe_b200_ctx {
     int trace_cap, trace_cta;
     int *d_abort;
     unsigned spin_limit; /* polls after which the stack kernel gives a wait up */
+    int act_f32;         /* 1: experts run with fp32 activations (the reference's second definition) */
     char err[256];
 };
 
@@ -442,6 +443,14 @@ int fomoe_b200_set_allreduce(fomoe_b200_ctx_t *c, fomoe_b200_allreduce_fn fn, vo
 
 void *fomoe_b200_stream(fomoe_b200_ctx_t *c) { return c ? (void *)c->stream : NULL; }
 
+int fomoe_b200_set_act_mode(fomoe_b200_ctx_t *c, int mode) {
+    if (!c || (mode != FOMOE_B200_ACT_Q8K && mode != FOMOE_B200_ACT_F32)) return -1;
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    drop_graph(c);
+    c->act_f32 = mode == FOMOE_B200_ACT_F32;
+    return 0;
+}
+
 int fomoe_b200_set_variant(fomoe_b200_ctx_t *c, int variant) {
     if (!c || variant < 0 || variant > 2) return -1;
     if (c->stream) cudaStreamSynchronize(c->stream);
@@ -757,6 +766,11 @@ static int grid_tasks(const fomoe_b200_ctx_t *c, int tasks) {
 
 /* expert phase of one layer: gate/up/SwiGLU then down/combine, on the slots already set */
 static int enqueue_experts(fomoe_b200_ctx_t *c, const fb_args_t *a) {
+    if (c->act_f32) {
+        CKL(c, fb_launch_gate_up_f32(a, grid_tasks(c, a->n_slots * a->gate_groups), c->stream));
+        CKL(c, fb_launch_down_f32(a, grid_tasks(c, a->n_slots * a->down_groups), c->stream));
+        return 0;
+    }
     if (c->variant != 1 || a->n_slots > 15) {
         CKL(c, fb_launch_gate_up(a, grid_tasks(c, a->n_slots * a->gate_groups), c->stream));
         CKL(c, fb_launch_down(a, grid_tasks(c, a->n_slots * a->down_groups), c->stream));
@@ -796,7 +810,7 @@ static int graphs_on(const fomoe_b200_ctx_t *c) { return c->use_graphs && !(c->a
 
 static int stack_kernel_usable(fomoe_b200_ctx_t *c) {
     fb_args_t a;
-    if (c->variant != 2) return 0;
+    if (c->variant != 2 || c->act_f32) return 0;
     if (c->cfg.tp_size > 1 && !c->tp_connected) return 0;
     fill_args(c, 0, &a);
     return fb_stack_supported(&a, c->n_sm);
@@ -1282,6 +1296,8 @@ static int op_engine_get(op_engine_t *o, int n_embd, int inter, int down_type) {
     cfg.car_threshold = 1.0f;
     o->eng = fomoe_b200_create(&cfg);
     if (!o->eng) return -1;
+    const char *act = getenv("FOMOE_B200_ACT"); /* "f32": the reference's fp32-activation definition */
+    if (act && (!strcmp(act, "f32") || !strcmp(act, "F32"))) o->eng->act_f32 = 1;
     o->n_embd = n_embd;
     o->inter = inter;
     o->down_type = down_type;

@@ -95,6 +95,9 @@ int fb_launch_router(const fb_args_t *a, int grid, void *stream);
 int fb_launch_set_slots(const fb_args_t *a, void *stream);
 int fb_launch_gate_up(const fb_args_t *a, int grid, void *stream);
 int fb_launch_down(const fb_args_t *a, int grid, void *stream);
+/* the same two phases with fp32 activations (kernels_f32.cu) */
+int fb_launch_gate_up_f32(const fb_args_t *a, int grid, void *stream);
+int fb_launch_down_f32(const fb_args_t *a, int grid, void *stream);
 /* same phases with weights streamed by bulk copies into per-warp shared-memory rings */
 int fb_launch_gate_up_ring(const fb_args_t *a, int grid, void *stream);
 int fb_launch_down_ring(const fb_args_t *a, int grid, void *stream);

@@ -129,6 +129,16 @@ uint64_t fomoe_b200_table_bytes(fomoe_b200_ctx_t *ctx);
 int fomoe_b200_table_generate(fomoe_b200_ctx_t *ctx, uint64_t seed);
 /* Upload one expert record in ggml order (expert == n_experts addresses the shared expert). */
 int fomoe_b200_table_upload(fomoe_b200_ctx_t *ctx, int layer, int expert, const void *record);
+/* Which of the reference's two definitions of the expert FFN the context computes.  FOMOE_B200_ACT_Q8K (default):
+ * activations quantised to Q8_K int8 blocks, integer dots -- src/cpu_expert.c, the reference's CPU expert engine.
+ * FOMOE_B200_ACT_F32: fp32 activations against dequantised weights -- the reference's CPU forward pass without
+ * cpu_expert (src/inference.c:556-575, dots src/quant.c:109-143, 177-212, 249-262) and, up to summation order, its
+ * GPU kernels.  The two differ by a few percent of the layer output on the same inputs.  The fp32 mode runs on
+ * the per-phase kernels (it is the parity path for that definition, not a tuned one); the environment variable
+ * FOMOE_B200_ACT=f32 selects it for the gpu_expert_ffn / b200_expert_* surfaces. */
+#define FOMOE_B200_ACT_Q8K 0
+#define FOMOE_B200_ACT_F32 1
+int fomoe_b200_set_act_mode(fomoe_b200_ctx_t *ctx, int mode);
 /* Optional scalar gate of the shared expert (src/inference.c:586-592, include/model.h shared_expert_gate): with a
  * vector w[n_embd] uploaded, the shared expert's output is multiplied by sigmoid(h . w) before it is added to the
  * routed sum; NULL removes the gate again (the default: weight 1). */

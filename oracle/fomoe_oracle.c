@@ -269,6 +269,113 @@ float orc_vec_dot_q6_K_q8_K(const void *xv, const void *yv, int nb) {
     return hsum8(acc);
 }
 
+/* ---- fp32-activation dots: src/quant.c:109-143 (Q4_K), 249-262 (Q5_K), 177-212 (Q6_K).  One sum per block, added
+ * to the row sum.  The reference build fuses `sum += w * y` into a multiply-add in the Q4_K loop and not in the
+ * other two (their products are computed first, vectorised, and added in order); each form below is pinned bit for
+ * bit against the compiled reference. ---- */
+static inline float acc_f32(float w, float y, float sum) { return fmaf(w, y, sum); }
+
+float orc_vec_dot_q4_K_f32(const void *xv, const float *y, int64_t n) {
+    const orc_block_q4_K *x = (const orc_block_q4_K *)xv;
+    int64_t nb = n / ORC_QK_K;
+    float sumf = 0.0f;
+    for (int64_t i = 0; i < nb; i++) {
+        const uint8_t *q = x[i].qs;
+        float d = orc_fp16_to_fp32(x[i].d), dmin = orc_fp16_to_fp32(x[i].dmin);
+        float sum = 0.0f;
+        for (int c = 0; c < 4; c++) {
+            uint8_t sc1, m1, sc2, m2;
+            scale_min_k4(2 * c, x[i].scales, &sc1, &m1);
+            scale_min_k4(2 * c + 1, x[i].scales, &sc2, &m2);
+            float d1 = d * (float)sc1, mm1 = dmin * (float)m1, d2 = d * (float)sc2, mm2 = dmin * (float)m2;
+            for (int l = 0; l < 32; l++) sum = acc_f32(d1 * (float)(q[l] & 0xF) - mm1, y[64 * c + l], sum);
+            for (int l = 0; l < 32; l++) sum = acc_f32(d2 * (float)(q[l] >> 4) - mm2, y[64 * c + 32 + l], sum);
+            q += 32;
+        }
+        sumf = sumf + sum;
+        y += ORC_QK_K;
+    }
+    return sumf;
+}
+
+float orc_vec_dot_q5_K_f32(const void *xv, const float *y, int64_t n) {
+    const orc_block_q5_K *x = (const orc_block_q5_K *)xv;
+    int64_t nb = n / ORC_QK_K;
+    float sumf = 0.0f, tmp[ORC_QK_K];
+    for (int64_t i = 0; i < nb; i++) {
+        orc_dequantize_row_q5_K(&x[i], tmp, ORC_QK_K);
+        float sum = 0.0f;
+        for (int j = 0; j < ORC_QK_K; j++) sum = sum + tmp[j] * y[i * ORC_QK_K + j];
+        sumf = sumf + sum;
+    }
+    return sumf;
+}
+
+float orc_vec_dot_q6_K_f32(const void *xv, const float *y, int64_t n) {
+    const orc_block_q6_K *x = (const orc_block_q6_K *)xv;
+    int64_t nb = n / ORC_QK_K;
+    float sumf = 0.0f;
+    for (int64_t i = 0; i < nb; i++) {
+        float d = orc_fp16_to_fp32(x[i].d);
+        float sum = 0.0f;
+        for (int h = 0; h < 2; h++) {
+            const uint8_t *ql = x[i].ql + 64 * h, *qh = x[i].qh + 32 * h;
+            const int8_t *sc = x[i].scales + 8 * h;
+            const float *yp = y + i * ORC_QK_K + 128 * h;
+            for (int l = 0; l < 32; l++) {
+                int is = l / 16;
+                int8_t q1 = (int8_t)((int8_t)((ql[l] & 0xF) | (((qh[l] >> 0) & 3) << 4)) - 32);
+                int8_t q2 = (int8_t)((int8_t)((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32);
+                int8_t q3 = (int8_t)((int8_t)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32);
+                int8_t q4 = (int8_t)((int8_t)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32);
+                sum = sum + d * (float)sc[is + 0] * (float)q1 * yp[l];
+                sum = sum + d * (float)sc[is + 2] * (float)q2 * yp[l + 32];
+                sum = sum + d * (float)sc[is + 4] * (float)q3 * yp[l + 64];
+                sum = sum + d * (float)sc[is + 6] * (float)q4 * yp[l + 96];
+            }
+        }
+        sumf = sumf + sum;
+    }
+    return sumf;
+}
+
+static void matvec_f32(float *out, const void *mat, int type, const float *x, int M, int K) {
+    uint64_t rb = orc_row_bytes(type, K);
+    const uint8_t *m = (const uint8_t *)mat;
+    for (int i = 0; i < M; i++) {
+        const void *row = m + (uint64_t)i * rb;
+        out[i] = type == ORC_TYPE_Q4_K ? orc_vec_dot_q4_K_f32(row, x, K)
+               : type == ORC_TYPE_Q5_K ? orc_vec_dot_q5_K_f32(row, x, K) : orc_vec_dot_q6_K_f32(row, x, K);
+    }
+}
+
+/* ---- src/inference.c:556-575 (routed experts: silu(gate) * up, down, out += score * down; the reference build
+ * fuses that multiply-add) and 361-374, 582-596 (shared expert, added with weight 1) ---- */
+void orc_moe_block_f32(float *out, const float *h, const void *const *experts, const float *scores, int k,
+                       const void *shared_data, int gate_type, int up_type, int down_type, uint64_t gate_size,
+                       uint64_t up_size, int n_embd, int inter) {
+    float *g = (float *)malloc(sizeof(float) * (size_t)inter);
+    float *u = (float *)malloc(sizeof(float) * (size_t)inter);
+    float *dn = (float *)malloc(sizeof(float) * (size_t)n_embd);
+    memset(out, 0, sizeof(float) * (size_t)n_embd);
+    for (int i = 0; i <= k; i++) {
+        const uint8_t *e = (const uint8_t *)(i < k ? experts[i] : shared_data);
+        if (!e) break;
+        matvec_f32(g, e, gate_type, h, inter, n_embd);
+        for (int r = 0; r < inter; r++) g[r] = g[r] / (1.0f + expf(-g[r]));
+        matvec_f32(u, e + gate_size, up_type, h, inter, n_embd);
+        for (int r = 0; r < inter; r++) g[r] = g[r] * u[r];
+        matvec_f32(dn, e + gate_size + up_size, down_type, g, n_embd, inter);
+        if (i < k)
+            for (int r = 0; r < n_embd; r++) out[r] = fmaf(scores[i], dn[r], out[r]);
+        else
+            for (int r = 0; r < n_embd; r++) out[r] = out[r] + dn[r];
+    }
+    free(g);
+    free(u);
+    free(dn);
+}
+
 /* ---- src/cpu_expert.c:52-72 ---- */
 void orc_matvec_q8(float *out, const void *mat, int type, const void *q8, int M, int K) {
     int nb = K / ORC_QK_K;

@@ -60,6 +60,14 @@ void orc_quantize_row_q8_K(const float *x, void *y, int64_t k);            /* sr
 float orc_vec_dot_q4_K_q8_K(const void *x, const void *y, int nb);         /* src/quant.c:405-476 */
 float orc_vec_dot_q5_K_q8_K(const void *x, const void *y, int nb);         /* src/quant.c:609-621 */
 float orc_vec_dot_q6_K_q8_K(const void *x, const void *y, int nb);         /* src/quant.c:478-607 */
+/* fp32-activation dots, the reference's second definition of the same products (its CPU forward pass without
+ * cpu_expert and, up to summation order, its GPU kernels) */
+float orc_vec_dot_q4_K_f32(const void *x, const float *y, int64_t n);      /* src/quant.c:109-143 */
+float orc_vec_dot_q5_K_f32(const void *x, const float *y, int64_t n);      /* src/quant.c:249-262 */
+float orc_vec_dot_q6_K_f32(const void *x, const float *y, int64_t n);      /* src/quant.c:177-212 */
+void orc_moe_block_f32(float *out, const float *h, const void *const *experts, const float *scores, int k,
+                       const void *shared_data, int gate_type, int up_type, int down_type, uint64_t gate_size,
+                       uint64_t up_size, int n_embd, int inter);            /* src/inference.c:556-596 */
 uint64_t orc_row_bytes(int type, int k);                                   /* include/quant_types.h:93-97 */
 
 /* out[i] = vec_dot(row_i, q8); src/cpu_expert.c:52-72 */

@@ -92,6 +92,8 @@ class _Common:
         g("moe").argtypes = [_f32p, _f32p, C.POINTER(C.c_void_p), _f32p, C.c_int, C.c_void_p, C.c_int,
                              C.c_int, C.c_int, C.c_uint64, C.c_uint64, C.c_int, C.c_int]
         g("moe").restype = None
+        g("moe_f32").argtypes = g("moe").argtypes
+        g("moe_f32").restype = None
 
     def _f(self, k):
         return getattr(self.lib, self.n[k])
@@ -163,14 +165,15 @@ class _Common:
         return ids, scores, all_scores, subs
 
     def moe_block(self, h, experts, scores, shared, gate_type, up_type, down_type, gate_size, up_size,
-                  n_embd, inter):
-        """experts: list of uint8 arrays (gate|up|down records); shared: uint8 array or None."""
+                  n_embd, inter, act_f32=False):
+        """experts: list of uint8 arrays (gate|up|down records); shared: uint8 array or None.
+        act_f32: the reference's fp32-activation definition instead of the Q8_K one of cpu_expert.c."""
         h, scores = _f32(h), _f32(scores)
         keep = [_u8(e) for e in experts]
         ptrs = (C.c_void_p * len(keep))(*[e.ctypes.data for e in keep])
         sh = _u8(shared) if shared is not None else None
         out = np.empty(n_embd, dtype=np.float32)
-        self._f("moe")(_fp(out), _fp(h), ptrs, _fp(scores), len(keep), _vp(sh) if sh is not None else None,
+        self._f("moe_f32" if act_f32 else "moe")(_fp(out), _fp(h), ptrs, _fp(scores), len(keep), _vp(sh) if sh is not None else None,
                        gate_type, up_type, down_type, gate_size, up_size, n_embd, inter)
         return out
 
@@ -184,7 +187,7 @@ class Oracle(_Common):
                                    q8="orc_quantize_row_q8_K", dot4="orc_vec_dot_q4_K_q8_K",
                                    dot6="orc_vec_dot_q6_K_q8_K", fp16="orc_fp16_to_fp32",
                                    softmax="orc_softmax", topk="orc_top_k", rms="orc_rms_norm",
-                                   route="orc_route", moe="orc_moe_block"))
+                                   route="orc_route", moe="orc_moe_block", moe_f32="orc_moe_block_f32"))
         lib.orc_car.argtypes = [_i32p, _f32p, C.c_int, _f32p, C.c_int, C.c_void_p, C.c_float, C.c_int]
         lib.orc_car.restype = C.c_int
         lib.orc_router_logits.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int]
@@ -239,7 +242,7 @@ class Ref(_Common):
                                    q8="quantize_row_q8_K", dot4="vec_dot_q4_K_q8_K",
                                    dot6="vec_dot_q6_K_q8_K", fp16="fp16_to_fp32", softmax="softmax",
                                    topk="top_k", rms="rms_norm", route="refdrv_route",
-                                   moe="refdrv_moe_block"))
+                                   moe="refdrv_moe_block", moe_f32="refdrv_moe_block_f32"))
         lib.mat_vec_mul.argtypes = [_f32p, C.c_void_p, C.c_int, _f32p, C.c_int64, C.c_int64]
         lib.mat_vec_mul.restype = None
         lib.refdrv_car_case.argtypes = [C.c_float, C.c_int, _i32p, _f32p, C.c_int, _f32p, C.c_int, _i32p,

@@ -129,6 +129,32 @@ void refdrv_moe_block(float *out, const float *h, const void *const *experts, co
     }
 }
 
+/* ---- the same block with fp32 activations: the reference's CPU forward pass without cpu_expert
+ * (src/inference.c:556-575 for the routed experts, 361-374 and 582-596 for the shared one), composed from its own
+ * mat_vec_mul / silu / vec_mul / vec_scaled_add / vec_add (src/tensor.c). ---- */
+void refdrv_moe_block_f32(float *out, const float *h, const void *const *experts, const float *scores, int k,
+                          const void *shared_data, int gate_type, int up_type, int down_type,
+                          uint64_t gate_size, uint64_t up_size, int n_embd, int inter) {
+    float *g = (float *)malloc(sizeof(float) * (size_t)inter);
+    float *u = (float *)malloc(sizeof(float) * (size_t)inter);
+    float *dn = (float *)malloc(sizeof(float) * (size_t)n_embd);
+    memset(out, 0, sizeof(float) * (size_t)n_embd);
+    for (int i = 0; i <= k; i++) {
+        const uint8_t *e = (const uint8_t *)(i < k ? experts[i] : shared_data);
+        if (!e) break;
+        mat_vec_mul(g, e, (enum ggml_dtype)gate_type, h, inter, n_embd);
+        silu(g, inter);
+        mat_vec_mul(u, e + gate_size, (enum ggml_dtype)up_type, h, inter, n_embd);
+        vec_mul(g, g, u, inter);
+        mat_vec_mul(dn, e + gate_size + up_size, (enum ggml_dtype)down_type, g, n_embd, inter);
+        if (i < k) vec_scaled_add(out, dn, scores[i], n_embd);
+        else vec_add(out, out, dn, n_embd);
+    }
+    free(g);
+    free(u);
+    free(dn);
+}
+
 /* ---- expert store files: written with the reference's own writer (src/expert_store.c:128-172) so that the
  * loader under test reads exactly what tools/prepare_experts.c produces.  records[l][e] = gate | up | down bytes of
  * expert e of layer l; every expert is padded to a 4096-aligned stride as prepare_experts.c does. ---- */

@@ -47,7 +47,7 @@ def zipf_resident_mask(seed, layer, n_experts, frac=0.4, s=1.1):
 
 
 def oracle_layer(orc, fb, seed, layer, h, n_embd, inter, n_experts, top_k, down_type, has_shared=True, mask=None,
-                 threshold=1.0, dampen=False, router=None, shared_gate_w=None):
+                 threshold=1.0, dampen=False, router=None, shared_gate_w=None, act_f32=False):
     """Router -> top-k -> CAR -> experts (+shared) through a CPU checker (Oracle or Ref)."""
     w = router if router is not None else router_weights(fb, seed, layer, n_experts, n_embd)
     ids, scores, all_scores, subs = orc.route(w, h, top_k, mask, threshold, dampen)
@@ -55,7 +55,7 @@ def oracle_layer(orc, fb, seed, layer, h, n_embd, inter, n_experts, top_k, down_
     experts = [expert_record(fb, seed, layer, int(e), down_type, n_embd, inter) for e in ids]
     shared = expert_record(fb, seed, layer, n_experts, down_type, n_embd, inter) if has_shared else None
     if shared_gate_w is None:
-        out = orc.moe_block(h, experts, scores, shared, Q4, Q4, down_type, gs, gs, n_embd, inter)
+        out = orc.moe_block(h, experts, scores, shared, Q4, Q4, down_type, gs, gs, n_embd, inter, act_f32=act_f32)
         return dict(ids=ids, scores=scores, all_scores=all_scores, subs=subs, out=out)
     # gated shared expert (the reference's src/inference.c:582-596): buf_down *= sigmoid(h . w); ffn += buf_down
     routed = orc.moe_block(h, experts, scores, None, Q4, Q4, down_type, gs, gs, n_embd, inter)

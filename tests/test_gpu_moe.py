@@ -217,6 +217,30 @@ def test_config2_full_shape_stack(fb, oracle):
     d.close()
 
 
+@pytest.mark.parametrize("down_type", [H.Q6, H.Q4, H.Q5])
+def test_fp32_activation_mode(fb, oracle, down_type):
+    """The reference's fp32-activation definition of the expert FFN (its forward pass without cpu_expert, and its GPU
+    kernels): selected per context, compared with the oracle's restatement of that definition; the routing is the
+    same in both modes; switching back restores the Q8_K bits."""
+    n_embd, inter, n_experts, top_k, seed = 4096, 1024, 64, 10, 131
+    d = fb.MoeDecoder(1, n_embd, inter, n_experts, top_k, True, [down_type])
+    d.generate(seed)
+    h = H.hidden(fb, seed, 0, n_embd)
+    q8 = d.moe_layer(0, h)
+    d.set_act_mode(True)
+    got = d.moe_layer(0, h)
+    want = H.oracle_layer(oracle, fb, seed, 0, h, n_embd, inter, n_experts, top_k, down_type, act_f32=True)
+    assert (got["ids"] == want["ids"]).all() and (got["ids"] == q8["ids"]).all()
+    assert H.rel_l2(got["out"], want["out"]) < 2e-5           # fp32 reassociation only
+    assert H.rel_l2(got["out"], q8["out"]) > 1e-3            # a different definition, not a rounding variant
+    x = d.stack_run(h)                                        # whole-stack entry points take the same path
+    assert np.isfinite(x).all()
+    d.set_act_mode(False)
+    assert (H.bits(d.moe_layer(0, h)["out"]) == H.bits(q8["out"])).all()
+    assert d.status() == 0
+    d.close()
+
+
 def test_shared_expert_gate(fb, oracle):
     """Optional scalar gate sigmoid(h . w) on the shared expert (src/inference.c:582-596), per-phase kernels and the
     persistent stack kernel; removing the gate restores the ungated bits."""

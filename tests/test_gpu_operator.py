@@ -45,6 +45,23 @@ def test_gpu_expert_ffn_takes_records_in_device_memory(fb):
     op.close()
 
 
+def test_gpu_expert_ffn_fp32_activation_definition(fb, oracle, monkeypatch):
+    """FOMOE_B200_ACT=f32 makes the operator compute the reference's fp32-activation definition (what its own GPU
+    kernels and its CPU fallback loop, src/inference.c:556-575, compute)."""
+    n_embd, inter, seed, n = 2048, 512, 73, 6
+    monkeypatch.setenv("FOMOE_B200_ACT", "f32")
+    op = fb.GpuOperator()
+    ex = _experts(fb, seed, n, H.Q6, n_embd, inter)
+    h = H.hidden(fb, seed, 0, n_embd)
+    sc = np.random.default_rng(3).dirichlet(np.ones(n)).astype(np.float32)
+    gs = fb.matrix_bytes(H.Q4, inter, n_embd)
+    rc, out = op.expert_ffn(h, ex, sc, n_embd, inter, gs, gs, ex[0].size, H.Q4, H.Q4, H.Q6)
+    assert rc == 0
+    want = oracle.moe_block(h, ex, sc, None, H.Q4, H.Q4, H.Q6, gs, gs, n_embd, inter, act_f32=True)
+    assert H.rel_l2(out, want) < 2e-5
+    op.close()
+
+
 def test_gpu_expert_ffn_rejects_like_the_reference(fb):
     """-1 = "fall back to CPU" for the reference's limits (src/gpu_kernels.hip:8393-8403)."""
     n_embd, inter, seed = 512, 256, 3

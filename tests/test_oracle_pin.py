@@ -131,6 +131,23 @@ def test_oracle_equals_compiled_reference(fb, oracle, ref):
     assert (H.bits(lay_o["out"]) == H.bits(lay_r["out"])).all()
 
 
+@pytest.mark.parametrize("down_type", [H.Q4, H.Q5, H.Q6])
+def test_fp32_activation_definition_equals_compiled_reference(fb, oracle, ref, down_type):
+    """The reference's second definition of the expert FFN (fp32 activations: src/inference.c:556-596 over
+    src/tensor.c and src/quant.c:109-143, 177-212, 249-262), restated and compared bit for bit."""
+    n_embd, inter, seed = 1024, 512, 9
+    ex = [H.expert_record(fb, seed, 0, e, down_type, n_embd, inter) for e in range(4)]
+    sh = H.expert_record(fb, seed, 0, 7, down_type, n_embd, inter)
+    h = H.hidden(fb, seed, 0, n_embd)
+    sc = np.array([.4, .3, .2, .1], dtype=np.float32)
+    gs = fb.matrix_bytes(H.Q4, inter, n_embd)
+    a = oracle.moe_block(h, ex, sc, sh, H.Q4, H.Q4, down_type, gs, gs, n_embd, inter, act_f32=True)
+    b = ref.moe_block(h, ex, sc, sh, H.Q4, H.Q4, down_type, gs, gs, n_embd, inter, act_f32=True)
+    assert (H.bits(a) == H.bits(b)).all()
+    q = ref.moe_block(h, ex, sc, sh, H.Q4, H.Q4, down_type, gs, gs, n_embd, inter)
+    assert 1e-3 < H.rel_l2(q, b) < 0.2      # the two definitions are not interchangeable at the 1e-3 bar
+
+
 def test_q8k_activation_path_differs_from_fp32_path(fb, ref):
     """The parity target is the Q8_K-activation path of src/cpu_expert.c; the fp32-activation matvec of
     src/tensor.c is a different definition (about 1e-2 apart), which is why the kernels quantise."""
