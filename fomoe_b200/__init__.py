@@ -87,6 +87,13 @@ _SIGS = {
     "fomoe_b200_tp_recv_ptr": (C.c_void_p, [C.c_void_p]),
     "fomoe_b200_tp_connect_ptrs": (C.c_int, [C.c_void_p, C.c_void_p]),
     "fomoe_b200_set_wait_limit": (C.c_int, [C.c_void_p, C.c_uint]),
+    "fomoe_b200_tp_enable_peer": (C.c_int, [C.c_void_p, C.c_int]),
+    "fomoe_b200_tp_inject": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_uint]),
+    "fomoe_b200_routing_trace_open": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "fomoe_b200_routing_trace_close": (C.c_int, [C.c_void_p]),
+    "fomoe_b200_enable_expert_freq": (C.c_int, [C.c_void_p]),
+    "fomoe_b200_get_expert_freq": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
+    "fomoe_b200_gpu_attach": (C.c_int, [C.c_void_p, C.c_void_p]),
     "fomoe_b200_set_act_mode": (C.c_int, [C.c_void_p, C.c_int]),
     "fomoe_b200_stream": (C.c_void_p, [C.c_void_p]),
     "fomoe_b200_set_car": (C.c_int, [C.c_void_p, C.c_float, C.c_int]),
@@ -200,7 +207,7 @@ class MoeDecoder:
         self._l = lib()
         self.n_layers, self.n_embd, self.n_inter = n_layers, n_embd, n_inter
         self.n_experts, self.top_k, self.has_shared = n_experts, top_k, bool(has_shared)
-        self.tp_rank, self.tp_size = tp_rank, tp_size
+        self.tp_rank, self.tp_size, self.device = tp_rank, tp_size, device
         self.down_types = list(down_types) if down_types is not None else [TYPE_Q6_K] * n_layers
         self._dt = (C.c_int * n_layers)(*self.down_types)
         cfg = Config(device, n_layers, n_embd, n_inter, n_experts, top_k, int(bool(has_shared)), TYPE_Q4_K,
@@ -236,10 +243,16 @@ class MoeDecoder:
         assert r.size == self.record_bytes(layer), (r.size, self.record_bytes(layer))
         self._ck(self._l.fomoe_b200_table_upload(self._h, layer, expert, r.ctypes.data), "table_upload")
 
+    @property
+    def half_mode(self):
+        """Twice as many ranks as 256-wide windows: two ranks share a window (see the C header)."""
+        return self.tp_size == 2 * (self.n_inter // 256)
+
     def _shard_shape(self, layer, matrix):
+        il = 256 if self.half_mode else self.n_inter // self.tp_size
         if matrix == M_DOWN:
-            return self.down_types[layer], self.n_embd, self.n_inter // self.tp_size
-        return TYPE_Q4_K, self.n_inter // self.tp_size, self.n_embd
+            return self.down_types[layer], self.n_embd, 128 if self.half_mode else il
+        return TYPE_Q4_K, il, self.n_embd
 
     def export_shard(self, layer, expert, matrix):
         """This rank's shard of one matrix, ggml block order, row-major over (rows, column blocks)."""
@@ -385,7 +398,7 @@ class MoeDecoder:
 
     def n_blocks(self):
         import torch
-        return torch.cuda.get_device_properties(0).multi_processor_count
+        return torch.cuda.get_device_properties(self.device).multi_processor_count
 
     def tp_recv_ptr(self):
         return int(self._l.fomoe_b200_tp_recv_ptr(self._h) or 0)
@@ -394,6 +407,30 @@ class MoeDecoder:
         """ptrs: the receive buffers (device addresses) of all tp_size ranks of this process, rank order."""
         arr = (C.c_void_p * len(ptrs))(*ptrs)
         self._ck(self._l.fomoe_b200_tp_connect_ptrs(self._h, arr), "tp_connect_ptrs")
+
+    def tp_enable_peer(self, peer_device):
+        self._ck(self._l.fomoe_b200_tp_enable_peer(self._h, int(peer_device)), "tp_enable_peer")
+
+    def tp_inject(self, src_rank, partial=None, ahead=1):
+        """Host-side stand-in for rank `src_rank`: its partial (zeros if None) for the layer-token `ahead` after the
+        last one launched."""
+        p = None if partial is None else _f32(partial)
+        self._ck(self._l.fomoe_b200_tp_inject(self._h, src_rank, None if p is None else p.ctypes.data, ahead), "tp_inject")
+
+    def trace_open(self, path):
+        """Append a routing-trace record (the reference's format, tools/read_trace.py) per layer and token from now on."""
+        self._ck(self._l.fomoe_b200_routing_trace_open(self._h, path.encode()), "routing_trace_open")
+
+    def trace_close(self):
+        self._ck(self._l.fomoe_b200_routing_trace_close(self._h), "routing_trace_close")
+
+    def enable_expert_freq(self):
+        self._ck(self._l.fomoe_b200_enable_expert_freq(self._h), "enable_expert_freq")
+
+    def expert_freq(self):
+        out = np.zeros((self.n_layers, self.n_experts), dtype=np.uint32)
+        self._ck(self._l.fomoe_b200_get_expert_freq(self._h, out.ctypes.data_as(C.POINTER(C.c_uint32))), "get_expert_freq")
+        return out
 
     def set_wait_limit(self, polls):
         self._ck(self._l.fomoe_b200_set_wait_limit(self._h, int(polls)), "set_wait_limit")
@@ -435,7 +472,7 @@ class MoeDecoder:
     def peek(self, what, n_slots=None):
         """Intermediates of the most recent layer call: 'act', 'q8a', 'q8h', 'dots', 'h'."""
         ns = self.top_k + int(self.has_shared) if n_slots is None else n_slots
-        il = self.n_inter // self.tp_size
+        il = 256 if self.half_mode else self.n_inter // self.tp_size
         sel, dtype, shape = {"act": (0, np.float32, (ns, il)), "q8a": (1, np.uint8, (ns, il // 256, 304)),
                              "q8h": (2, np.uint8, (self.n_embd // 256, 304)),
                              "dots": (3, np.float32, (ns, self.n_embd)), "h": (4, np.float32, (self.n_embd,))}[what]
@@ -474,6 +511,27 @@ class GpuOperator:
             self._h = None
 
     __del__ = close
+
+    def attach(self, decoder):
+        """The statistics calls of this surface (expert histogram, dims) report `decoder` (a MoeDecoder) from now on."""
+        if self._l.fomoe_b200_gpu_attach(self._h, decoder._h if decoder is not None else None) != 0:
+            raise RuntimeError("fomoe_b200_gpu_attach failed")
+
+    def enable_expert_freq(self):
+        self._l.gpu_enable_expert_freq(self._h)
+
+    def expert_dims(self):
+        a, b = C.c_int(0), C.c_int(0)
+        self._l.gpu_get_expert_dims(self._h, C.byref(a), C.byref(b))
+        return a.value, b.value
+
+    def expert_freq(self):
+        """uint32[n_layers, n_experts] or None (not enabled / nothing attached)."""
+        p = self._l.gpu_get_expert_freq(self._h)
+        if not p:
+            return None
+        nl, ne = self.expert_dims()
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint32)), shape=(nl, ne)).copy()
 
     def expert_ffn(self, h, expert_buffers, scores, n_embd, inter, gate_size, up_size, stride, gate_type, up_type,
                    down_type):

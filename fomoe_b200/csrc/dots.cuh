@@ -422,6 +422,101 @@ __device__ __forceinline__ float fb_dot_q6k_sm(const uint4 (&ql)[8], const uint4
     return __fmul_rn(d, (float)total);
 }
 
+/* ---- HALF super-blocks (layout.h): the 128 columns of half `half` (0 or 1) of one block against the same half of
+ * the activation entry at a_u (shared memory).  Same integer arithmetic as the whole-block dots restricted to the
+ * chunks / groups of that half, so the two halves' results add up to the whole block's (the fp32 products
+ * d*isum - dmin*msum are formed per half: one more rounding than the whole block, far inside the parity bound). */
+__device__ __forceinline__ uint2 fb_lds64_a(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ float fb_dot_q4k_half_sm(const uint4 &hdr, const uint4 (&qs)[4], uint32_t a_u, int half) {
+    const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+    /* sub-block scales / mins 4*half .. 4*half+3 (src/quant.c:72-80) */
+    const uint32_t scw = half ? ((u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4)) : (u0 & 0x3f3f3f3fu);
+    const uint32_t mw = half ? (((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4)) : (u1 & 0x3f3f3f3fu);
+    const uint32_t ah_u = a_u + 128u * (uint32_t)half; /* int8 values 128*half .. of the entry */
+    int isum = 0;
+#pragma unroll
+    for (int cc = 0; cc < 2; cc++) {
+        int lo = 0, hi16 = 0;
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            const uint4 w = qs[2 * cc + kk];
+            const uint4 al = fb_lds128_a(ah_u + 16 * (4 * cc + kk));
+            const uint4 ah = fb_lds128_a(ah_u + 16 * (4 * cc + 2 + kk));
+            lo = fb_dp4a(w.x & 0x0f0f0f0fu, al.x, lo);
+            lo = fb_dp4a(w.y & 0x0f0f0f0fu, al.y, lo);
+            lo = fb_dp4a(w.z & 0x0f0f0f0fu, al.z, lo);
+            lo = fb_dp4a(w.w & 0x0f0f0f0fu, al.w, lo);
+            hi16 = fb_dp4a_us(w.x & 0xf0f0f0f0u, ah.x, hi16);
+            hi16 = fb_dp4a_us(w.y & 0xf0f0f0f0u, ah.y, hi16);
+            hi16 = fb_dp4a_us(w.z & 0xf0f0f0f0u, ah.z, hi16);
+            hi16 = fb_dp4a_us(w.w & 0xf0f0f0f0u, ah.w, hi16);
+        }
+        const int s0 = (scw >> (16 * cc)) & 0xff, s1 = (scw >> (16 * cc + 8)) & 0xff;
+        isum += s0 * lo + s1 * (hi16 >> 4);
+    }
+    const uint4 b = fb_lds128_a(a_u + 256 + 16u * (uint32_t)half); /* bsums 8*half .. 8*half+7 */
+    int msum = 0;
+    {
+        const uint32_t d01 = __byte_perm(mw, 0, 0x1100), d23 = __byte_perm(mw, 0, 0x3322);
+        msum = fb_dp2a_lo_su(b.x, d01, msum);
+        msum = fb_dp2a_hi_su(b.y, d01, msum);
+        msum = fb_dp2a_lo_su(b.z, d23, msum);
+        msum = fb_dp2a_hi_su(b.w, d23, msum);
+    }
+    float yd;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(yd) : "r"(a_u + 288));
+    const float d = __fmul_rn(yd, fb_half_bits_to_float(hdr.x & 0xffff));
+    const float dmin = __fmul_rn(yd, fb_half_bits_to_float(hdr.x >> 16));
+    return __fmaf_rn(d, (float)isum, -__fmul_rn(dmin, (float)msum));
+}
+
+__device__ __forceinline__ float fb_dot_q6k_half_sm(const uint4 (&ql)[4], const uint4 (&qh)[2], const uint2 &sc,
+                                                    uint32_t d16, uint32_t a_u, int half) {
+    int totA = 0, totB = 0;
+    const uint32_t ah_u = a_u + 128u * (uint32_t)half;
+#pragma unroll
+    for (int tq = 0; tq < 2; tq++) {
+        const uint4 A = ql[tq], B = ql[2 + tq], H = qh[tq];
+        const uint4 a0 = fb_lds128_a(ah_u + 16 * (0 + tq)), a1 = fb_lds128_a(ah_u + 16 * (2 + tq));
+        const uint4 a2 = fb_lds128_a(ah_u + 16 * (4 + tq)), a3 = fb_lds128_a(ah_u + 16 * (6 + tq));
+        int l0 = 0, l1 = 0, l2 = 0, l3 = 0, h0 = 0, h1 = 0, h2 = 0, h3 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t qa = fb_u4c(A, i), qb = fb_u4c(B, i), hh = fb_u4c(H, i);
+            const uint32_t x0 = fb_u4c(a0, i), x1 = fb_u4c(a1, i), x2 = fb_u4c(a2, i), x3 = fb_u4c(a3, i);
+            l0 = fb_dp4a_us(qa & 0x0f0f0f0fu, x0, l0);
+            h0 = fb_dp4a_us(hh & 0x03030303u, x0, h0);
+            l1 = fb_dp4a_us(qb & 0x0f0f0f0fu, x1, l1);
+            h1 = fb_dp4a_us(hh & 0x0c0c0c0cu, x1, h1);
+            l2 = fb_dp4a_us(qa & 0xf0f0f0f0u, x2, l2);
+            h2 = fb_dp4a_us(hh & 0x30303030u, x2, h2);
+            l3 = fb_dp4a_us(qb & 0xf0f0f0f0u, x3, l3);
+            h3 = fb_dp4a_us(hh & 0xc0c0c0c0u, x3, h3);
+        }
+        const int s0 = (int)(signed char)((sc.x >> (8 * tq)) & 0xff), s1 = (int)(signed char)((sc.x >> (8 * (2 + tq))) & 0xff);
+        const int s2 = (int)(signed char)((sc.y >> (8 * tq)) & 0xff), s3 = (int)(signed char)((sc.y >> (8 * (2 + tq))) & 0xff);
+        totA += s0 * (l0 + 16 * h0) + s1 * (l1 + 4 * h1);
+        totB += s2 * (l2 + 16 * h2) + s3 * (l3 + 4 * h3);
+    }
+    int total = totA + (totB >> 4);
+    const uint4 b = fb_lds128_a(a_u + 256 + 16u * (uint32_t)half);
+    int corr = 0;
+    corr = fb_dp2a_lo_ss(b.x, sc.x, corr);
+    corr = fb_dp2a_hi_ss(b.y, sc.x, corr);
+    corr = fb_dp2a_lo_ss(b.z, sc.y, corr);
+    corr = fb_dp2a_hi_ss(b.w, sc.y, corr);
+    total -= 32 * corr;
+    float yd;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(yd) : "r"(a_u + 288));
+    const float d = __fmul_rn(yd, fb_half_bits_to_float(d16));
+    return __fmul_rn(d, (float)total);
+}
+
 /* Sum over the `span` consecutive lanes (span a power of two <= 32) that share a row. */
 __device__ __forceinline__ float fb_span_sum(float v, int span) {
     for (int o = span >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -30,6 +30,7 @@ typedef struct {
     int down_type;
     float *router_w, *resid, *normw;
     uint32_t *mask; /* device copy of the residency mask */
+    uint32_t mask_host[16];
     int mask_set;
     float *shared_gate_w; /* [n_embd] or NULL */
 } fb_layer_t;
@@ -44,6 +45,8 @@ struct fomoe_b200_ctx {
     uint64_t table_bytes;
     /* geometry */
     int inter_local, gate_bpr, down_bpr, gate_groups, down_groups, n_slots;
+    int gate_part;  /* which inter_local-row slice of gate/up this rank computes */
+    int down_half;  /* -1, or which half of every down super-block this rank owns (twice as many ranks as windows) */
     uint64_t gate_bytes; /* bytes of one gate (or up) shard */
     /* state */
     float *x, *h, *moe_out, *logits, *all_scores, *scores, *act, *dots;
@@ -58,6 +61,12 @@ struct fomoe_b200_ctx {
     /* staging */
     uint8_t *stage;       /* device staging for uploads / exports */
     uint64_t stage_bytes;
+    /* record uploads of the operator surfaces: two staging buffers filled on a copy stream, so that the host never
+     * waits between records and the copy of one record overlaps the regrouping of the one before */
+    uint8_t *stage2;
+    cudaStream_t copy_stream;
+    cudaEvent_t ev_full[2], ev_free[2];
+    int serial_upload;    /* 1: one record at a time with a synchronise after each (comparison arm) */
     float *pin;           /* pinned host scratch, 4 * n_embd floats + routing scratch (mapped into the device) */
     float *pin_dev;       /* the same memory as the device sees it */
     /* graphs */
@@ -79,8 +88,13 @@ struct fomoe_b200_ctx {
     int layer_args_valid;
     unsigned long long *d_trace, *d_ll_dots;
     /* tensor parallelism: this rank's receive buffer and every rank's buffer as mapped here */
-    unsigned long long *tp_recv, *tp_peer[FB_MAX_TP];
-    int tp_connected;
+    unsigned long long *tp_recv, *tp_peer[FB_MAX_TP], *tp_xsum;
+    int tp_connected, tp_two_stage;
+    int *host_flags;      /* in the mapped pinned block: [0] = code of a stack launch that gave a wait up */
+    int last_status;      /* what fomoe_b200_status reports next: the code of the most recent failed run */
+    fb_route_rec_t *route_log; /* [max_tokens + 1][n_layers] routing decisions, or NULL */
+    FILE *trace_fp;            /* routing-trace file being written, or NULL */
+    uint32_t trace_tokens;     /* tokens written to it so far */
     unsigned long long *d_bar;     /* grid barrier words */
     unsigned long long bar_count;  /* arrivals all finished stack launches have added */
     unsigned gen_count;            /* layer-tokens of all finished stack launches */
@@ -133,8 +147,9 @@ static fb_shard_geom_t geom_gate(const fomoe_b200_ctx_t *c) {
     g.type = c->cfg.gate_type;
     g.rows_local = c->inter_local;
     g.bpr_local = g.bpr_full = c->gate_bpr;
-    g.row0 = c->cfg.tp_rank * c->inter_local;
+    g.row0 = c->gate_part * c->inter_local;
     g.b0 = 0;
+    g.half = -1;
     return g;
 }
 
@@ -145,7 +160,8 @@ static fb_shard_geom_t geom_down(const fomoe_b200_ctx_t *c, int type) {
     g.bpr_local = c->down_bpr;
     g.bpr_full = c->cfg.n_inter / FB_QK;
     g.row0 = 0;
-    g.b0 = c->cfg.tp_rank * c->down_bpr;
+    g.b0 = c->gate_part * c->down_bpr;
+    g.half = c->down_half;
     return g;
 }
 
@@ -181,6 +197,15 @@ void fomoe_b200_destroy(fomoe_b200_ctx_t *c) {
     for (int p = 0; p < FB_MAX_TP; p++)
         if (c->tp_connected == 1 && c->tp_peer[p] && c->tp_peer[p] != c->tp_recv) cudaIpcCloseMemHandle(c->tp_peer[p]);
     cudaFree(c->tp_recv);
+    cudaFree(c->tp_xsum);
+    cudaFree(c->route_log);
+    if (c->trace_fp) fclose(c->trace_fp);
+    cudaFree(c->stage2);
+    for (int i = 0; i < 2; i++) {
+        if (c->ev_full[i]) cudaEventDestroy(c->ev_full[i]);
+        if (c->ev_free[i]) cudaEventDestroy(c->ev_free[i]);
+    }
+    if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     cudaFree(c->d_trace); cudaFree(c->stage); cudaFree(c->d_layer_args); cudaFree(c->d_bar); cudaFree(c->d_ll_dots); cudaFree(c->d_abort);
     if (c->pin) cudaFreeHost(c->pin);
     for (int i = 0; i < c->pev_cap; i++) cudaEventDestroy(c->pev[i]);
@@ -215,14 +240,35 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
     const int N = cfg->tp_size > 0 ? cfg->tp_size : 1;
     c->cfg.tp_size = N;
     if (cfg->device < 0 || cfg->device >= ndev || cfg->n_layers < 1 || cfg->n_embd % FB_QK || cfg->n_embd > 8192 ||
-        cfg->n_embd < FB_QK || cfg->n_inter % (FB_QK * N) || cfg->n_inter < FB_QK * N || cfg->n_experts < 1 ||
+        cfg->n_embd < FB_QK || cfg->n_inter % FB_QK || cfg->n_inter < FB_QK || N > FB_MAX_TP || cfg->n_experts < 1 ||
         cfg->n_experts > FB_MAX_EXPERTS || cfg->top_k < 1 || cfg->top_k > FB_MAX_TOPK || cfg->top_k > cfg->n_experts ||
         cfg->gate_type != FB_TYPE_Q4_K || cfg->tp_rank < 0 || cfg->tp_rank >= N) {
         set_err(c, "unsupported configuration");
         free(c);
         return NULL;
     }
-    c->inter_local = cfg->n_inter / N;
+    /* Shards: N ranks over W = n_inter/256 activation windows.  N divides W: rank r owns W/N whole windows (gate/up
+     * rows and down column blocks).  N == 2 W: the ranks 2p and 2p+1 share window p -- both compute its 256 gate/up
+     * rows (quantising a window needs the maximum over all 256 values, src/quant.c:343-375, and recomputing the
+     * partner's 128 rows is cheaper than exchanging maxima between GPUs in the middle of a layer) and each owns
+     * one 128-column half of the down super-blocks of that window. */
+    {
+        const int W = cfg->n_inter / FB_QK;
+        if (N <= W && W % N == 0) {
+            c->inter_local = cfg->n_inter / N;
+            c->gate_part = cfg->tp_rank;
+            c->down_half = -1;
+        } else if (N == 2 * W) {
+            c->inter_local = FB_QK;
+            c->gate_part = cfg->tp_rank >> 1;
+            c->down_half = cfg->tp_rank & 1;
+        } else {
+            set_err(c, "tp_size %d does not divide the %d activation windows of n_inter %d (nor is it twice their number)", N,
+                    W, cfg->n_inter);
+            free(c);
+            return NULL;
+        }
+    }
     c->gate_bpr = cfg->n_embd / FB_QK;
     c->down_bpr = c->inter_local / FB_QK;
     if (!is_pow2(c->gate_bpr) || !is_pow2(c->down_bpr) || c->gate_bpr > 32 || c->down_bpr > 32 ||
@@ -240,8 +286,10 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
     c->down_types = (int *)malloc(sizeof(int) * (size_t)cfg->n_layers);
     for (int l = 0; l < cfg->n_layers; l++) {
         c->down_types[l] = cfg->down_types ? cfg->down_types[l] : FB_TYPE_Q6_K;
-        if (c->down_types[l] != FB_TYPE_Q4_K && c->down_types[l] != FB_TYPE_Q5_K && c->down_types[l] != FB_TYPE_Q6_K) {
-            set_err(c, "layer %d: down type %d unsupported", l, c->down_types[l]);
+        if ((c->down_types[l] != FB_TYPE_Q4_K && c->down_types[l] != FB_TYPE_Q5_K && c->down_types[l] != FB_TYPE_Q6_K) ||
+            (c->down_half >= 0 && c->down_types[l] == FB_TYPE_Q5_K)) {
+            set_err(c, "layer %d: down type %d unsupported%s", l, c->down_types[l],
+                    c->down_half >= 0 ? " for shards of half super-blocks" : "");
             free(c->down_types);
             free(c);
             return NULL;
@@ -264,7 +312,7 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
     for (int l = 0; l < cfg->n_layers; l++) {
         fb_layer_t *L = &c->layers[l];
         L->down_type = c->down_types[l];
-        L->down_bytes = fb_shard_bytes(L->down_type, (uint64_t)cfg->n_embd * c->down_bpr);
+        L->down_bytes = fb_shard_bytes_h(L->down_type, c->down_half, (uint64_t)cfg->n_embd * c->down_bpr);
         L->rec_bytes = 2 * c->gate_bytes + L->down_bytes;
         const uint64_t tb = L->rec_bytes * (uint64_t)n_recs;
         if (cudaMalloc((void **)&L->table, tb) != cudaSuccess) {
@@ -301,10 +349,13 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
         dev_alloc(c, (void **)&c->tok_in, sizeof(float) * (uint64_t)(c->max_tokens + 1) * ne) ||
         dev_alloc(c, (void **)&c->tok_out, sizeof(float) * (uint64_t)(c->max_tokens + 1) * ne))
         goto fail;
-    if (N > 1) { /* [tp_size][n_embd] words; plain cudaMalloc so that it can be shared with the other ranks */
-        if (N > FB_MAX_TP || cudaMalloc((void **)&c->tp_recv, sizeof(unsigned long long) * (size_t)N * ne) != cudaSuccess ||
-            cudaMemset(c->tp_recv, 0, sizeof(unsigned long long) * (size_t)N * ne) != cudaSuccess)
+    if (N > 1) { /* [2][tp_size][n_embd] words; plain cudaMalloc so that it can be shared with the other ranks */
+        if (cudaMalloc((void **)&c->tp_recv, sizeof(unsigned long long) * 2 * (size_t)N * ne) != cudaSuccess ||
+            cudaMemset(c->tp_recv, 0, sizeof(unsigned long long) * 2 * (size_t)N * ne) != cudaSuccess ||
+            dev_alloc(c, (void **)&c->tp_xsum, sizeof(unsigned long long) * (size_t)ne))
             goto fail;
+        /* many ranks: add the partials up once per GPU instead of in every thread (stack.cu) */
+        c->tp_two_stage = getenv("FOMOE_B200_TP_TWO_STAGE") ? atoi(getenv("FOMOE_B200_TP_TWO_STAGE")) : (N >= 4);
     }
     c->stage_bytes = max_rec_ggml > sizeof(float) * (uint64_t)ne * 1024 ? max_rec_ggml : sizeof(float) * (uint64_t)ne * 1024;
     if (cudaMalloc((void **)&c->stage, c->stage_bytes) != cudaSuccess) goto fail;
@@ -312,6 +363,8 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
         cudaSuccess)
         goto fail;
     if (cudaHostGetDevicePointer((void **)&c->pin_dev, c->pin, 0) != cudaSuccess) goto fail;
+    memset(c->pin, 0, sizeof(float) * (4 * (size_t)ne + 4 * FB_MAX_EXPERTS));
+    c->host_flags = (int *)(c->pin + 3 * (size_t)ne);
     return c;
 fail:
     if (!c->err[0]) set_err(c, "CUDA setup failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -321,19 +374,44 @@ fail:
 
 const char *fomoe_b200_last_error(fomoe_b200_ctx_t *c) { return c ? c->err : "null context"; }
 
+/* A stack launch that gave a wait up leaves its barrier words, hand-over words and abort flag in an unknown state:
+ * clear them so that the next launch starts clean.  Generations are NOT reset: every launch, finished or not, has
+ * advanced gen_count by its layer-tokens on every rank that made the call, so the ranks still agree, and no word
+ * an aborted launch left behind (here or in a peer's receive buffer) can ever match a later generation. */
+static void stack_recover(fomoe_b200_ctx_t *c) {
+    cudaMemsetAsync(c->d_abort, 0, sizeof(int), c->stream);
+    cudaMemsetAsync(c->d_bar, 0, 32 * sizeof(unsigned long long), c->stream);
+    cudaMemsetAsync(c->status, 0, sizeof(int), c->stream);
+    cudaStreamSynchronize(c->stream);
+    c->bar_count = 0;
+    c->host_flags[0] = 0;
+}
+
+/* after the synchronise that follows a stack launch: 0, or -1 when a block gave a wait up (the kernel said so in
+ * mapped host memory; no copy is needed to find out) */
+static int stack_finish(fomoe_b200_ctx_t *c) {
+    const int code = c->host_flags[0];
+    if (!code) return 0;
+    c->last_status = code;
+    stack_recover(c);
+    set_err(c, "the stack kernel gave up a bounded wait (status %d): a peer rank did not deliver, or the wait limit is too "
+               "short; results of this call are not valid", code);
+    return -1;
+}
+
 int fomoe_b200_status(fomoe_b200_ctx_t *c) {
     int st = -1;
     if (!c) return -1;
     cudaSetDevice(c->cfg.device);
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1;
     if (cudaMemcpy(&st, c->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (st == FB_ST_WAIT_TIMEOUT) { /* a stack launch gave up half way: its flags are in an unknown state, start over */
-        cudaMemset(c->d_abort, 0, sizeof(int));
-        cudaMemset(c->d_bar, 0, 32 * sizeof(unsigned long long));
-        cudaMemset(c->d_ll_dots, 0, sizeof(unsigned long long) * FB_MAX_SLOTS * (size_t)c->cfg.n_embd);
-        c->bar_count = 0;
-        c->gen_count = 0;
+    if (c->host_flags[0]) { /* a launch whose caller did not synchronise through this library */
+        c->last_status = c->host_flags[0];
+        stack_recover(c);
     }
+    if (st != FB_ST_OK) cudaMemset(c->status, 0, sizeof(int));
+    if (c->last_status) st = c->last_status;
+    c->last_status = 0; /* reported once: a later successful run reads 0 again */
     return st;
 }
 
@@ -466,6 +544,174 @@ int fomoe_b200_set_graphs(fomoe_b200_ctx_t *c, int enable) {
     return 0;
 }
 
+/* ------------------------------------------------------------------ routing trace, expert histogram
+ * The reference writes one record per layer and token to the file named by QMOE_TRACE_FILE: a 32-byte header and
+ * packed records of token id, layer id, the top-k before and after cache-aware routing with their weights, and
+ * where each expert came from (src/gpu_kernels.hip:451-484, written at 6306-6340, read by tools/read_trace.py).
+ * Here the kernels log every decision on the device (fb_route_rec_t) and the host appends the records after each
+ * run.  Arrays hold top_k entries and the record is padded to a multiple of 8 bytes, which is what
+ * tools/read_trace.py parses and, for top_k = 10, byte for byte the reference's 144-byte record.  Source codes: every
+ * expert is in HBM here, so an expert the residency mask marks as cached (or any expert when no mask is set) is
+ * "VRAM" (0), one it does not is what the reference would have fetched: "NVMe" (2); a substituted slot is "CAR" (3),
+ * a slot whose weight ended at zero "DROP" (4). */
+#define FB_TRACE_MAGIC 0x54524345u
+
+int fomoe_b200_routing_trace_open(fomoe_b200_ctx_t *c, const char *path) {
+    if (!c || !path) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    if (c->trace_fp) fclose(c->trace_fp);
+    c->trace_fp = fopen(path, "wb");
+    if (!c->trace_fp) {
+        set_err(c, "cannot create routing trace %s", path);
+        return -1;
+    }
+    if (!c->route_log) {
+        if (dev_alloc(c, (void **)&c->route_log, sizeof(fb_route_rec_t) * (size_t)(c->max_tokens + 1) * c->cfg.n_layers)) return -1;
+        drop_graph(c); /* the kernels' arguments change */
+    }
+    uint8_t hd[32];
+    memset(hd, 0, sizeof(hd));
+    const uint32_t magic = FB_TRACE_MAGIC, version = 1;
+    const uint16_t nl = (uint16_t)c->cfg.n_layers, ne = (uint16_t)c->cfg.n_experts, tk = (uint16_t)c->cfg.top_k;
+    memcpy(hd, &magic, 4);
+    memcpy(hd + 4, &version, 4);
+    memcpy(hd + 8, &nl, 2);
+    memcpy(hd + 10, &ne, 2);
+    memcpy(hd + 12, &tk, 2);
+    c->trace_tokens = 0;
+    return fwrite(hd, 1, 32, c->trace_fp) == 32 ? 0 : -1;
+}
+
+int fomoe_b200_routing_trace_close(fomoe_b200_ctx_t *c) {
+    if (!c) return -1;
+    int rc = 0;
+    if (c->trace_fp) rc = fclose(c->trace_fp) ? -1 : 0;
+    c->trace_fp = NULL;
+    return rc;
+}
+
+/* records of tokens [first, first + count) x layers [l0, l1) from the device log to the file */
+static int trace_append(fomoe_b200_ctx_t *c, int first, int count, int l0, int l1) {
+    if (!c->trace_fp || !c->route_log) return 0;
+    const int nl = c->cfg.n_layers, k = c->cfg.top_k;
+    const size_t nrec = (size_t)count * nl;
+    fb_route_rec_t *h = (fb_route_rec_t *)malloc(sizeof(fb_route_rec_t) * nrec);
+    if (!h) return -1;
+    if (cudaMemcpy(h, c->route_log + (size_t)first * nl, sizeof(fb_route_rec_t) * nrec, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        free(h);
+        set_err(c, "routing trace: copy failed");
+        return -1;
+    }
+    const size_t raw = 8 + (size_t)k * (2 + 4 + 2 + 4 + 1), rec_bytes = (raw + 7) & ~(size_t)7;
+    uint8_t *buf = (uint8_t *)calloc(1, rec_bytes);
+    int rc = buf ? 0 : -1;
+    for (int t = 0; t < count && !rc; t++) {
+        for (int l = l0; l < l1 && !rc; l++) {
+            const fb_route_rec_t *r = &h[(size_t)t * nl + l];
+            const fb_layer_t *L = &c->layers[l];
+            memset(buf, 0, rec_bytes);
+            const uint32_t tok = c->trace_tokens + (uint32_t)t;
+            const uint16_t lid = (uint16_t)l;
+            uint8_t n_subs = 0;
+            uint8_t *o_ids = buf + 8, *o_sc = o_ids + 2 * k, *f_ids = o_sc + 4 * k, *f_sc = f_ids + 2 * k, *src = f_sc + 4 * k;
+            for (int i = 0; i < k; i++) {
+                const int16_t oi = (int16_t)r->ids_orig[i], fi = (int16_t)r->ids[i];
+                memcpy(o_ids + 2 * i, &oi, 2);
+                memcpy(o_sc + 4 * i, &r->scores_orig[i], 4);
+                memcpy(f_ids + 2 * i, &fi, 2);
+                memcpy(f_sc + 4 * i, &r->scores[i], 4);
+                const int e = r->ids_orig[i];
+                const int resident = !L->mask_set || ((L->mask_host[(e >> 5) & 15] >> (e & 31)) & 1u);
+                uint8_t s = resident ? 0 : 2;
+                if (r->ids[i] != r->ids_orig[i]) {
+                    s = 3;
+                    n_subs++;
+                } else if (r->scores[i] == 0.0f)
+                    s = 4;
+                src[i] = s;
+            }
+            memcpy(buf, &tok, 4);
+            memcpy(buf + 4, &lid, 2);
+            buf[6] = (uint8_t)k;
+            buf[7] = n_subs;
+            if (fwrite(buf, 1, rec_bytes, c->trace_fp) != rec_bytes) rc = -1;
+        }
+    }
+    c->trace_tokens += (uint32_t)count;
+    free(buf);
+    free(h);
+    if (rc) set_err(c, "routing trace: write failed");
+    return rc;
+}
+
+/* Histogram of the routed expert ids before substitution, [n_layers][n_experts] counters since it was enabled (the
+ * reference: gpu_enable_expert_freq / gpu_get_expert_freq, include/gpu.h:50-57, counted at src/gpu_kernels.hip:7832-7835). */
+int fomoe_b200_enable_expert_freq(fomoe_b200_ctx_t *c) {
+    if (!c) return -1;
+    if (c->freq) return 0;
+    CK(c, cudaSetDevice(c->cfg.device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    if (dev_alloc(c, (void **)&c->freq, sizeof(uint32_t) * (size_t)c->cfg.n_layers * c->cfg.n_experts)) return -1;
+    drop_graph(c);
+    return 0;
+}
+
+int fomoe_b200_get_expert_freq(fomoe_b200_ctx_t *c, uint32_t *out) {
+    if (!c || !out || !c->freq) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    CK(c, cudaMemcpy(out, c->freq, sizeof(uint32_t) * (size_t)c->cfg.n_layers * c->cfg.n_experts, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+/* Ranks in one process: let this context's device store into `peer_device`'s memory. */
+int fomoe_b200_tp_enable_peer(fomoe_b200_ctx_t *c, int peer_device) {
+    if (!c) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    if (peer_device == c->cfg.device) return 0;
+    int can = 0;
+    CK(c, cudaDeviceCanAccessPeer(&can, c->cfg.device, peer_device));
+    if (!can) {
+        set_err(c, "device %d cannot access device %d", c->cfg.device, peer_device);
+        return -1;
+    }
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+        set_err(c, "cudaDeviceEnablePeerAccess(%d): %s", peer_device, cudaGetErrorString(e));
+        return -1;
+    }
+    cudaGetLastError();
+    return 0;
+}
+
+/* Diagnostic stand-in for a rank: writes `partial` (n_embd floats, NULL = zeros) into this context's receive buffer
+ * as rank src_rank's contribution to the layer-token that lies `ahead` layer-tokens after the last one launched
+ * (ahead = 1: the first layer-token of the next call).  Lets a test, or a supervisor that has lost a rank, feed a
+ * rank's share from the host instead of from a peer GPU. */
+int fomoe_b200_tp_inject(fomoe_b200_ctx_t *c, int src_rank, const float *partial, unsigned ahead) {
+    if (!c || !c->tp_recv || src_rank < 0 || src_rank >= c->cfg.tp_size || ahead < 1) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    const int n = c->cfg.n_embd;
+    const uint32_t gen = c->gen_count + ahead;
+    unsigned long long *w = (unsigned long long *)malloc(sizeof(unsigned long long) * (size_t)n);
+    if (!w) return -1;
+    for (int i = 0; i < n; i++) {
+        uint32_t bits = 0;
+        if (partial) memcpy(&bits, &partial[i], 4);
+        w[i] = ((unsigned long long)gen << 32) | bits;
+    }
+    const cudaError_t e = cudaMemcpy(c->tp_recv + ((size_t)(gen & 1u) * c->cfg.tp_size + src_rank) * n, w,
+                                     sizeof(unsigned long long) * (size_t)n, cudaMemcpyHostToDevice);
+    free(w);
+    if (e != cudaSuccess) {
+        set_err(c, "tp_inject: %s", cudaGetErrorString(e));
+        return -1;
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------ table */
 int fomoe_b200_table_generate(fomoe_b200_ctx_t *c, uint64_t seed) {
     if (!c) return -1;
@@ -499,33 +745,76 @@ static int check_rec(fomoe_b200_ctx_t *c, int layer, int expert) {
     return 0;
 }
 
-/* enqueue: H2D of one ggml record + repack of its three matrices into record slot `expert` */
-static int upload_record(fomoe_b200_ctx_t *c, int layer, int expert, const void *record) {
+/* enqueue: H2D of one ggml record + repack of its three matrices into record slot `expert`.  down_type: 0 = the
+ * layer's own; the one-layer engines behind the operator surfaces take whatever type a call brings (their record
+ * slots are sized for the largest).  stage_idx < 0: the single staging buffer on the context's stream (the caller
+ * synchronises before reusing it); >= 0: staging buffer stage_idx & 1, filled on the copy stream. */
+static int upload_record(fomoe_b200_ctx_t *c, int layer, int expert, const void *record, int down_type, int stage_idx) {
     fb_layer_t *L = &c->layers[layer];
+    const int dt = down_type ? down_type : L->down_type;
     const uint64_t gb = ggml_matrix_bytes(c->cfg.gate_type, c->cfg.n_inter, c->cfg.n_embd);
-    const uint64_t rb = fomoe_b200_record_bytes(c, layer);
+    const uint64_t rb = 2 * gb + ggml_matrix_bytes(dt, c->cfg.n_embd, c->cfg.n_inter);
     uint8_t *dst = L->table + (uint64_t)expert * L->rec_bytes;
     /* `record` may be a host pointer (the reference's callers, src/inference.c:538-549: staged through a device
      * buffer) or memory of this GPU (an expert that a caller already keeps in device memory: repacked where it lies) */
     const uint8_t *src = c->stage;
     struct cudaPointerAttributes at;
+    int buf = -1;
     if (cudaPointerGetAttributes(&at, record) == cudaSuccess && at.type == cudaMemoryTypeDevice &&
         at.device == c->cfg.device) {
         src = (const uint8_t *)record;
     } else {
         cudaGetLastError(); /* an unregistered host pointer is not an error */
-        CK(c, cudaMemcpyAsync(c->stage, record, rb, cudaMemcpyDefault, c->stream));
+        if (rb > c->stage_bytes) {
+            set_err(c, "record of %llu bytes exceeds the staging buffer", (unsigned long long)rb);
+            return -1;
+        }
+        if (stage_idx < 0) {
+            CK(c, cudaMemcpyAsync(c->stage, record, rb, cudaMemcpyDefault, c->stream));
+        } else {
+            buf = stage_idx & 1;
+            if (!c->copy_stream) {
+                CK(c, cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+                CK(c, cudaMalloc((void **)&c->stage2, c->stage_bytes));
+                for (int i = 0; i < 2; i++) {
+                    CK(c, cudaEventCreateWithFlags(&c->ev_full[i], cudaEventDisableTiming));
+                    CK(c, cudaEventCreateWithFlags(&c->ev_free[i], cudaEventDisableTiming));
+                }
+            }
+            uint8_t *stg = buf ? c->stage2 : c->stage;
+            src = stg;
+            CK(c, cudaStreamWaitEvent(c->copy_stream, c->ev_free[buf], 0)); /* its previous contents have been regrouped */
+            CK(c, cudaMemcpyAsync(stg, record, rb, cudaMemcpyDefault, c->copy_stream));
+            CK(c, cudaEventRecord(c->ev_full[buf], c->copy_stream));
+            CK(c, cudaStreamWaitEvent(c->stream, c->ev_full[buf], 0));
+        }
     }
+    fb_shard_geom_t gd = geom_down(c, dt);
     CKL(c, fb_launch_repack(dst, src, geom_gate(c), c->stream));
     CKL(c, fb_launch_repack(dst + c->gate_bytes, src + gb, geom_gate(c), c->stream));
-    CKL(c, fb_launch_repack(dst + 2 * c->gate_bytes, src + 2 * gb, geom_down(c, L->down_type), c->stream));
+    CKL(c, fb_launch_repack(dst + 2 * c->gate_bytes, src + 2 * gb, gd, c->stream));
+    if (buf >= 0) CK(c, cudaEventRecord(c->ev_free[buf], c->stream));
+    return 0;
+}
+
+/* records [0, n) of layer 0 from the caller's buffers, without the host waiting in between */
+static int upload_records(fomoe_b200_ctx_t *c, int n, void *const *records, const b200_expert_work_t *work, int down_type) {
+    for (int e = 0; e < n; e++) {
+        const void *r = records ? records[e] : work[e].expert_data;
+        if (!r) return -1;
+        if (c->serial_upload) {
+            if (upload_record(c, 0, e, r, down_type, -1)) return -1;
+            CK(c, cudaStreamSynchronize(c->stream));
+        } else if (upload_record(c, 0, e, r, down_type, e))
+            return -1;
+    }
     return 0;
 }
 
 int fomoe_b200_table_upload(fomoe_b200_ctx_t *c, int layer, int expert, const void *record) {
     if (!c || !record || check_rec(c, layer, expert)) return -1;
     CK(c, cudaSetDevice(c->cfg.device));
-    if (upload_record(c, layer, expert, record)) return -1;
+    if (upload_record(c, layer, expert, record, 0, -1)) return -1;
     CK(c, cudaStreamSynchronize(c->stream)); /* the staging buffer is reused by the next call */
     return 0;
 }
@@ -615,6 +904,10 @@ int fomoe_b200_table_export(fomoe_b200_ctx_t *c, int layer, int expert, int matr
     const uint8_t *shard;
     fb_shard_geom_t g;
     if (!c || !out || shard_of(c, layer, expert, matrix, &shard, &g)) return -1;
+    if (g.half >= 0) {
+        set_err(c, "table_export: a shard of half super-blocks has no ggml form (use table_dequant)");
+        return -1;
+    }
     CK(c, cudaSetDevice(c->cfg.device));
     const uint64_t bytes = (uint64_t)g.rows_local * g.bpr_local * fb_block_bytes(g.type);
     CKL(c, fb_launch_export_ggml(c->stage, shard, g, c->stream));
@@ -628,7 +921,7 @@ int fomoe_b200_table_dequant(fomoe_b200_ctx_t *c, int layer, int expert, int mat
     fb_shard_geom_t g;
     if (!c || !out || shard_of(c, layer, expert, matrix, &shard, &g)) return -1;
     CK(c, cudaSetDevice(c->cfg.device));
-    const uint64_t bytes = sizeof(float) * (uint64_t)g.rows_local * g.bpr_local * FB_QK;
+    const uint64_t bytes = sizeof(float) * (uint64_t)g.rows_local * g.bpr_local * (g.half >= 0 ? FB_QK / 2 : FB_QK);
     float *tmp = NULL;
     CK(c, cudaMalloc((void **)&tmp, bytes));
     int rc = fb_launch_dequant(tmp, shard, g, c->stream);
@@ -687,6 +980,7 @@ int fomoe_b200_set_resident_mask(fomoe_b200_ctx_t *c, int layer, const uint32_t 
     drop_graph(c);
     c->layers[layer].mask_set = mask != NULL;
     if (mask) {
+        memcpy(c->layers[layer].mask_host, mask, sizeof(uint32_t) * 16);
         CK(c, cudaMemcpyAsync(c->layers[layer].mask, mask, sizeof(uint32_t) * 16, cudaMemcpyHostToDevice, c->stream));
         CK(c, cudaStreamSynchronize(c->stream));
     }
@@ -726,6 +1020,7 @@ static void fill_args(const fomoe_b200_ctx_t *c, int layer, fb_args_t *a) {
     a->table_layer = L->table;
     a->rec_bytes = L->rec_bytes;
     a->down_type = L->down_type;
+    a->down_half = c->down_half;
     a->router_w = L->router_w;
     a->resid = L->resid;
     a->normw = L->normw;
@@ -751,6 +1046,8 @@ static void fill_args(const fomoe_b200_ctx_t *c, int layer, fb_args_t *a) {
     a->tok_in = c->tok_in;
     a->tok_out = c->tok_out;
     a->tok_ctr = c->tok_ctr;
+    a->route_log = c->route_log ? c->route_log + layer : NULL;
+    a->route_stride = c->cfg.n_layers;
 }
 
 static int grid_router(const fomoe_b200_ctx_t *c) {
@@ -788,6 +1085,7 @@ static int enqueue_stack(fomoe_b200_ctx_t *c, int l0, int l1, int load_store) {
     fb_args_t a;
     for (int l = l0; l < l1; l++) {
         fill_args(c, l, &a);
+        if (!load_store) a.route_log = NULL; /* the log is indexed by the token counter, which only token runs set */
         int flags = FB_PRO_RESID | FB_PRO_NORM | FB_PRO_QUANT;
         if (l > l0) flags |= FB_PRO_ADD_PREV;
         else if (load_store) flags |= FB_PRO_LOAD;
@@ -851,10 +1149,13 @@ static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int first, i
     k.tp_size = c->cfg.tp_size;
     k.tp_recv = c->tp_recv;
     for (int p = 0; p < FB_MAX_TP; p++) k.tp_peer[p] = c->tp_peer[p];
+    k.tp_xsum = c->tp_xsum;
+    k.tp_two_stage = c->tp_two_stage;
+    k.host_flags = (int *)(c->pin_dev + 3 * (size_t)c->cfg.n_embd);
     k.trace = c->d_trace;
     k.trace_cap = c->d_trace ? c->trace_cap : 0;
     k.trace_cta = c->trace_cta;
-    /* the abort flag is zero unless an earlier launch gave up; fomoe_b200_status clears it again */
+    /* the abort flag is zero unless an earlier launch gave up; stack_finish / fomoe_b200_status clear it again */
     CKL(c, fb_launch_stack(&k, c->n_sm, c->stream));
     /* grid barriers per layer-token: logits, activations and (one GPU only; tensor-parallel ranks exchange the
      * block output through their receive buffers instead) the block output; every block arrives once at each */
@@ -870,6 +1171,7 @@ int fomoe_b200_moe_layer(fomoe_b200_ctx_t *c, int layer, const float *h, float *
     const size_t nb = sizeof(float) * c->cfg.n_embd;
     fb_args_t a;
     fill_args(c, layer, &a);
+    a.route_log = NULL; /* single-layer calls are not part of a token's trace */
     memcpy(c->pin, h, nb);
     CK(c, cudaMemcpyAsync(c->x, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
     CKL(c, fb_launch_prologue(&a, FB_PRO_QUANT, c->stream));
@@ -888,7 +1190,7 @@ int fomoe_b200_moe_layer(fomoe_b200_ctx_t *c, int layer, const float *h, float *
 
 /* shared by moe_layer_routed and the operator surfaces: n experts given by the caller */
 static int run_routed(fomoe_b200_ctx_t *c, int layer, const float *h, const int *ids, const float *scores, int n,
-                      int with_shared, int accumulate, float *out, int sync) {
+                      int with_shared, int accumulate, float *out, int sync, int down_type) {
     if (n < 1 || n > FB_MAX_TOPK) {
         set_err(c, "n experts %d out of range", n);
         return -1;
@@ -900,6 +1202,8 @@ static int run_routed(fomoe_b200_ctx_t *c, int layer, const float *h, const int 
         c->pin_busy = 0;
     }
     fill_args(c, layer, &a);
+    a.route_log = NULL;
+    if (down_type) a.down_type = down_type; /* operator surfaces: the type of this call's records */
     a.top_k = n;
     a.has_shared = with_shared ? 1 : 0;
     a.n_slots = n + a.has_shared;
@@ -937,7 +1241,7 @@ int fomoe_b200_moe_layer_routed(fomoe_b200_ctx_t *c, int layer, const float *h, 
         return -1;
     }
     CK(c, cudaSetDevice(c->cfg.device));
-    return run_routed(c, layer, h, ids, scores, n, c->cfg.has_shared, 0, out, 1);
+    return run_routed(c, layer, h, ids, scores, n, c->cfg.has_shared, 0, out, 1, 0);
 }
 
 int fomoe_b200_stack_run(fomoe_b200_ctx_t *c, const float *x_in, int l0, int l1, float *x_out) {
@@ -953,8 +1257,9 @@ int fomoe_b200_stack_run(fomoe_b200_ctx_t *c, const float *x_in, int l0, int l1,
         CK(c, cudaMemcpyAsync(c->tok_in + (size_t)c->max_tokens * c->cfg.n_embd, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
         if (launch_stack_kernel(c, l0, l1, c->max_tokens, 1, c->pin_dev + c->cfg.n_embd)) return -1;
         CK(c, cudaStreamSynchronize(c->stream));
+        if (stack_finish(c)) return -1; /* x_out is left untouched */
         memcpy(x_out, c->pin + c->cfg.n_embd, nb);
-        return 0;
+        return trace_append(c, c->max_tokens, 1, l0, l1);
     }
     CK(c, cudaMemcpyAsync(c->x, c->pin, nb, cudaMemcpyHostToDevice, c->stream));
     if (enqueue_stack(c, l0, l1, 0)) return -1;
@@ -1019,7 +1324,8 @@ int fomoe_b200_tokens_run(fomoe_b200_ctx_t *c, int first, int count, float *elap
         CK(c, cudaEventRecord(c->ev1, c->stream));
         CK(c, cudaStreamSynchronize(c->stream));
         if (elapsed_ms) CK(c, cudaEventElapsedTime(elapsed_ms, c->ev0, c->ev1));
-        return 0;
+        if (stack_finish(c)) return -1;
+        return trace_append(c, first, count, 0, c->cfg.n_layers);
     }
     if (graphs_on(c) && !c->graph_exec && build_graph(c)) return -1;
     CK(c, cudaMemcpyAsync(c->tok_ctr, &f, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
@@ -1034,7 +1340,7 @@ int fomoe_b200_tokens_run(fomoe_b200_ctx_t *c, int first, int count, float *elap
     CK(c, cudaEventRecord(c->ev1, c->stream));
     CK(c, cudaStreamSynchronize(c->stream));
     if (elapsed_ms) CK(c, cudaEventElapsedTime(elapsed_ms, c->ev0, c->ev1));
-    return 0;
+    return trace_append(c, first, count, 0, c->cfg.n_layers);
 }
 
 /* records an event before each kernel launch while profiling; the phase is read off the call text */
@@ -1111,8 +1417,9 @@ int fomoe_b200_decode_token(fomoe_b200_ctx_t *c, const float *x_in, float *x_out
         /* one copy in, one launch, one synchronise: the kernel writes the result into the pinned buffer itself */
         if (launch_stack_kernel(c, 0, c->cfg.n_layers, c->max_tokens, 1, c->pin_dev + c->cfg.n_embd)) return -1;
         CK(c, cudaStreamSynchronize(c->stream));
+        if (stack_finish(c)) return -1; /* x_out is left untouched */
         memcpy(x_out, c->pin + c->cfg.n_embd, nb);
-        return 0;
+        return c->trace_fp ? trace_append(c, c->max_tokens, 1, 0, c->cfg.n_layers) : 0;
     }
     CK(c, cudaMemcpyAsync(c->tok_ctr, slot, sizeof(unsigned), cudaMemcpyHostToDevice, c->stream));
     if (graphs_on(c)) {
@@ -1123,7 +1430,7 @@ int fomoe_b200_decode_token(fomoe_b200_ctx_t *c, const float *x_in, float *x_out
     CK(c, cudaMemcpyAsync(c->pin + c->cfg.n_embd, c->tok_out + spare, nb, cudaMemcpyDeviceToHost, c->stream));
     CK(c, cudaStreamSynchronize(c->stream));
     memcpy(x_out, c->pin + c->cfg.n_embd, nb);
-    return 0;
+    return trace_append(c, c->max_tokens, 1, 0, c->cfg.n_layers);
 }
 
 int fomoe_b200_get_routing(fomoe_b200_ctx_t *c, int layer, int *ids, float *scores, int *ids_orig) {
@@ -1170,7 +1477,7 @@ int fomoe_b200_matvec(fomoe_b200_ctx_t *c, int type, const void *w, int rows, in
         return -1;
     }
     CK(c, cudaSetDevice(c->cfg.device));
-    fb_shard_geom_t g = {type, rows, bpr, 0, 0, bpr};
+    fb_shard_geom_t g = {type, rows, bpr, 0, 0, bpr, -1};
     const uint64_t wb = ggml_matrix_bytes(type, rows, cols), sb = fb_shard_bytes(type, (uint64_t)rows * bpr);
     uint8_t *dw = NULL, *ds = NULL;
     float *dx = NULL, *dy = NULL;
@@ -1270,16 +1577,19 @@ void fomoe_b200_synth_f32(uint64_t seed, int layer, int stream_id, float mean, f
 
 typedef struct {
     fomoe_b200_ctx_t *eng;
-    int n_embd, inter, down_type;
+    int n_embd, inter;
 } op_engine_t;
 
-static int op_engine_get(op_engine_t *o, int n_embd, int inter, int down_type) {
-    if (o->eng && o->n_embd == n_embd && o->inter == inter && o->down_type == down_type) return 0;
+/* One engine per shape serves every down type: its record slots are sized for the largest block format (Q6_K) and
+ * the type of a call's records travels with the call.  (The 397B model alternates Q6_K and Q4_K down projections
+ * from layer to layer; an engine per type, rebuilt on every change, would allocate and free on every layer.) */
+static int op_engine_get(op_engine_t *o, int n_embd, int inter) {
+    if (o->eng && o->n_embd == n_embd && o->inter == inter) return 0;
     if (o->eng) fomoe_b200_destroy(o->eng);
     o->eng = NULL;
     fomoe_b200_config_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    int dev = 0;
+    int dev = 0, down_type = FB_TYPE_Q6_K;
     cudaGetDevice(&dev);
     cfg.device = dev;
     cfg.n_layers = 1;
@@ -1298,14 +1608,16 @@ static int op_engine_get(op_engine_t *o, int n_embd, int inter, int down_type) {
     if (!o->eng) return -1;
     const char *act = getenv("FOMOE_B200_ACT"); /* "f32": the reference's fp32-activation definition */
     if (act && (!strcmp(act, "f32") || !strcmp(act, "F32"))) o->eng->act_f32 = 1;
+    const char *ser = getenv("FOMOE_B200_SERIAL_UPLOAD"); /* comparison arm: a synchronise after every record */
+    if (ser && atoi(ser)) o->eng->serial_upload = 1;
     o->n_embd = n_embd;
     o->inter = inter;
-    o->down_type = down_type;
     return 0;
 }
 
 struct gpu_ctx {
     op_engine_t op;
+    fomoe_b200_ctx_t *dec; /* decoder whose routing the statistics calls report (fomoe_b200_gpu_attach), or NULL */
     uint32_t *freq_host;
     int freq_enabled;
 };
@@ -1358,17 +1670,32 @@ int gpu_seed_vram_cache(gpu_ctx_t *ctx, void *model, const char *path) {
     (void)ctx; (void)model; (void)path;
     return 0;
 }
+/* The reference counts expert selections inside its own forward pass (src/gpu_kernels.hip:7832-7835).  The operator
+ * gpu_expert_ffn receives its routing from the caller, so there is nothing to count there; the counters of this
+ * surface are those of the decoder context attached to it, which routes on the device. */
+int fomoe_b200_gpu_attach(gpu_ctx_t *ctx, fomoe_b200_ctx_t *dec) {
+    if (!ctx) return -1;
+    ctx->dec = dec;
+    if (dec && ctx->freq_enabled) return fomoe_b200_enable_expert_freq(dec);
+    return 0;
+}
 void gpu_enable_expert_freq(gpu_ctx_t *ctx) {
-    if (ctx) ctx->freq_enabled = 1;
+    if (!ctx) return;
+    ctx->freq_enabled = 1;
+    if (ctx->dec) fomoe_b200_enable_expert_freq(ctx->dec);
 }
 const uint32_t *gpu_get_expert_freq(gpu_ctx_t *ctx) {
-    (void)ctx;
-    return NULL; /* the operator form receives its routing from the caller; nothing to count */
+    if (!ctx || !ctx->freq_enabled || !ctx->dec || !ctx->dec->freq) return NULL; /* NULL when not enabled, include/gpu.h:52 */
+    const size_t n = (size_t)ctx->dec->cfg.n_layers * ctx->dec->cfg.n_experts;
+    uint32_t *p = (uint32_t *)realloc(ctx->freq_host, sizeof(uint32_t) * n);
+    if (!p) return NULL;
+    ctx->freq_host = p;
+    if (fomoe_b200_get_expert_freq(ctx->dec, p)) return NULL;
+    return p; /* owned by the context: the caller does not free it */
 }
 void gpu_get_expert_dims(gpu_ctx_t *ctx, int *n_layers, int *n_experts) {
-    (void)ctx;
-    if (n_layers) *n_layers = 0;
-    if (n_experts) *n_experts = 0;
+    if (n_layers) *n_layers = (ctx && ctx->dec) ? ctx->dec->cfg.n_layers : 0;
+    if (n_experts) *n_experts = (ctx && ctx->dec) ? ctx->dec->cfg.n_experts : 0;
 }
 void gpu_get_pingpong_relay_stats(gpu_ctx_t *ctx, uint64_t *handoffs, uint64_t *payload_bytes, uint64_t *d2h_bytes,
                                   uint64_t *h2d_bytes, uint64_t *dma_bytes) {
@@ -1396,15 +1723,12 @@ int gpu_expert_ffn(gpu_ctx_t *ctx, const float *h, void **expert_buffers, const 
     if (expert_gate_size != ggml_matrix_bytes(gate_type, expert_intermediate, n_embd) ||
         expert_up_size != ggml_matrix_bytes(up_type, expert_intermediate, n_embd))
         return -1;
-    if (op_engine_get(&ctx->op, n_embd, expert_intermediate, down_type)) return -1;
+    if (op_engine_get(&ctx->op, n_embd, expert_intermediate)) return -1;
     fomoe_b200_ctx_t *c = ctx->op.eng;
     int ids[OP_MAX_EXPERTS];
-    for (int e = 0; e < n_experts; e++) {
-        if (!expert_buffers[e] || upload_record(c, 0, e, expert_buffers[e])) return -1;
-        if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1; /* staging buffer reuse */
-        ids[e] = e;
-    }
-    return run_routed(c, 0, h, ids, expert_scores, n_experts, 0, 0, ffn_out, 1);
+    for (int e = 0; e < n_experts; e++) ids[e] = e;
+    if (upload_records(c, n_experts, expert_buffers, NULL, down_type)) return -1;
+    return run_routed(c, 0, h, ids, expert_scores, n_experts, 0, 0, ffn_out, 1, down_type);
 }
 
 struct b200_expert_ctx {
@@ -1461,15 +1785,14 @@ static int expert_batch(b200_expert_ctx_t *x, const float *input, const b200_exp
             work[i].down_type != work[0].down_type || !work[i].expert_data)
             return -1;
     const int had = x->op.eng != NULL;
-    if (op_engine_get(&x->op, x->n_embd, x->inter, work[0].down_type)) return -1;
+    if (op_engine_get(&x->op, x->n_embd, x->inter)) return -1;
     fomoe_b200_ctx_t *c = x->op.eng;
     if (!had || !x->dirty) cudaMemsetAsync(c->moe_out, 0, sizeof(float) * (size_t)x->n_embd, c->stream);
     int ids[OP_MAX_WORK];
     float sc[OP_MAX_WORK];
     cudaEventRecord(x->e0, c->stream);
+    if (upload_records(c, n, NULL, work, work[0].down_type)) return -1;
     for (int i = 0; i < n; i++) {
-        if (upload_record(c, 0, i, work[i].expert_data)) return -1;
-        if (cudaStreamSynchronize(c->stream) != cudaSuccess) return -1;
         ids[i] = i;
         sc[i] = work[i].score;
     }
@@ -1478,7 +1801,7 @@ static int expert_batch(b200_expert_ctx_t *x, const float *input, const b200_exp
     while (done < n) {
         const int m = n - done > FB_MAX_TOPK ? FB_MAX_TOPK : n - done;
         if (run_routed(c, 0, (done == 0 && !x->input_valid) ? input : NULL, ids + done, sc + done, m, 0,
-                       accumulate || done > 0, NULL, 0))
+                       accumulate || done > 0, NULL, 0, work[0].down_type))
             return -1;
         x->input_valid = 1;
         done += m;

@@ -30,6 +30,18 @@
 #define FULL 0xffffffffu
 #endif
 
+/* template selectors of the down kernels for shards of half super-blocks (never stored anywhere) */
+#define FB_TYPE_Q4_K_H 112
+#define FB_TYPE_Q6_K_H 114
+
+/* cudaFuncSetAttribute holds for one device: remember per device ordinal whether it has been done */
+#define FB_MAX_DEVICES 64
+static bool fb_device_once(unsigned char (&done)[FB_MAX_DEVICES], int &dev) {
+    dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= FB_MAX_DEVICES) dev = 0;
+    return done[dev] != 0;
+}
+
 __device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
     /* weights are read exactly once: keep them out of L1 */
     uint4 v;
@@ -245,7 +257,25 @@ __global__ void __launch_bounds__(256) k_down(fb_args_t A) {
         const uint8_t *rec = A.slot_rec[slot] + A.down_off;
         const uint4 *a = smem + (slot * bpr + lane % bpr) * FB_Q8_U4;
         float f;
-        if (TYPE == FB_TYPE_Q4_K) {
+        if (TYPE == FB_TYPE_Q4_K_H) { /* half super-blocks: one half-block per row, 32 rows per group */
+            const uint4 *p = reinterpret_cast<const uint4 *>(rec + (uint64_t)rg * FB_Q4K_HGROUP) + lane;
+            const uint4 hd = ldg_stream(p);
+            uint4 q[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) q[i] = ldg_stream(p + 32 * (i + 1));
+            f = fb_dot_q4k_half_sm(hd, q, fb_smem_u32(a), A.down_half);
+        } else if (TYPE == FB_TYPE_Q6_K_H) {
+            const uint8_t *gb = rec + (uint64_t)rg * FB_Q6K_HGROUP;
+            const uint4 *p = reinterpret_cast<const uint4 *>(gb) + lane;
+            uint4 ql[4], qh[2];
+#pragma unroll
+            for (int i = 0; i < 4; i++) ql[i] = ldg_stream(p + 32 * i);
+#pragma unroll
+            for (int i = 0; i < 2; i++) qh[i] = ldg_stream(p + 32 * (4 + i));
+            const uint2 sc = __ldg(reinterpret_cast<const uint2 *>(gb + FB_Q6K_HOFF_SC) + lane);
+            const uint32_t d16 = __ldg(reinterpret_cast<const unsigned short *>(gb + FB_Q6K_HOFF_D) + lane);
+            f = fb_dot_q6k_half_sm(ql, qh, sc, d16, fb_smem_u32(a), A.down_half);
+        } else if (TYPE == FB_TYPE_Q4_K) {
             const uint4 *p = reinterpret_cast<const uint4 *>(rec + (uint64_t)rg * FB_Q4K_GROUP) + lane;
             uint4 hd = ldg_stream(p);
             uint4 q[8];
@@ -535,28 +565,34 @@ extern "C" int fb_launch_gate_up(const fb_args_t *a, int grid, void *stream) {
 
 extern "C" int fb_launch_gate_up_ring(const fb_args_t *a, int grid, void *stream) {
     const size_t sm = (size_t)GU_WARPS * GU_STAGES * GU_STAGE_BYTES + (size_t)GU_WARPS * GU_STAGES * 8;
-    static int configured = 0;
-    if (!configured) {
+    static unsigned char configured[FB_MAX_DEVICES];
+    int dev;
+    if (!fb_device_once(configured, dev)) {
         cudaError_t e = cudaFuncSetAttribute(k_gate_up_ring, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
         if (e != cudaSuccess) return (int)e;
-        configured = 1;
+        configured[dev] = 1;
     }
     k_gate_up_ring<<<grid, GU_WARPS * 32, sm, (cudaStream_t)stream>>>(*a);
     return (int)cudaGetLastError();
 }
 
 extern "C" int fb_launch_down_ring(const fb_args_t *a, int grid, void *stream) {
-    if (a->down_type == FB_TYPE_Q5_K) return fb_launch_down(a, grid, stream); /* no ring variant for Q5_K */
+    if (a->down_type == FB_TYPE_Q5_K || a->down_half >= 0) {
+        /* no ring variant for Q5_K or half super-blocks: the plain kernel with its own grid (8 warps per block) */
+        const int tasks = a->n_slots * a->down_groups, g = (tasks + 7) / 8;
+        return fb_launch_down(a, g < 1 ? 1 : (g > 2 * grid ? 2 * grid : g), stream);
+    }
     const int ns = a->n_slots;
     const size_t sm = (size_t)ns * DN_STAGES * DN_STAGE_BYTES + sizeof(float) * 2 * ns * 32 + 8 * (ns * DN_STAGES + 4);
-    static int configured = 0;
-    if (!configured) {
+    static unsigned char configured[FB_MAX_DEVICES];
+    int dev;
+    if (!fb_device_once(configured, dev)) {
         const int mx = FB_MAX_SLOTS * DN_STAGES * DN_STAGE_BYTES + 4 * 2 * FB_MAX_SLOTS * 32 + 8 * (FB_MAX_SLOTS * DN_STAGES + 4);
         cudaError_t e = cudaFuncSetAttribute(k_down_ring<FB_TYPE_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, mx);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(k_down_ring<FB_TYPE_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, mx);
         if (e != cudaSuccess) return (int)e;
-        configured = 1;
+        configured[dev] = 1;
     }
     if (a->down_type == FB_TYPE_Q4_K)
         k_down_ring<FB_TYPE_Q4_K><<<grid, (ns + 1) * 32, sm, (cudaStream_t)stream>>>(*a);
@@ -567,7 +603,14 @@ extern "C" int fb_launch_down_ring(const fb_args_t *a, int grid, void *stream) {
 
 extern "C" int fb_launch_down(const fb_args_t *a, int grid, void *stream) {
     const size_t sm = (size_t)a->n_slots * a->down_bpr * sizeof(fb_q8_entry_t);
-    if (a->down_type == FB_TYPE_Q4_K)
+    if (a->down_half >= 0) {
+        if (a->down_type == FB_TYPE_Q4_K)
+            k_down<FB_TYPE_Q4_K_H><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
+        else if (a->down_type == FB_TYPE_Q6_K)
+            k_down<FB_TYPE_Q6_K_H><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
+        else
+            return (int)cudaErrorInvalidValue;
+    } else if (a->down_type == FB_TYPE_Q4_K)
         k_down<FB_TYPE_Q4_K><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
     else if (a->down_type == FB_TYPE_Q5_K)
         k_down<FB_TYPE_Q5_K><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);

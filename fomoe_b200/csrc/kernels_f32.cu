@@ -219,11 +219,13 @@ __global__ void __launch_bounds__(256) k_down_f32(fb_args_t A) {
 
 extern "C" int fb_launch_gate_up_f32(const fb_args_t *a, int grid, void *stream) {
     const size_t sm = sizeof(float) * (size_t)a->n_embd;
-    static int configured = 0;
-    if (!configured) {
+    static unsigned char configured[64]; /* the attribute holds for one device */
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(k_gate_up_f32, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
         if (e != cudaSuccess) return (int)e;
-        configured = 1;
+        configured[dev] = 1;
     }
     if (sm > 128 * 1024) return (int)cudaErrorInvalidValue;
     k_gate_up_f32<<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
@@ -232,15 +234,18 @@ extern "C" int fb_launch_gate_up_f32(const fb_args_t *a, int grid, void *stream)
 
 extern "C" int fb_launch_down_f32(const fb_args_t *a, int grid, void *stream) {
     const size_t sm = sizeof(float) * (size_t)a->n_slots * a->inter_local;
-    static int configured = 0;
-    if (!configured) {
+    if (a->down_half >= 0) return (int)cudaErrorInvalidValue; /* the fp32 definition is not built for half super-blocks */
+    static unsigned char configured[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(k_down_f32<FB_TYPE_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(k_down_f32<FB_TYPE_Q5_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(k_down_f32<FB_TYPE_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         if (e != cudaSuccess) return (int)e;
-        configured = 1;
+        configured[dev] = 1;
     }
     if (sm > 160 * 1024) return (int)cudaErrorInvalidValue;
     if (a->down_type == FB_TYPE_Q4_K)

@@ -34,6 +34,16 @@ typedef struct {
 
 #define FB_MAX_TP 8 /* tensor-parallel ranks */
 
+/* Routing decision of one layer-token as the kernels log it (when a log is attached): the top-k before cache-aware
+ * routing with its renormalised weights, and what was used.  The host turns these into the reference's routing-trace
+ * records (src/gpu_kernels.hip:451-484). */
+typedef struct {
+    int ids_orig[16];
+    float scores_orig[16];
+    int ids[16];
+    float scores[16];
+} fb_route_rec_t;
+
 /* Argument block passed by value to every hot-path kernel. */
 typedef struct {
     /* shapes */
@@ -48,6 +58,7 @@ typedef struct {
     const uint8_t *table_layer; /* record of expert e at table_layer + e * rec_bytes; shared expert = index n_experts */
     uint64_t rec_bytes;
     int down_type;
+    int down_half;            /* -1: the down shard holds whole super-blocks; 0 / 1: that half of every super-block */
     const float *router_w;    /* [n_experts][n_embd] */
     const float *resid;       /* [n_embd] or NULL */
     const float *normw;       /* [n_embd] or NULL */
@@ -75,6 +86,8 @@ typedef struct {
     const float *tok_in;   /* device-resident token inputs [max_tokens][n_embd] */
     float *tok_out;        /* device-resident token outputs */
     unsigned *tok_ctr;     /* index of the token in flight */
+    fb_route_rec_t *route_log; /* NULL, or this layer's record of token 0; token t's lies route_stride records on */
+    int route_stride;
 } fb_args_t;
 
 #define FB_CNT_ROUTER 0
@@ -120,11 +133,16 @@ typedef struct {
     int *abort_flag;         /* raised by a block that gave up a wait; cleared by the host before a launch */
     int *status;
     /* tensor parallelism: the combine step stores this rank's partial block output into slot tp_rank of every
-     * rank's receive buffer ([tp_size][n_embd] {generation, value} words); tp_peer[p] is rank p's buffer as mapped
-     * into this process (tp_peer[tp_rank] == tp_recv, this GPU's own) */
+     * rank's receive buffer ({generation, value} words, double-buffered by generation parity so that a fast rank can
+     * never overwrite words a slow block of a peer still has to read); tp_peer[p] is rank p's buffer as mapped into
+     * this process (tp_peer[tp_rank] == tp_recv, this GPU's own) */
     int tp_rank, tp_size;
-    unsigned long long *tp_recv;
+    unsigned long long *tp_recv;     /* [2][tp_size][n_embd]: words of generation g lie in half g & 1 */
     unsigned long long *tp_peer[FB_MAX_TP];
+    unsigned long long *tp_xsum;     /* [n_embd] {generation, value}: the rank-ordered sum, formed once per GPU */
+    int tp_two_stage;                /* 1: a few warps add the ranks' partials up and publish the sum in tp_xsum,
+                                        everyone else reads that; 0: every thread polls every rank's slot itself */
+    int *host_flags;                 /* mapped host memory: [0] receives the status code of a block that gave up */
     unsigned long long *trace; /* optional phase stamps of one block (profiling), or NULL */
     int trace_cap, trace_cta;
 } fb_stack_args_t;
@@ -138,6 +156,7 @@ typedef struct {
     int type;
     int rows_local, bpr_local; /* shard geometry */
     int row0, b0, bpr_full;    /* position of the shard inside the full matrix */
+    int half;                  /* -1 whole super-blocks; 0 / 1: the shard holds that half of each of its blocks */
 } fb_shard_geom_t;
 
 /* generate expert `e`'s matrix stream (seed, layer, e, matrix) for e in [0, n_recs) straight into

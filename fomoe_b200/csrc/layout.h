@@ -23,6 +23,18 @@
  * by column blocks), so with bpr blocks per row a group covers 32/bpr consecutive rows.
  * Shards whose block count is not a multiple of 32 are padded with zero blocks at the end
  * (never the case at the 397B shape).
+ *
+ * HALF super-blocks (down shards when twice as many tensor-parallel ranks as 256-column windows share an expert:
+ * each rank then owns 128 columns of every row).  Both halves of a Q6_K block are self-contained apart from the
+ * fp16 d (src/quant.c:157-173); the halves of a Q4_K block share the 12 scale bytes (src/quant.c:72-80), so the
+ * 16-byte header is stored with both halves.  Half h of block L:
+ *
+ *   Q4_K half group (2560 B):  uint4 hdr[32]      the full header {d | dmin<<16, scales[0..11]}
+ *                              uint4 qs[4][32]    bytes 64h+16k .. 64h+16k+15 of block L's qs
+ *   Q6_K half group (3392 B):  uint4 ql[4][32]    bytes 64h+16k .. of block L's ql
+ *                              uint4 qh[2][32]    bytes 32h+16k .. of block L's qh
+ *                              uint2 sc[32]       scales 8h .. 8h+7
+ *                              uint16 d[32]
  */
 #ifndef FOMOE_B200_LAYOUT_H
 #define FOMOE_B200_LAYOUT_H
@@ -43,6 +55,13 @@
 #define FB_Q6K_OFF_QH 4096u
 #define FB_Q6K_OFF_SC 6144u
 #define FB_Q6K_OFF_D 6656u
+#define FB_Q4K_HALF 80u
+#define FB_Q6K_HALF 106u
+#define FB_Q4K_HGROUP (FB_Q4K_HALF * FB_GROUP) /* 2560 */
+#define FB_Q6K_HGROUP (FB_Q6K_HALF * FB_GROUP) /* 3392 */
+#define FB_Q6K_HOFF_QH 2048u
+#define FB_Q6K_HOFF_SC 3072u
+#define FB_Q6K_HOFF_D 3328u
 
 #define FB_MAX_SLOTS 16   /* routed experts per token + shared expert */
 #define FB_MAX_TOPK 15
@@ -58,10 +77,19 @@ FB_HD uint64_t fb_block_bytes(int type) {
     return type == FB_TYPE_Q4_K ? FB_Q4K_BLOCK : type == FB_TYPE_Q5_K ? FB_Q5K_BLOCK : type == FB_TYPE_Q6_K ? FB_Q6K_BLOCK : 0;
 }
 FB_HD uint64_t fb_group_bytes(int type) { return fb_block_bytes(type) * FB_GROUP; }
+/* the same for a shard of half super-blocks (half = 0 or 1; half < 0: whole blocks); Q5_K has no half form */
+FB_HD uint64_t fb_block_bytes_h(int type, int half) {
+    if (half < 0) return fb_block_bytes(type);
+    return type == FB_TYPE_Q4_K ? FB_Q4K_HALF : type == FB_TYPE_Q6_K ? FB_Q6K_HALF : 0;
+}
+FB_HD uint64_t fb_group_bytes_h(int type, int half) { return fb_block_bytes_h(type, half) * FB_GROUP; }
 FB_HD uint64_t fb_n_groups(uint64_t n_blocks) { return (n_blocks + FB_GROUP - 1) / FB_GROUP; }
 /* bytes of a shard of n_blocks blocks in the device layout */
 FB_HD uint64_t fb_shard_bytes(int type, uint64_t n_blocks) {
     return fb_n_groups(n_blocks) * fb_group_bytes(type);
+}
+FB_HD uint64_t fb_shard_bytes_h(int type, int half, uint64_t n_blocks) {
+    return fb_n_groups(n_blocks) * fb_group_bytes_h(type, half);
 }
 
 #endif

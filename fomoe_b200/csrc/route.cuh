@@ -146,8 +146,16 @@ static __device__ void fb_route_select(const fb_args_t &A, int lane, bool leader
         const float sinv = __fdiv_rn(1.0f, ssum);
         for (int r = 0; r < k; r++) cand_v[r] = __fmul_rn(cand_v[r], sinv);
     }
+    /* the routing log (when attached) keeps this layer-token's decision for the trace writer */
+    fb_route_rec_t *rec = (leader && A.route_log) ? A.route_log + (size_t)(*A.tok_ctr) * A.route_stride : nullptr;
     if (lane == 0)
-        for (int r = 0; r < k; r++) A.ids_orig[r] = cand_id[r];
+        for (int r = 0; r < k; r++) {
+            A.ids_orig[r] = cand_id[r];
+            if (rec) {
+                rec->ids_orig[r] = cand_id[r];
+                rec->scores_orig[r] = cand_v[r];
+            }
+        }
     if (leader && A.freq && lane < k) {
         int e = 0;
         for (int r = 0; r < k; r++)
@@ -244,6 +252,10 @@ static __device__ void fb_route_select(const fb_args_t &A, int lane, bool leader
             A.ids[r] = e;
             A.scores[r] = cand_v[r];
             A.slot_rec[r] = A.table_layer + (uint64_t)e * A.rec_bytes;
+            if (rec) {
+                rec->ids[r] = e;
+                rec->scores[r] = cand_v[r];
+            }
         }
         if (A.has_shared) {
             A.ids[k] = nE;

@@ -160,10 +160,11 @@ static __device__ __noinline__ int fb_select_car(const fb_args_t &A, fb_sel_smem
 
 /* Must be called by all 512 threads of the block.  Outputs (shared memory): ids[n_slots], scores[n_slots],
  * ids_orig[top_k], slot_rec[n_slots], all_scores[n_experts].  `leader` updates the global counters;
- * `shared_score` is the weight of the shared expert's slot. */
+ * `shared_score` is the weight of the shared expert's slot; `rec` (leader only, may be NULL) receives the decision
+ * for the routing trace. */
 __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const float *h_smem, float *all_scores, int *ids,
                                 int *ids_orig, float *scores, const uint8_t **slot_rec, bool leader,
-                                float shared_score = 1.0f) {
+                                float shared_score = 1.0f, fb_route_rec_t *rec = nullptr) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nE = A.n_experts, k = A.top_k, kk = min(k + 1, nE);
     float lg = (tid < nE) ? __ldcg(A.logits + tid) : -INFINITY;
@@ -271,7 +272,13 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
             W->cv[lane] = cv;
             W->ci[lane] = ci;
         }
-        if (lane < k) ids_orig[lane] = ci;
+        if (lane < k) {
+            ids_orig[lane] = ci;
+            if (rec) { /* routing log: the decision before cache-aware routing */
+                rec->ids_orig[lane] = ci;
+                rec->scores_orig[lane] = cv;
+            }
+        }
         __syncwarp();
         if (leader && A.freq && lane < k) atomicAdd(A.freq + W->ci[lane], 1u);
 
@@ -287,6 +294,10 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
             ids[lane] = e;
             scores[lane] = W->cv[lane];
             slot_rec[lane] = A.table_layer + (uint64_t)e * A.rec_bytes;
+            if (rec) {
+                rec->ids[lane] = e;
+                rec->scores[lane] = W->cv[lane];
+            }
         }
         if (lane == 0) {
             if (A.has_shared) {

@@ -66,6 +66,7 @@ struct sk_bar_t {
     unsigned long long *ctr;  /* [0] arrivals, [16] generation of the last completed barrier */
     int *abort_flag;
     int *status;
+    int *host_flags;          /* mapped host memory: the host learns of a given-up wait without a copy */
     unsigned grid;
     unsigned long long base;  /* arrivals before this launch */
     unsigned limit;           /* polls before a wait is given up */
@@ -82,6 +83,16 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
     unsigned long long v;
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
+}
+
+/* A wait ran out: release every other block (abort flag), record why for fomoe_b200_status, and tell the host,
+ * which reads the mapped word after its synchronise and reports the call as failed. */
+__device__ __forceinline__ void sk_give_up(const sk_bar_t &B) {
+    atomicExch(B.abort_flag, 1);
+    atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
+    if (B.host_flags) {
+        asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(B.host_flags), "r"((int)FB_ST_WAIT_TIMEOUT) : "memory");
+    }
 }
 
 /* Grid barrier.  Arrivals are counted on one cache line (an atomic that returns the count, so the last block
@@ -115,10 +126,7 @@ __device__ __forceinline__ bool sk_wait(const sk_bar_t &B, sk_smem_t *S) {
                 break;
             }
         }
-        if (!ok) {
-            atomicExch(B.abort_flag, 1);
-            atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
-        }
+        if (!ok) sk_give_up(B);
         S->ok = ok;
     }
     __syncthreads();
@@ -150,12 +158,18 @@ __device__ __forceinline__ void sk_put_sys(sk_word_t *p, float v, uint32_t gen) 
 }
 
 /* Tensor-parallel output exchange, receiving side.  Every rank's combine step has stored its partial block output
- * into slot `src` of EVERY rank's receive buffer ([tp_size][n_embd] words, in this GPU's own memory).  A thread
- * polls its 8 elements of every slot until all carry `gen`, then adds the partials in rank order, so all ranks
- * form bit-identical sums (the reference's tp_allreduce_sum, src/tp.hip:85-124, has the same meaning: out = p_0 +
- * p_1 on both ranks).  false = gave up. */
+ * into slot `src` of EVERY rank's receive buffer ([2][tp_size][n_embd] words in this GPU's own memory; the words of
+ * generation g lie in half g & 1).  A thread polls its 8 elements of every slot until all carry `gen`, then adds the
+ * partials in rank order, so all ranks form bit-identical sums (the reference's tp_allreduce_sum,
+ * src/tp.hip:85-124, has the same meaning: out = p_0 + p_1 on both ranks).  false = gave up.
+ *
+ * Why two halves: a rank may store generation g+1 as soon as it has gathered g from everyone, which does not mean
+ * that every block of every peer has read ITS g yet.  With the halves, g+2 is the first generation that reuses
+ * g's words, and a rank stores g+2 only after gathering g+1 from every peer; a peer stores g+1 only after all its
+ * blocks have passed the grid barriers of that layer, i.e. after all of them have read g. */
 __device__ __forceinline__ bool sk_gather8(const sk_word_t *recv, int tp, int n, int e0, uint32_t gen, float (&v)[8],
                                            const int *abort_flag, unsigned limit) {
+    recv += (size_t)(gen & 1u) * tp * n;
 #pragma unroll
     for (int k = 0; k < 8; k++) v[k] = 0.0f;
     for (int src = 0; src < tp; src++) { /* rank order: every rank forms the same sum */
@@ -177,6 +191,57 @@ __device__ __forceinline__ bool sk_gather8(const sk_word_t *recv, int tp, int n,
         if (!got) return false;
     }
     return true;
+}
+
+/* The same exchange in two steps, for many ranks: polling tp slots one after the other costs tp dependent trips to
+ * L2 in every thread of every block.  Step 1: one warp per 32 elements (128 warps on the whole GPU for n = 4096)
+ * polls ALL ranks' words of its elements at once -- one word per rank and lane, so few registers -- adds them in rank
+ * order and publishes the sum as a {generation, value} word in xsum (this GPU's memory).  Step 2: every thread reads
+ * its 8 elements from xsum.  Two dependent trips whatever the number of ranks, and tp x fewer words polled. */
+__device__ __forceinline__ bool sk_reduce_elem(const sk_word_t *recv, sk_word_t *xsum, int tp, int n, int e, uint32_t gen,
+                                               const int *abort_flag, unsigned limit) {
+    const sk_word_t *p = recv + (size_t)(gen & 1u) * tp * n + e;
+    float s = 0.0f;
+    for (int s0 = 0; s0 < tp; s0 += 4) { /* four ranks at a time: eight registers of words in flight */
+        sk_word_t w[4];
+        unsigned need = (tp - s0 >= 4) ? 15u : ((1u << (tp - s0)) - 1u);
+        for (unsigned nsp = 0; nsp < limit && need; nsp++) {
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                if ((need >> k) & 1u)
+                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w[k]) : "l"(p + (size_t)(s0 + k) * n) : "memory");
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                if (((need >> k) & 1u) && (uint32_t)(w[k] >> 32) == gen) need &= ~(1u << k);
+            if (need && (nsp & 255u) == 255u && ld_volatile_s32(abort_flag)) break;
+        }
+        if (need) return false;
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            if (s0 + k < tp) s = __fadd_rn(s, __uint_as_float((uint32_t)w[k]));
+    }
+    sk_put(xsum + e, s, gen);
+    return true;
+}
+
+__device__ __forceinline__ bool sk_gather8_local(const sk_word_t *xsum, int e0, uint32_t gen, float (&v)[8],
+                                                 const int *abort_flag, unsigned limit) {
+    for (unsigned nsp = 0; nsp < limit; nsp++) {
+        sk_word_t w[8];
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[2 * k]), "=l"(w[2 * k + 1]) : "l"(xsum + e0 + 2 * k) : "memory");
+        bool got = true;
+#pragma unroll
+        for (int k = 0; k < 8; k++) got = got && ((uint32_t)(w[k] >> 32) == gen);
+        if (got) {
+#pragma unroll
+            for (int k = 0; k < 8; k++) v[k] = __uint_as_float((uint32_t)w[k]);
+            return true;
+        }
+        if ((nsp & 255u) == 255u && ld_volatile_s32(abort_flag)) break;
+    }
+    return false;
 }
 
 __device__ __forceinline__ unsigned long long sk_now() {
@@ -204,7 +269,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cta = blockIdx.x, G = gridDim.x;
     const bool leader = (cta == 0);
-    sk_bar_t B = {K.bar, K.abort_flag, K.status, (unsigned)G, K.bar_base, K.spin_limit, 0u};
+    sk_bar_t B = {K.bar, K.abort_flag, K.status, K.host_flags, (unsigned)G, K.bar_base, K.spin_limit, 0u};
 
     const uint32_t full_u = fb_smem_u32(&S->full[warp][0]);
     if (tid == 0) {
@@ -278,12 +343,19 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             float mo[8];
             if (TP) {
                 bool got = true;
-                if (l > 0 && own) got = sk_gather8(K.tp_recv, K.tp_size, n, e0, gen - 1u, mo, K.abort_flag, K.spin_limit);
-                if (!__syncthreads_and(got ? 1 : 0)) {
-                    if (tid == 0) {
-                        atomicExch(B.abort_flag, 1);
-                        atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
+                if (l > 0 && K.tp_two_stage) {
+                    for (int c = cta + warp * G; c < n / 32 && got; c += G * SK_WARPS) {
+                        got = sk_reduce_elem(K.tp_recv, K.tp_xsum, K.tp_size, n, 32 * c + lane, gen - 1u, K.abort_flag, K.spin_limit);
+                        if (!__all_sync(FULL, got)) { /* release the threads that are about to poll for this sum */
+                            if (lane == 0) sk_give_up(B);
+                            got = false;
+                        }
                     }
+                    if (own && got) got = sk_gather8_local(K.tp_xsum, e0, gen - 1u, mo, K.abort_flag, K.spin_limit);
+                } else if (l > 0 && own)
+                    got = sk_gather8(K.tp_recv, K.tp_size, n, e0, gen - 1u, mo, K.abort_flag, K.spin_limit);
+                if (!__syncthreads_and(got ? 1 : 0)) {
+                    if (tid == 0) sk_give_up(B);
                     alive = false;
                     break;
                 }
@@ -408,7 +480,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
 
             /* ---- SEL: routing, redundantly in every block (results identical by construction) */
             fb_block_select(A, &S->sel, h_sm, S->all_scores, S->ids, S->ids_orig, S->scores, S->slot_rec, leader,
-                            S->shared_gate);
+                            S->shared_gate,
+                            (leader && A.route_log) ? A.route_log + (size_t)tok * A.route_stride : nullptr);
             if (leader) {
                 if (tid < A.n_slots) {
                     A.ids[tid] = S->ids[tid];
@@ -462,10 +535,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     }
                 }
                 if (!__syncthreads_and(alive ? 1 : 0)) {
-                    if (tid == 0) {
-                        atomicExch(B.abort_flag, 1);
-                        atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
-                    }
+                    if (tid == 0) sk_give_up(B);
                     alive = false;
                     break;
                 }
@@ -477,7 +547,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
              *      long run per block dealt round-robin to 12 warps (two ring stages of one group each). */
             sk_arrive(B, S);
             const int ns = A.n_slots, dbpr = A.down_bpr, drpg = 32 / dbpr;
-            const uint32_t GB = (A.down_type == FB_TYPE_Q4_K) ? FB_Q4K_GROUP : (A.down_type == FB_TYPE_Q5_K) ? FB_Q5K_GROUP : FB_Q6K_GROUP;
+            const uint32_t GB = (uint32_t)fb_group_bytes_h(A.down_type, A.down_half);
             const int dtotal = A.down_groups * ns;
             const int d0 = (int)(((long long)cta * dtotal) / G), d1 = (int)(((long long)(cta + 1) * dtotal) / G);
             /* the run [d0, d1): its last row group continues in the next block when d1 is not a multiple of ns;
@@ -539,7 +609,27 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     const uint32_t st = dring_u + s * FB_Q6K_GROUP + 16 * lane;
                     const uint32_t a_u = fb_smem_u32(&S->q8a[slot * dbpr + lane % dbpr]);
                     float f;
-                    if (A.down_type == FB_TYPE_Q4_K) {
+                    if (A.down_half >= 0 && A.down_type == FB_TYPE_Q4_K) { /* half super-blocks (layout.h) */
+                        const uint4 hd = fb_lds128(st);
+                        uint4 q[4];
+#pragma unroll
+                        for (int k = 0; k < 4; k++) q[k] = fb_lds128(st + 512 * (k + 1));
+                        __syncwarp();
+                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        f = fb_dot_q4k_half_sm(hd, q, a_u, A.down_half);
+                    } else if (A.down_half >= 0) {
+                        uint4 ql[4], qh[2];
+#pragma unroll
+                        for (int k = 0; k < 4; k++) ql[k] = fb_lds128(st + 512 * k);
+#pragma unroll
+                        for (int k = 0; k < 2; k++) qh[k] = fb_lds128(st + 512 * (4 + k));
+                        const uint2 sc = fb_lds64_a(dring_u + s * FB_Q6K_GROUP + FB_Q6K_HOFF_SC + 8 * lane);
+                        uint32_t d16;
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d16) : "r"(dring_u + s * FB_Q6K_GROUP + FB_Q6K_HOFF_D + 2 * lane));
+                        __syncwarp();
+                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        f = fb_dot_q6k_half_sm(ql, qh, sc, d16, a_u, A.down_half);
+                    } else if (A.down_type == FB_TYPE_Q4_K) {
                         const uint4 hd = fb_lds128(st);
                         uint4 q[8];
 #pragma unroll
@@ -580,10 +670,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 }
             }
             if (!__syncthreads_and(alive ? 1 : 0)) {
-                if (tid == 0) {
-                    atomicExch(B.abort_flag, 1);
-                    atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
-                }
+                if (tid == 0) sk_give_up(B);
                 alive = false;
                 break;
             }
@@ -627,10 +714,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         ok = need == 0u;
                     }
                     if (!__all_sync(FULL, ok)) {
-                        if (lane == 0) {
-                            atomicExch(B.abort_flag, 1);
-                            atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
-                        }
+                        if (lane == 0) sk_give_up(B);
                         break; /* the grid barrier that follows sees the abort flag */
                     }
                     __syncwarp();
@@ -645,7 +729,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     if (TP) {
                         /* fused all-reduce, sending side: the partial goes straight into slot tp_rank of every
                          * rank's receive buffer over NVLink (plain peer stores of {generation, value} words) */
-                        for (int p = 0; p < K.tp_size; p++) sk_put_sys(K.tp_peer[p] + (size_t)K.tp_rank * n + r, acc, gen);
+                        const size_t at = ((size_t)(gen & 1u) * K.tp_size + K.tp_rank) * n + r;
+                        for (int p = 0; p < K.tp_size; p++) sk_put_sys(K.tp_peer[p] + at, acc, gen);
                     } else {
                         A.moe_out[r] = acc;
                     }
@@ -668,10 +753,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 if (leader && e0 < A.n_embd)
                     got = sk_gather8(K.tp_recv, K.tp_size, A.n_embd, e0, K.gen_base + (uint32_t)((tk + 1) * K.n_layers), mo, K.abort_flag, K.spin_limit);
                 if (!__syncthreads_and(got ? 1 : 0)) {
-                    if (tid == 0) {
-                        atomicExch(B.abort_flag, 1);
-                        atomicExch(B.status, FB_ST_WAIT_TIMEOUT);
-                    }
+                    if (tid == 0) sk_give_up(B);
                     alive = false;
                     break;
                 }
@@ -709,18 +791,21 @@ extern "C" int fb_stack_supported(const fb_args_t *a, int grid) {
     const int dtotal = a->down_groups * a->n_slots;
     const int run = (dtotal + grid - 1) / grid;                       /* longest run of down tasks of one block */
     const int max_rg = (run + a->n_slots - 2) / a->n_slots + 2;       /* row groups such a run can touch */
+    if (a->down_half >= 0 && a->down_type != FB_TYPE_Q4_K && a->down_type != FB_TYPE_Q6_K) return 0;
     return a->n_embd <= 4096 && a->n_slots <= SK_DN_SLOTS && a->n_slots * a->down_bpr <= SK_MAX_Q8A &&
            a->n_embd / FB_QK <= 16 && a->tp_size <= FB_MAX_TP && a->inter_local % FB_QK == 0 && max_rg <= SK_MAX_RG;
 }
 
 extern "C" int fb_launch_stack(const fb_stack_args_t *k, int grid, void *stream) {
-    static int configured = 0;
+    static unsigned char configured[64]; /* the attribute holds for one device: one flag per device ordinal */
     const int sm = fb_stack_smem_bytes();
-    if (!configured) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(k_stack<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(k_stack<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
         if (e != cudaSuccess) return (int)e;
-        configured = 1;
+        configured[dev] = 1;
     }
     fb_stack_args_t kk = *k;
     void *params[] = {&kk};

@@ -50,6 +50,28 @@ __device__ __forceinline__ void store_q6k(uint8_t *shard, int lb, const uint32_t
     reinterpret_cast<uint16_t *>(gb + FB_Q6K_OFF_D)[lb & 31] = d;
 }
 
+/* half super-blocks: w / ql, qh, sc, d are the WHOLE block as generated or read; only half `h` is kept */
+__device__ __forceinline__ void store_q4k_half(uint8_t *shard, int lb, const uint32_t w[36], int h) {
+    uint4 *grp = reinterpret_cast<uint4 *>(shard + (uint64_t)(lb >> 5) * FB_Q4K_HGROUP) + (lb & 31);
+    grp[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    const uint32_t *q = w + 4 + 16 * h;
+#pragma unroll
+    for (int k = 0; k < 4; k++) grp[32 * (k + 1)] = make_uint4(q[4 * k], q[4 * k + 1], q[4 * k + 2], q[4 * k + 3]);
+}
+
+__device__ __forceinline__ void store_q6k_half(uint8_t *shard, int lb, const uint32_t ql[32], const uint32_t qh[16],
+                                               const uint32_t sc[4], uint16_t d, int h) {
+    uint8_t *gb = shard + (uint64_t)(lb >> 5) * FB_Q6K_HGROUP;
+    uint4 *grp = reinterpret_cast<uint4 *>(gb) + (lb & 31);
+    const uint32_t *l = ql + 16 * h, *q = qh + 8 * h;
+#pragma unroll
+    for (int k = 0; k < 4; k++) grp[32 * k] = make_uint4(l[4 * k], l[4 * k + 1], l[4 * k + 2], l[4 * k + 3]);
+#pragma unroll
+    for (int k = 0; k < 2; k++) grp[32 * (4 + k)] = make_uint4(q[4 * k], q[4 * k + 1], q[4 * k + 2], q[4 * k + 3]);
+    reinterpret_cast<uint2 *>(gb + FB_Q6K_HOFF_SC)[lb & 31] = make_uint2(sc[2 * h], sc[2 * h + 1]);
+    reinterpret_cast<uint16_t *>(gb + FB_Q6K_HOFF_D)[lb & 31] = d;
+}
+
 __global__ void k_gen_shards(uint8_t *dst0, uint64_t rec_stride, uint64_t seed, uint32_t layer, uint32_t matrix,
                              fb_shard_geom_t g) {
     const int n_local = g.rows_local * g.bpr_local;
@@ -63,7 +85,8 @@ __global__ void k_gen_shards(uint8_t *dst0, uint64_t rec_stride, uint64_t seed, 
             if (lb < n_local) fsyn_q4k_block(key, full_block_index(g, lb), w);
             else
                 for (int i = 0; i < 36; i++) w[i] = 0;
-            store_q4k(shard, lb, w);
+            if (g.half >= 0) store_q4k_half(shard, lb, w, g.half);
+            else store_q4k(shard, lb, w);
         } else if (g.type == FB_TYPE_Q5_K) {
             uint32_t w[44];
             if (lb < n_local) fsyn_q5k_block(key, full_block_index(g, lb), w);
@@ -79,7 +102,8 @@ __global__ void k_gen_shards(uint8_t *dst0, uint64_t rec_stride, uint64_t seed, 
                 for (int i = 0; i < 16; i++) qh[i] = 0;
                 for (int i = 0; i < 4; i++) sc[i] = 0;
             }
-            store_q6k(shard, lb, ql, qh, sc, d);
+            if (g.half >= 0) store_q6k_half(shard, lb, ql, qh, sc, d, g.half);
+            else store_q6k(shard, lb, ql, qh, sc, d);
         }
     }
 }
@@ -102,7 +126,8 @@ __global__ void k_repack(uint8_t *shard, const uint8_t *src, fb_shard_geom_t g) 
                 for (int i = 0; i < 36; i++) w[i] = s[i];
             } else
                 for (int i = 0; i < 36; i++) w[i] = 0;
-            store_q4k(shard, lb, w);
+            if (g.half >= 0) store_q4k_half(shard, lb, w, g.half);
+            else store_q4k(shard, lb, w);
         } else if (g.type == FB_TYPE_Q5_K) {
             uint32_t w[44];
             if (lb < n_local) {
@@ -120,7 +145,8 @@ __global__ void k_repack(uint8_t *shard, const uint8_t *src, fb_shard_geom_t g) 
                 d = s[104];
             } else
                 for (int i = 0; i < 52; i++) w[i] = 0;
-            store_q6k(shard, lb, w, w + 32, w + 48, d);
+            if (g.half >= 0) store_q6k_half(shard, lb, w, w + 32, w + 48, d, g.half);
+            else store_q6k(shard, lb, w, w + 32, w + 48, d);
         }
     }
 }
@@ -154,10 +180,73 @@ __global__ void k_export_ggml(uint8_t *dst, const uint8_t *shard, fb_shard_geom_
     }
 }
 
+/* one half super-block (layout.h) -> 128 fp32 values: the arithmetic of the whole-block kernel below restricted to
+ * chunks 2h, 2h+1 (Q4_K) / half h (Q6_K).  Kept out of line on purpose: inlined into k_dequant, nvcc 12.9 produced a
+ * whole-block Q6_K path whose values were exactly twice the right ones (the bit-exact dequant test caught it). */
+__device__ __noinline__ void dequant_half_block(float *dst, const uint8_t *shard, int type, int half, int lb) {
+        /* half super-blocks: 128 values per block, the arithmetic of the whole-block branches below restricted to
+         * chunks 2h, 2h+1 (Q4_K) / half h (Q6_K) */
+        const int h = half;
+        float *y = dst + (uint64_t)lb * (FB_QK / 2);
+        if (type == FB_TYPE_Q4_K) {
+            const uint4 *grp = reinterpret_cast<const uint4 *>(shard + (uint64_t)(lb >> 5) * FB_Q4K_HGROUP) + (lb & 31);
+            const uint4 hdr = grp[0];
+            const float d = fb_half_bits_to_float(hdr.x & 0xffff), mn = fb_half_bits_to_float(hdr.x >> 16);
+            const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+            const uint32_t scw = h ? ((u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4)) : (u0 & 0x3f3f3f3fu);
+            const uint32_t mw = h ? (((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4)) : (u1 & 0x3f3f3f3fu);
+            for (int cc = 0; cc < 2; cc++) {
+                const float d1 = __fmul_rn(d, (float)((scw >> (16 * cc)) & 0xff));
+                const float d2 = __fmul_rn(d, (float)((scw >> (16 * cc + 8)) & 0xff));
+                const float m1 = __fmul_rn(mn, (float)((mw >> (16 * cc)) & 0xff));
+                const float m2 = __fmul_rn(mn, (float)((mw >> (16 * cc + 8)) & 0xff));
+                for (int kk = 0; kk < 2; kk++) {
+                    const uint4 v = grp[32 * (1 + 2 * cc + kk)];
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                    for (int i = 0; i < 16; i++) {
+                        const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xff;
+                        y[64 * cc + 16 * kk + i] = __fsub_rn(__fmul_rn(d1, (float)(byte & 0xf)), m1);
+                        y[64 * cc + 32 + 16 * kk + i] = __fsub_rn(__fmul_rn(d2, (float)(byte >> 4)), m2);
+                    }
+                }
+            }
+        } else {
+            const uint8_t *gb = shard + (uint64_t)(lb >> 5) * FB_Q6K_HGROUP;
+            const uint4 *grp = reinterpret_cast<const uint4 *>(gb) + (lb & 31);
+            const float d = fb_half_bits_to_float(reinterpret_cast<const uint16_t *>(gb + FB_Q6K_HOFF_D)[lb & 31]);
+            const uint2 scv = reinterpret_cast<const uint2 *>(gb + FB_Q6K_HOFF_SC)[lb & 31];
+            const uint32_t scw[2] = {scv.x, scv.y};
+            for (int l = 0; l < 32; l++) {
+                auto byte_at = [&](int plane_first, int byte) -> uint32_t {
+                    const uint4 v = grp[32 * (plane_first + (byte >> 4))];
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                    return (w[(byte & 15) >> 2] >> (8 * (byte & 3))) & 0xff;
+                };
+                const uint32_t a = byte_at(0, l), b = byte_at(0, 32 + l), hh = byte_at(4, l);
+                const int is = l / 16;
+                const int q1 = (int)((a & 0xf) | (((hh >> 0) & 3) << 4)) - 32;
+                const int q2 = (int)((b & 0xf) | (((hh >> 2) & 3) << 4)) - 32;
+                const int q3 = (int)((a >> 4) | (((hh >> 4) & 3) << 4)) - 32;
+                const int q4 = (int)((b >> 4) | (((hh >> 6) & 3) << 4)) - 32;
+                auto scale = [&](int idx) -> float {
+                    return (float)(int)(signed char)((scw[idx >> 2] >> (8 * (idx & 3))) & 0xff);
+                };
+                y[l] = __fmul_rn(__fmul_rn(d, scale(is + 0)), (float)q1);
+                y[l + 32] = __fmul_rn(__fmul_rn(d, scale(is + 2)), (float)q2);
+                y[l + 64] = __fmul_rn(__fmul_rn(d, scale(is + 4)), (float)q3);
+                y[l + 96] = __fmul_rn(__fmul_rn(d, scale(is + 6)), (float)q4);
+            }
+        }
+}
+
 /* shard -> fp32, one thread per block; arithmetic of src/quant.c:82-105 and 147-175 */
 __global__ void k_dequant(float *dst, const uint8_t *shard, fb_shard_geom_t g) {
     const int n_local = g.rows_local * g.bpr_local;
     for (int lb = blockIdx.x * blockDim.x + threadIdx.x; lb < n_local; lb += gridDim.x * blockDim.x) {
+        if (g.half >= 0) {
+            dequant_half_block(dst, shard, g.type, g.half, lb);
+            continue;
+        }
         float *y = dst + (uint64_t)lb * FB_QK; /* row-major: block lb covers row lb/bpr, columns 256*(lb%bpr).. */
         if (g.type == FB_TYPE_Q4_K) {
             const uint4 *grp = reinterpret_cast<const uint4 *>(shard + (uint64_t)(lb >> 5) * FB_Q4K_GROUP) + (lb & 31);
@@ -418,7 +507,7 @@ extern "C" int fomoe_b200_matvec_noalloc(int type, const void *w_ggml_dev, int r
     }
     unsigned char *shard = fb_noalloc_ptr[dev];
     fb_q8_entry_t *q8 = reinterpret_cast<fb_q8_entry_t *>(fb_noalloc_ptr[dev] + FB_NOALLOC_SHARD_BYTES);
-    const fb_shard_geom_t g = {type, rows, bpr, 0, 0, bpr};
+    const fb_shard_geom_t g = {type, rows, bpr, 0, 0, bpr, -1};
     const int n_groups = (int)fb_n_groups((uint64_t)rows * bpr);
     int rc = fb_launch_repack(shard, (const uint8_t *)w_ggml_dev, g, stream);
     if (!rc) rc = fb_launch_quantize(q8, x_dev, bpr, stream);

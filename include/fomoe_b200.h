@@ -51,8 +51,11 @@ float *gpu_forward(gpu_ctx_t *ctx, void *model, int token_id, int pos);         
 void gpu_reset_state(gpu_ctx_t *ctx);                                              /* gpu.h:41, no-op */
 int gpu_seed_vram_cache(gpu_ctx_t *ctx, void *model, const char *freq_profile_path); /* gpu.h:46, returns 0 */
 void gpu_enable_expert_freq(gpu_ctx_t *ctx);                                       /* gpu.h:50 */
-const uint32_t *gpu_get_expert_freq(gpu_ctx_t *ctx);                               /* gpu.h:54 */
-void gpu_get_expert_dims(gpu_ctx_t *ctx, int *n_layers, int *n_experts);           /* gpu.h:57 */
+const uint32_t *gpu_get_expert_freq(gpu_ctx_t *ctx);                               /* gpu.h:54: [n_layers * n_experts]
+                                                                                       counters of the attached decoder
+                                                                                       (fomoe_b200_gpu_attach), NULL when
+                                                                                       not enabled; not to be freed */
+void gpu_get_expert_dims(gpu_ctx_t *ctx, int *n_layers, int *n_experts);           /* gpu.h:57: of the attached decoder */
 void gpu_get_pingpong_relay_stats(gpu_ctx_t *ctx, uint64_t *handoffs, uint64_t *payload_bytes,
                                   uint64_t *d2h_bytes, uint64_t *h2d_bytes, uint64_t *dma_bytes); /* gpu.h:61, zeros */
 
@@ -60,8 +63,10 @@ void gpu_get_pingpong_relay_stats(gpu_ctx_t *ctx, uint64_t *handoffs, uint64_t *
  * Same arguments as reference gpu.h:70-83.  expert_buffers[e] points at one expert record
  * in ggml byte order (gate | up | down back to back).  Returns 0, or -1 for shapes/types
  * outside the supported set (the reference's limits, src/gpu_kernels.hip:8393-8403, plus:
- * gate/up must be Q4_K, down Q4_K or Q6_K), in which case the caller falls back
- * (src/inference.c:551).  Activations are quantised to Q8_K as in src/cpu_expert.c. */
+ * gate/up must be Q4_K, down Q4_K, Q5_K or Q6_K), in which case the caller falls back
+ * (src/inference.c:551).  Activations are quantised to Q8_K as in src/cpu_expert.c.
+ * expert_buffers[e] may be host memory (staged: two staging buffers filled on a copy stream, the host does not
+ * wait between records) or memory of the current GPU (regrouped where it lies, no staging). */
 int gpu_expert_ffn(gpu_ctx_t *ctx, const float *h, void **expert_buffers, const float *expert_scores,
                    int n_experts, int n_embd, int expert_intermediate, uint64_t expert_gate_size,
                    uint64_t expert_up_size, uint64_t expert_stride, int gate_type, int up_type, int down_type,
@@ -101,13 +106,16 @@ typedef struct {
     int device;              /* CUDA device ordinal */
     int n_layers;
     int n_embd;              /* hidden size, multiple of 256, <= 8192 */
-    int n_inter;             /* expert intermediate size, multiple of 256 * tp_size */
+    int n_inter;             /* expert intermediate size, multiple of 256; tp_size divides n_inter/256, or is twice it */
     int n_experts;           /* routed experts per layer, <= 512 */
     int top_k;               /* experts used per token, <= 15 */
     int has_shared;          /* 1: one shared expert per layer (record index n_experts) */
     int gate_type;           /* gate and up type: FOMOE_TYPE_Q4_K */
-    const int *down_types;   /* [n_layers] FOMOE_TYPE_Q4_K / FOMOE_TYPE_Q6_K; NULL = all Q6_K */
-    int tp_rank, tp_size;    /* tensor parallelism over the intermediate dimension */
+    const int *down_types;   /* [n_layers] FOMOE_TYPE_Q4_K / FOMOE_TYPE_Q5_K / FOMOE_TYPE_Q6_K; NULL = all Q6_K */
+    int tp_rank, tp_size;    /* tensor parallelism over the intermediate dimension, tp_size <= 8.  With W = n_inter/256
+                                windows: tp_size dividing W gives every rank W/tp_size whole windows; tp_size == 2 W
+                                (8 ranks at n_inter 1024) gives ranks 2p and 2p+1 window p together: both compute its
+                                gate/up rows, each owns one 128-column half of the down projection (Q4_K / Q6_K only) */
     float rms_eps;
     float car_threshold;     /* CAR runs when 0 < threshold < 1 (reference src/car.c:68, gpu_kernels.hip:7170) */
     int car_dampen;          /* 1: substitute weight = original weight * ratio, no renormalise */
@@ -117,7 +125,9 @@ typedef struct {
 fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg);
 void fomoe_b200_destroy(fomoe_b200_ctx_t *ctx);
 const char *fomoe_b200_last_error(fomoe_b200_ctx_t *ctx);
-/* device status word written by kernels: 0 ok, 1 bad expert id, 2 bounded wait ran out */
+/* What went wrong on the device since the last call of this function: 0 nothing, 1 a kernel met an expert id
+ * outside the table, 2 the stack kernel gave a bounded wait up (the run that met it has already returned -1 and left
+ * its output buffer untouched).  Reading clears it: after a failure, a later successful run reports 0 again. */
 int fomoe_b200_status(fomoe_b200_ctx_t *ctx);
 /* bytes of one expert record in the reference's ggml order (gate | up | down), full (unsharded) */
 uint64_t fomoe_b200_record_bytes(fomoe_b200_ctx_t *ctx, int layer);
@@ -183,6 +193,19 @@ int fomoe_b200_decode_token(fomoe_b200_ctx_t *ctx, const float *x_in, float *x_o
 int fomoe_b200_tokens_profile(fomoe_b200_ctx_t *ctx, int first, int count, float *phase_ms, int *phase_launches);
 /* Routing of the most recent token at `layer`. */
 int fomoe_b200_get_routing(fomoe_b200_ctx_t *ctx, int layer, int *ids, float *scores, int *ids_orig);
+/* Routing trace in the reference's file format (32-byte header, one packed record per layer and token: the top-k
+ * before and after cache-aware routing with their weights and a source code per slot; src/gpu_kernels.hip:451-484,
+ * read by tools/read_trace.py).  While a trace is open every token that stack_run (whole stack), tokens_run or
+ * decode_token runs is appended.  Source codes: 0 expert marked resident (or no mask set), 2 not resident (what the
+ * reference would fetch from NVMe; here it is in HBM like every other expert), 3 substituted by CAR, 4 weight zero. */
+int fomoe_b200_routing_trace_open(fomoe_b200_ctx_t *ctx, const char *path);
+int fomoe_b200_routing_trace_close(fomoe_b200_ctx_t *ctx);
+/* Histogram of routed expert ids before substitution (the reference: include/gpu.h:50-57): enable, then read
+ * out[n_layers * n_experts].  fomoe_b200_gpu_attach makes gpu_enable_expert_freq / gpu_get_expert_freq /
+ * gpu_get_expert_dims of a gpu_ctx_t report this decoder. */
+int fomoe_b200_enable_expert_freq(fomoe_b200_ctx_t *ctx);
+int fomoe_b200_get_expert_freq(fomoe_b200_ctx_t *ctx, uint32_t *out);
+int fomoe_b200_gpu_attach(gpu_ctx_t *gpu, fomoe_b200_ctx_t *decoder);
 /* Counters since creation: CAR substitutions, kernels launched by this library. */
 uint64_t fomoe_b200_substitutions(fomoe_b200_ctx_t *ctx);
 uint64_t fomoe_b200_kernel_launches(fomoe_b200_ctx_t *ctx);
@@ -191,9 +214,17 @@ uint64_t fomoe_b200_kernel_launches(fomoe_b200_ctx_t *ctx);
  * between the devices (cudaDeviceEnablePeerAccess). */
 void *fomoe_b200_tp_recv_ptr(fomoe_b200_ctx_t *ctx);
 int fomoe_b200_tp_connect_ptrs(fomoe_b200_ctx_t *ctx, void *const *recv_ptrs /* tp_size pointers, rank order */);
+/* cudaDeviceEnablePeerAccess from this context's device to peer_device (already enabled is fine). */
+int fomoe_b200_tp_enable_peer(fomoe_b200_ctx_t *ctx, int peer_device);
+/* Host-side stand-in for a rank (diagnostics, tests, a supervisor that lost a rank): writes partial[n_embd]
+ * (NULL = zeros) into this context's receive buffer as rank src_rank's contribution to the layer-token `ahead`
+ * (>= 1) layer-tokens after the last one launched. */
+int fomoe_b200_tp_inject(fomoe_b200_ctx_t *ctx, int src_rank, const float *partial, unsigned ahead);
 /* Every wait of the stack kernel on another block or rank gives up after `polls` polls (0 = the default, about
  * four million: seconds), sets status 2 ("bounded wait ran out") and lets the kernel return; a rank whose peer
- * has gone away therefore reports instead of hanging.  fomoe_b200_status re-arms the kernel's flags afterwards. */
+ * has gone away therefore reports instead of hanging: the call returns -1, fomoe_b200_status says 2, the kernel's
+ * flags are re-armed, and the context stays usable.  Every rank must have made the same calls (a launch advances the
+ * generation numbers of the exchange on the rank that made it, finished or not). */
 int fomoe_b200_set_wait_limit(fomoe_b200_ctx_t *ctx, unsigned polls);
 /* Tensor parallelism with the CALLER's collective instead of the fused exchange (the reference's arrangement:
  * kernels per phase and tp_allreduce_sum between them, include/tp.h:53-79).  With a hook installed and the per-phase

@@ -18,9 +18,12 @@ def test_rank_layout():
     assert [b.tp_layout(2, r) for r in range(2)] == [(2, 1, 0, 0), (2, 1, 0, 1)]
     assert [b.tp_layout(4, r)[2:] for r in range(4)] == [(0, 0), (0, 1), (0, 2), (0, 3)]
     lay = [b.tp_layout(8, r) for r in range(8)]
-    assert all(t == 4 and n == 2 for t, n, _, _ in lay)                  # two groups of four
-    assert [g for _, _, g, _ in lay] == [0, 0, 0, 0, 1, 1, 1, 1]          # consecutive ranks form a group
-    assert [r for _, _, _, r in lay] == [0, 1, 2, 3, 0, 1, 2, 3]
+    assert all(t == 8 and n == 1 and g == 0 for t, n, g, _ in lay)       # one stream over all eight GPUs
+    assert [r for _, _, _, r in lay] == list(range(8))
+    rep = [b.tp_layout(8, r, 4) for r in range(8)]                        # --tp 4: two replicas, comparison only
+    assert all(t == 4 and n == 2 for t, n, _, _ in rep)
+    assert [g for _, _, g, _ in rep] == [0, 0, 0, 0, 1, 1, 1, 1]          # consecutive ranks form a group
+    assert [r for _, _, _, r in rep] == [0, 1, 2, 3, 0, 1, 2, 3]
 
 
 def test_workload_record_and_bytes():
@@ -29,5 +32,39 @@ def test_workload_record_and_bytes():
     assert b.expert_bytes_per_token(60) == 5028249600
     c1, c8 = b.workload_config(1, 12, 256), b.workload_config(8, 60, 128)
     assert c1["parallelism"] == "tp1" and "first 12 of 60 layers" in c1["workload"]
-    assert c8["parallelism"].startswith("2 independent batch-1 streams x tp4")
+    assert c8["parallelism"] == "tp8"
+    assert b.workload_config(8, 60, 128, 4)["parallelism"].startswith("2 replicas x tp4")
     assert set(c1) == set(c8)
+
+
+def test_reference_arm_runs_without_the_cuda_library():
+    """`bench.py --impl reference` prints a line whose config equals the GPU arm's for the same arguments, takes its
+    inputs from the host-only generator, and never maps libfomoe_b200.so."""
+    import json
+    import subprocess
+    import sys
+    code = ("import sys, runpy; sys.argv = ['bench.py', '--impl', 'reference', '--steps', '2', '--warmup', '0'];\n"
+            "import bench; bench.cpu_baseline.__defaults__ = (None, 2, 0.05)\n"
+            "bench.main()\n"
+            "maps = open('/proc/self/maps').read()\n"
+            "print('MAPPED_PRODUCT', 'libfomoe_b200.so' in maps, 'libfomoe_synth.so' in maps)\n")
+    out = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = out.stdout.strip().splitlines()
+    line = json.loads(next(l for l in lines if l.startswith("{")))
+    assert line["impl"] == "reference" and line["cpu_baseline"]["kind"] in ("reference", "port")
+    assert line["config"] == _bench().workload_config(1, 12, 2)
+    assert "MAPPED_PRODUCT False True" in lines[-1]
+
+
+def test_host_generator_library_matches_the_main_library(fb=None):
+    import numpy as np
+    import fomoe_b200
+    from fomoe_b200 import synth
+    a = fomoe_b200.synth_expert_record(5, 1, 3, 14, 512, 256)
+    assert (a == synth.expert_record(5, 1, 3, 14, 512, 256)).all()
+    assert (fomoe_b200.synth_hidden(5, 2, 512) == synth.hidden(5, 2, 512)).all()
+    assert (fomoe_b200.synth_router(5, 1, 8, 512) == synth.router(5, 1, 8, 512)).all()
+    for x, y in zip(fomoe_b200.synth_glue(5, 1, 512), synth.glue(5, 1, 512)):
+        assert (x == y).all()
+    assert (fomoe_b200.synth_matrix(9, 0, 1, 2, 13, 256, 512) == synth.matrix(9, 0, 1, 2, 13, 256, 512)).all()

@@ -323,25 +323,238 @@ def test_tensor_parallel_partials_sum_to_full(fb, oracle, tp):
     assert H.rel_l2(acc, o["out"]) < 2e-5
 
 
-def test_missing_peer_times_out_and_reports(fb):
-    """Failure detection without a fault: a tensor-parallel rank whose peer never delivers (its slot of the receive
+@pytest.mark.parametrize("two_stage", ["0", "1"])
+def test_missing_peer_times_out_and_reports(fb, monkeypatch, two_stage):
+    """Both forms of the receive step (every thread polls every rank's slot / a few warps add the ranks up first).
+    Failure detection without a fault: a tensor-parallel rank whose peer never delivers (its slot of the receive
     buffer is a flag that nothing sets) gives the wait up after the configured number of polls, the kernel returns,
-    the status word says so, and the GPU goes on working."""
+    the call reports failure without touching its output, the status word says why exactly once, and the SAME context
+    goes on working when the peer's share does arrive (here: fed from the host)."""
     n_embd, inter, n_experts, top_k, seed = 1024, 512, 16, 2, 23
     dts = [H.Q6, H.Q4]
+    monkeypatch.setenv("FOMOE_B200_TP_TWO_STAGE", two_stage)
     d = fb.MoeDecoder(2, n_embd, inter, n_experts, top_k, True, dts, tp_rank=0, tp_size=2, rms_eps=1e-6, max_tokens=2)
     d.generate(seed)
     own = d.tp_recv_ptr()
     d.tp_connect_ptrs([own, own])          # "rank 1" is nobody: its partial sums never arrive
     d.set_wait_limit(20000)                # about 15 ms instead of seconds
-    d.tokens_upload(0, np.stack([H.hidden(fb, seed, t, n_embd) for t in range(2)]))
-    d.tokens_run(0, 2)                     # returns: the kernel gave up at layer 1's receive step
-    assert d.status() == 2                 # bounded wait ran out (and the flags are re-armed)
-    d.tokens_run(0, 1)
-    assert d.status() == 2                 # still nobody there: reported again, not hung
+    toks = np.stack([H.hidden(fb, seed, t, n_embd) for t in range(2)])
+    d.tokens_upload(0, toks)
+    with pytest.raises(RuntimeError):
+        d.tokens_run(0, 2)                 # the kernel gave up at layer 1's receive step: the call fails
+    assert d.status() == 2                 # bounded wait ran out ...
+    assert d.status() == 0                 # ... reported once
+    sentinel = np.full(n_embd, 7.0, dtype=np.float32)
+    out = sentinel.copy()
+    rc = fb.lib().fomoe_b200_decode_token(d._h, toks[0].ctypes.data_as(fb._f32p), out.ctypes.data_as(fb._f32p))
+    assert rc == -1 and (out == sentinel).all()      # still nobody there: failure again, output untouched
+    assert d.status() == 2
+    # retry on the same context with a DIFFERENT token, rank 1's share now delivered (zeros, from the host) for
+    # both layer-tokens of the call: succeeds, reports 0, and equals rank 0's own partial stack
+    d.tp_inject(1, None, ahead=1)
+    d.tp_inject(1, None, ahead=2)
+    got = d.decode_token(toks[1])
+    assert d.status() == 0 and np.isfinite(got).all()
+    d.tp_inject(1, None, ahead=1)
+    d.tp_inject(1, None, ahead=2)
+    again = d.decode_token(toks[1])
+    assert (H.bits(again) == H.bits(got)).all()      # no stale word of the failed runs was picked up
     d.close()
     ok = fb.MoeDecoder(2, n_embd, inter, n_experts, top_k, True, dts, rms_eps=1e-6, max_tokens=2)
     ok.generate(seed)
     x = H.hidden(fb, seed, 0, n_embd)
     assert np.isfinite(ok.decode_token(x)).all() and ok.status() == 0
     ok.close()
+
+
+def test_config3_full_shape_stack_with_car(fb, oracle):
+    """Config 3 at the FULL layer shape through the persistent kernel: hidden 4096, 512 experts, top-10 + shared,
+    intermediate 1024, CAR 0.35 with dampening over 204-expert Zipf(1.1) residency masks, four layers (Q6_K / Q4_K
+    down alternating), teacher-forced: ids, ids before substitution and substitution counts exact."""
+    n_layers, n_embd, inter, n_experts, top_k, seed, eps = 4, 4096, 1024, 512, 10, 3977, 1e-6
+    dts = [H.Q6, H.Q4, H.Q6, H.Q4]
+    d = fb.MoeDecoder(n_layers, n_embd, inter, n_experts, top_k, True, dts, rms_eps=eps, car_threshold=0.35,
+                      car_dampen=True)
+    d.generate(seed)
+    masks = [H.zipf_resident_mask(seed, l, n_experts) for l in range(n_layers)]
+    for l in range(n_layers):
+        assert sum(bin(int(w)).count("1") for w in masks[l]) == 204
+        d.set_resident_mask(l, masks[l])
+    total = 0
+    for t in range(3):
+        x = H.hidden(fb, seed, t, n_embd)
+        tr = _oracle_stack(oracle, fb, seed, x, range(n_layers), n_embd, inter, n_experts, top_k, dts, eps, masks, 0.35,
+                           True)
+        for l in range(n_layers):
+            got = d.stack_run(tr[l]["x_in"], l, l + 1)
+            ids, _, ids0 = d.get_routing(l)
+            assert (ids == tr[l]["ids"]).all(), (t, l, ids, tr[l]["ids"])
+            assert int((ids != ids0).sum()) == tr[l]["subs"]
+            assert H.rel_l2(got, tr[l]["x_out"]) < OUT_EXPECT
+            total += tr[l]["subs"]
+        # free-running, the layers' deviations compound (each layer is within the bar against the SAME input; a
+        # moved int8 activation in one layer changes the next layer's input): four layers, four times the bar
+        free = d.stack_run(x)
+        assert H.rel_l2(free, tr[-1]["x_out"]) < n_layers * OUT_TOL
+    assert total > 0
+    # the free-running calls substitute as well; count the teacher-forced ones through the ids instead
+    assert d.substitutions() >= total and d.status() == 0
+    d.close()
+
+
+def test_routing_soak_full_shape(fb, oracle):
+    """Bit-exact top-k at volume: 2048 layer-tokens of routing at the 397B router shape (512 x 4096 fp32, top-10)
+    through the persistent kernel's selection, every one teacher-forced from a fresh hidden state; ids must equal the
+    CPU's index for index.  Prints how often two neighbours among the best eleven logits were closer than the
+    arbiter's window (4e-5 relative) and the smallest margin met."""
+    n_layers, n_embd, inter, n_experts, top_k, seed, eps = 4, 4096, 256, 512, 10, 811, 1e-6
+    dts = [H.Q4] * n_layers                      # small experts: this test is about the router
+    d = fb.MoeDecoder(n_layers, n_embd, inter, n_experts, top_k, False, dts, rms_eps=eps)
+    d.generate(seed)
+    routers = [H.router_weights(fb, seed, l, n_experts, n_embd) for l in range(n_layers)]
+    glue = [H.glue(fb, seed, l, n_embd) for l in range(n_layers)]
+    close, worst, n = 0, np.inf, 0
+    for t in range(512):
+        x = H.hidden(fb, seed, 5000 + t, n_embd) * np.float32(1.0 + (t % 7))
+        for l in range(n_layers):
+            d.stack_run(x, l, l + 1)
+            ids, _, _ = d.get_routing(l)
+            r, w = glue[l]
+            h = oracle.rms_norm(x + r, w, eps)
+            want, _, _, _ = oracle.route(routers[l], h, top_k)
+            assert (ids == want).all(), (t, l, ids, want)
+            lg = np.sort(oracle.router_logits(routers[l], h))[::-1][:top_k + 1].astype(np.float64)
+            gap = (lg[:-1] - lg[1:]) / np.maximum(1.0, np.abs(lg[:-1]))
+            close += int((gap <= 4e-5).any())
+            worst = min(worst, float(gap.min()))
+            n += 1
+    print(f"routing soak: {n} layer-tokens ids exact; {close} with a pair inside the arbiter window; "
+          f"smallest relative margin among the best {top_k + 1}: {worst:.3e}")
+    assert n >= 2000 and d.status() == 0
+    d.close()
+
+
+@pytest.mark.parametrize("inter,tp,down_type", [(1024, 8, H.Q6), (1024, 8, H.Q4), (512, 4, H.Q6), (256, 2, H.Q4)])
+def test_half_window_shards_sum_to_full(fb, oracle, inter, tp, down_type):
+    """Twice as many ranks as 256-wide activation windows (8 ranks at intermediate 1024): ranks 2p and 2p+1 both
+    compute window p's gate/up rows and each owns one 128-column half of the down super-blocks.  All ranks emulated on
+    one GPU: dequantised half shards are bit-exact slices of the CPU's dequantisation, every rank routes alike, and
+    the partial outputs summed in rank order equal the single-rank result and the oracle."""
+    n_embd, n_experts, top_k, seed = 1024, 16, 4, 58
+    h = H.hidden(fb, seed, 0, n_embd)
+    full = fb.MoeDecoder(1, n_embd, inter, n_experts, top_k, True, [down_type])
+    full.generate(seed)
+    want = full.moe_layer(0, h)
+    full.close()
+    raw = fb.synth_matrix(seed, 0, 3, fb.M_DOWN, down_type, n_embd, inter)
+    rb = fb.matrix_bytes(down_type, 1, inter)
+    acc = np.zeros(n_embd, dtype=np.float32)
+    for r in range(tp):
+        d = fb.MoeDecoder(1, n_embd, inter, n_experts, top_k, True, [down_type], tp_rank=r, tp_size=tp)
+        assert d.half_mode
+        d.generate(seed)
+        dq = d.dequant_shard(0, 3, fb.M_DOWN)                    # [n_embd, 128]
+        c0 = 256 * (r >> 1) + 128 * (r & 1)
+        for row in (0, 1, 517, n_embd - 1):
+            ref_row = oracle.dequantize(raw[row * rb:(row + 1) * rb], down_type, inter)
+            assert (H.bits(dq[row]) == H.bits(ref_row[c0:c0 + 128])).all(), (r, row)
+        gq = d.dequant_shard(0, 3, fb.M_GATE)                    # [256, n_embd]: window r >> 1 of the gate rows
+        graw = fb.synth_matrix(seed, 0, 3, fb.M_GATE, H.Q4, inter, n_embd)
+        grb = fb.matrix_bytes(H.Q4, 1, n_embd)
+        g_row = 256 * (r >> 1) + 7
+        assert (H.bits(gq[7]) == H.bits(oracle.dequantize(graw[g_row * grb:(g_row + 1) * grb], H.Q4, n_embd))).all()
+        got = d.moe_layer(0, h)
+        assert (got["ids"] == want["ids"]).all()
+        acc = acc + got["out"]
+        with pytest.raises(RuntimeError):
+            d.export_shard(0, 3, fb.M_DOWN)                       # half super-blocks have no ggml form
+        d.close()
+    assert H.rel_l2(acc, want["out"]) < 1e-5
+    o = H.oracle_layer(oracle, fb, seed, 0, h, n_embd, inter, n_experts, top_k, down_type)
+    assert H.rel_l2(acc, o["out"]) < 2e-5
+
+
+def _parse_trace(path):
+    """The reader's view of a routing trace (the format tools/read_trace.py of the reference parses)."""
+    import struct
+    data = open(path, "rb").read()
+    magic, version, n_layers, n_experts, top_k, _, _, _ = struct.unpack("<IIHHHHQQ", data[:32])
+    assert magic == 0x54524345 and version == 1
+    fmt = f"<IHBB{top_k}h{top_k}f{top_k}h{top_k}f{top_k}B"
+    pad = (8 - struct.calcsize(fmt) % 8) % 8
+    fmt += f"{pad}x" if pad else ""
+    size = struct.calcsize(fmt)
+    assert (len(data) - 32) % size == 0
+    recs = []
+    for off in range(32, len(data), size):
+        f = struct.unpack_from(fmt, data, off)
+        k = top_k
+        recs.append(dict(token=f[0], layer=f[1], n_used=f[2], n_subs=f[3], orig_ids=list(f[4:4 + k]),
+                         orig_scores=list(f[4 + k:4 + 2 * k]), final_ids=list(f[4 + 2 * k:4 + 3 * k]),
+                         final_scores=list(f[4 + 3 * k:4 + 4 * k]), source=list(f[4 + 4 * k:4 + 5 * k])))
+    return dict(n_layers=n_layers, n_experts=n_experts, top_k=top_k, rec_size=size, records=recs)
+
+
+def test_routing_trace_and_expert_histogram(fb, oracle, tmp_path):
+    """Routing trace in the reference's format (144-byte records at top-10) and the expert histogram: a 3-layer
+    stack with CAR 0.35 + dampening, three tokens through decode_token and two more through tokens_run; every record
+    equals the oracle's routing of the same (teacher-forced by the device's own layer inputs is not possible here, so
+    the first layer of every token, whose input is known exactly, is compared; the others are checked for internal
+    consistency), the histogram equals the count of ids before substitution over all records."""
+    import os
+    n_layers, n_embd, inter, n_experts, top_k, seed, eps = 3, 1024, 256, 128, 10, 93, 1e-6
+    dts = [H.Q6, H.Q4, H.Q6]
+    d = fb.MoeDecoder(n_layers, n_embd, inter, n_experts, top_k, True, dts, rms_eps=eps, car_threshold=0.35,
+                      car_dampen=True, max_tokens=4)
+    d.generate(seed)
+    masks = [H.zipf_resident_mask(seed, l, n_experts) for l in range(n_layers)]
+    for l in range(n_layers):
+        d.set_resident_mask(l, masks[l])
+    op = fb.GpuOperator()
+    op.enable_expert_freq()
+    assert op.expert_freq() is None and op.expert_dims() == (0, 0)     # nothing attached yet
+    op.attach(d)
+    assert op.expert_dims() == (n_layers, n_experts)
+    path = str(tmp_path / "trace.bin")
+    d.trace_open(path)
+    toks = np.stack([H.hidden(fb, seed, t, n_embd) for t in range(5)])
+    for t in range(3):
+        d.decode_token(toks[t])
+    d.tokens_upload(0, toks[3:5])
+    d.tokens_run(0, 2)
+    d.trace_close()
+    tr = _parse_trace(path)
+    assert tr["rec_size"] == 144 and (tr["n_layers"], tr["n_experts"], tr["top_k"]) == (n_layers, n_experts, top_k)
+    recs = tr["records"]
+    assert [(r["token"], r["layer"]) for r in recs] == [(t, l) for t in range(5) for l in range(n_layers)]
+    hist = np.zeros((n_layers, n_experts), dtype=np.uint32)
+    subs = 0
+    for r in recs:
+        l = r["layer"]
+        assert r["n_used"] == top_k
+        for i in range(top_k):
+            hist[l, r["orig_ids"][i]] += 1
+            resident = (int(masks[l][r["orig_ids"][i] >> 5]) >> (r["orig_ids"][i] & 31)) & 1
+            if r["final_ids"][i] != r["orig_ids"][i]:
+                assert r["source"][i] == 3 and not resident
+                assert (int(masks[l][r["final_ids"][i] >> 5]) >> (r["final_ids"][i] & 31)) & 1
+            else:
+                assert r["source"][i] == (0 if resident else 2)
+        assert r["n_subs"] == sum(a != b for a, b in zip(r["orig_ids"], r["final_ids"]))
+        subs += r["n_subs"]
+        assert abs(sum(r["orig_scores"]) - 1.0) < 1e-5
+        if l == 0:       # the first layer's input is the token itself: compare with the oracle
+            rr, w = H.glue(fb, seed, 0, n_embd)
+            hh = oracle.rms_norm(toks[r["token"]] + rr, w, eps)
+            ids, scores, _, nsub = oracle.route(H.router_weights(fb, seed, 0, n_experts, n_embd), hh, top_k, masks[0],
+                                                0.35, True)
+            assert r["final_ids"] == [int(e) for e in ids] and r["n_subs"] == nsub
+            assert np.allclose(r["final_scores"], scores, rtol=2e-5, atol=0)
+    assert subs > 0 and subs == d.substitutions()
+    assert (op.expert_freq() == hist).all() and (d.expert_freq() == hist).all()
+    keep = os.environ.get("FOMOE_KEEP_TRACE")      # a copy for the CPU-side format test's fixture
+    if keep:
+        import shutil
+        shutil.copy(path, keep)
+    op.close()
+    d.close()

@@ -103,3 +103,35 @@ def test_expert_engine_twin(fb, oracle):
     _, comp_us, n = eng.timing()
     assert n >= 2 and comp_us > 0
     eng.close()
+
+
+def test_down_type_alternates_without_rebuilding(fb, oracle):
+    """The 397B model alternates Q6_K and Q4_K down projections from layer to layer: one operator context and one
+    expert engine take both (and Q5_K) call after call, and an engine keeps its accumulated sum and quantised input
+    when the type changes between two b200_expert_ffn calls of the same layer."""
+    n_embd, inter, seed = 2048, 512, 79
+    gs = fb.matrix_bytes(H.Q4, inter, n_embd)
+    h = H.hidden(fb, seed, 0, n_embd)
+    op = fb.GpuOperator()
+    for rnd in range(2):
+        for dt in (H.Q6, H.Q4, H.Q5):
+            ex = _experts(fb, seed + dt, 4, dt, n_embd, inter)
+            sc = np.array([0.4, 0.3, 0.2, 0.1], dtype=np.float32)
+            rc, out = op.expert_ffn(h, ex, sc, n_embd, inter, gs, gs, ex[0].size, H.Q4, H.Q4, dt)
+            assert rc == 0
+            want = oracle.moe_block(h, ex, sc, None, H.Q4, H.Q4, dt, gs, gs, n_embd, inter)
+            assert H.rel_l2(out, want) < 3e-4, (rnd, dt)
+    op.close()
+    eng = fb.ExpertEngine(n_embd, inter)
+    e6 = _experts(fb, seed, 2, H.Q6, n_embd, inter)
+    e4 = _experts(fb, seed + 1, 2, H.Q4, n_embd, inter)
+    eng.reset()
+    eng.ffn(e6[0], h, 0.5, H.Q4, H.Q4, H.Q6, gs, gs)
+    eng.ffn(e4[0], h, 0.3, H.Q4, H.Q4, H.Q4, gs, gs)       # another type inside the same layer
+    eng.ffn(e6[1], h, 0.2, H.Q4, H.Q4, H.Q6, gs, gs)
+    one = np.ones(1, dtype=np.float32)
+    want = (0.5 * oracle.moe_block(h, [e6[0]], one, None, H.Q4, H.Q4, H.Q6, gs, gs, n_embd, inter)
+            + 0.3 * oracle.moe_block(h, [e4[0]], one, None, H.Q4, H.Q4, H.Q4, gs, gs, n_embd, inter)
+            + 0.2 * oracle.moe_block(h, [e6[1]], one, None, H.Q4, H.Q4, H.Q6, gs, gs, n_embd, inter))
+    assert H.rel_l2(eng.result(), want) < 3e-4
+    eng.close()

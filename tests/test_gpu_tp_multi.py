@@ -18,8 +18,9 @@ SHAPE = dict(n_layers=3, n_embd=1024, n_inter=1024, n_experts=32, top_k=4)
 SEED = 19
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, n_inter=1024):
     try:
+        SHAPE["n_inter"] = n_inter
         _run_rank(rank, world, port, q)
     except Exception as e:      # report instead of leaving the parent waiting for its time-out
         import traceback
@@ -79,16 +80,19 @@ def _run_rank(rank, world, port, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_tensor_parallel_stack_across_gpus(fb, world):
+@pytest.mark.parametrize("world,n_inter", [(2, 1024), (4, 1024), (4, 512), (8, 1024)])
+def test_tensor_parallel_stack_across_gpus(fb, world, n_inter):
+    """(4, 512) and (8, 1024) have twice as many ranks as 256-wide windows: two ranks share a window, each owns one
+    half of the down super-blocks (see the C header)."""
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
+    SHAPE["n_inter"] = n_inter
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29600 + os.getpid() % 1000 + world
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    port = 29600 + os.getpid() % 1000 + world + (16 if n_inter != 1024 else 0)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, n_inter)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=240) for _ in range(world)]
@@ -118,3 +122,52 @@ def test_tensor_parallel_stack_across_gpus(fb, world):
         assert (H.bits(one) == H.bits(out[1])).all()           # host-to-host call == resident run
         assert H.rel_l2(out, want) < 1e-4                       # == single GPU up to reassociation
     single.close()
+
+
+def test_two_ranks_in_one_process(fb):
+    """Both ranks live in ONE process (one context per GPU, as the reference drives its two GPUs, src/tp.hip): plain
+    device pointers instead of IPC handles, peer access enabled by the library, one host thread per rank.  Also covers
+    kernel attributes that are per device (dynamic shared memory of the stack kernel on a second device)."""
+    import threading
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    dts = [H.Q6, H.Q4, H.Q6]
+    SHAPE["n_inter"] = 1024
+    ds = [fb.MoeDecoder(SHAPE["n_layers"], SHAPE["n_embd"], SHAPE["n_inter"], SHAPE["n_experts"], SHAPE["top_k"], True, dts,
+                        device=r, tp_rank=r, tp_size=2, rms_eps=1e-6, max_tokens=4) for r in range(2)]
+    for r, d in enumerate(ds):
+        d.generate(SEED)
+        d.tp_enable_peer(1 - r)
+    ptrs = [d.tp_recv_ptr() for d in ds]
+    for d in ds:
+        d.tp_connect_ptrs(ptrs)
+        d.set_wait_limit(1 << 21)
+    toks = np.stack([H.hidden(fb, SEED, t, SHAPE["n_embd"]) for t in range(4)])
+    outs, errs = [None, None], []
+
+    def run(r):
+        try:
+            ds[r].tokens_upload(0, toks)
+            ds[r].tokens_run(0, 4)
+            outs[r] = ds[r].tokens_download(0, 4)
+        except Exception as e:      # a failed rank makes the other give up after its bounded wait
+            errs.append((r, repr(e)))
+
+    ths = [threading.Thread(target=run, args=(r,)) for r in range(2)]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join(timeout=120)
+    assert not errs, errs
+    assert all(d.status() == 0 for d in ds)
+    assert (H.bits(outs[0]) == H.bits(outs[1])).all()
+    single = fb.MoeDecoder(SHAPE["n_layers"], SHAPE["n_embd"], SHAPE["n_inter"], SHAPE["n_experts"], SHAPE["top_k"], True,
+                           dts, rms_eps=1e-6, max_tokens=4)
+    single.generate(SEED)
+    single.tokens_upload(0, toks)
+    single.tokens_run(0, 4)
+    assert H.rel_l2(outs[0], single.tokens_download(0, 4)) < 1e-4
+    single.close()
+    for d in ds:
+        d.close()

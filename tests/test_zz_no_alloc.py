@@ -56,3 +56,28 @@ def test_noalloc_refuses_what_does_not_fit(fb):
     assert lib.fomoe_b200_matvec_noalloc(H.Q4, _dev(d), 4, 16384, _dev(d), _dev(d), None) == -1   # > 8192 columns
     assert lib.fomoe_b200_matvec_noalloc(8, _dev(d), 4, 256, _dev(d), _dev(d), None) == -1        # Q8_0: not a type it takes
     assert lib.fomoe_b200_matvec_noalloc(H.Q4, None, 4, 256, _dev(d), _dev(d), None) == -1
+
+
+def test_noalloc_second_device_after_the_first(fb, oracle):
+    """The array's device address is looked up per device: a call on device 1 after calls on device 0 must use
+    device 1's copy (needs two GPUs)."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    lib = fb.lib()
+    qtype, rows, cols = H.Q4, 512, 1024
+    w = fb.synth_matrix(77, 0, 0, fb.M_GATE, qtype, rows, cols)
+    x = H.hidden(fb, 77, 0, cols)
+    want = oracle.matvec_q8(w, qtype, x, rows, cols)
+    outs = []
+    for dev in (0, 1, 0):
+        torch.cuda.set_device(dev)
+        w_dev, x_dev = torch.from_numpy(w).cuda(dev), torch.from_numpy(x).cuda(dev)
+        y_dev = torch.full((rows,), float("nan"), dtype=torch.float32, device=f"cuda:{dev}")
+        torch.cuda.synchronize(dev)
+        assert lib.fomoe_b200_matvec_noalloc(qtype, _dev(w_dev), rows, cols, _dev(x_dev), _dev(y_dev), None) == 0
+        torch.cuda.synchronize(dev)
+        outs.append(y_dev.cpu().numpy())
+        assert H.rel_l2(outs[-1], want) < 2e-6
+    assert (H.bits(outs[0]) == H.bits(outs[1])).all() and (H.bits(outs[0]) == H.bits(outs[2])).all()
+    torch.cuda.set_device(0)
