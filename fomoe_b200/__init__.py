@@ -17,7 +17,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfomoe_b200.so")
+LIB_PATH = os.environ.get("FOMOE_B200_LIB") or os.path.join(_HERE, "libfomoe_b200.so")  # override: a differently built library
 
 TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K = 12, 13, 14
 STREAM_ROUTER, STREAM_RESID, STREAM_NORMW, STREAM_HIDDEN = 3, 4, 5, 6

@@ -1132,6 +1132,9 @@ static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int first, i
     fb_stack_args_t k;
     k.layers = c->d_layer_args + l0;
     k.n_layers = l1 - l0;
+    k.down_mode = c->down_half >= 0 ? 2 : 0;
+    for (int l = 0; l < c->cfg.n_layers; l++)
+        if (c->down_half < 0 && c->down_types[l] == FB_TYPE_Q5_K) k.down_mode = 1;
     k.tok_count = count;
     k.tok_first = first;
     k.tok_in = c->tok_in;

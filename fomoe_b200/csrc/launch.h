@@ -119,6 +119,7 @@ int fb_launch_down_ring(const fb_args_t *a, int grid, void *stream);
 typedef struct {
     const fb_args_t *layers; /* device array, one entry per layer of the range to run */
     int n_layers;
+    int down_mode;           /* down formats among the layers: 0 whole Q4_K/Q6_K, 1 whole incl. Q5_K, 2 half super-blocks */
     int tok_count;           /* tokens tok_first .. tok_first + tok_count - 1 */
     int tok_first;
     const float *tok_in;

@@ -76,75 +76,86 @@ static __device__ __noinline__ float fb_exact_logit(const fb_args_t &A, const fl
     return exact;
 }
 
-/* Cache-aware routing over one residency tier (src/car.c:36-264; classify as src/gpu_kernels.hip:7097-7149), run by
- * one warp on the renormalised selection in W->ci / W->cv.  Returns the number of substitutions.  Out of line: it
- * only runs when a residency mask and a threshold inside (0, 1) are set. */
-static __device__ __noinline__ int fb_select_car(const fb_args_t &A, fb_sel_smem_t *W, const float *all_scores, int lane) {
-    const int nE = A.n_experts, k = A.top_k;
-    int n_subs = 0;
-
-    uint32_t res = 0, sel = 0; /* bit j <-> expert j*32 + lane */
-#pragma unroll
-    for (int j = 0; j < FB_EPL; j++)
-        if ((__ldg(A.resident + j) >> lane) & 1u) res |= 1u << j;
-    for (int r = 0; r < k; r++) {
-        const int e = W->ci[r];
-        if ((e & 31) == lane) sel |= 1u << (e >> 5);
+/* The block's best 16 of one (value, id) pair per thread, in order (value descending, lower id first), left in
+ * W->lv[1][slot][*] / W->li[1][slot][*].  Every warp sorts its 32 pairs; the best 16 of each warp (256 candidates) are
+ * merged by rank: candidate p of warp list w has p better entries in its own list, a 5-step binary search in each of
+ * the other 15 sorted lists counts the rest; ranks below 16 are the block's best 16.  Called by all 512 threads.
+ * Out of line and shared by the selection proper, its repeat after the near-tie arbiter and cache-aware routing: one
+ * copy of this code stays in the instruction cache from layer to layer (inlined at each use the stack kernel's hot
+ * path outgrew the cache, and every phase of every layer slowed down by a third). */
+static __device__ __noinline__ void fb_block_best16(fb_sel_smem_t *W, float v, int id, int slot) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    fb_sort32(v, id, lane);
+    if (lane < 16) {
+        W->lv[0][warp][lane] = v;
+        W->li[0][warp][lane] = id;
     }
-    int c_idx[FB_MAX_TOPK], c_best[FB_MAX_TOPK];
-    float c_score[FB_MAX_TOPK], c_ratio[FB_MAX_TOPK];
-    int nc = 0;
-    for (int r = 0; r < k; r++) {
-        const int orig = W->ci[r];
-        if ((__ldg(A.resident + (orig >> 5)) >> (orig & 31)) & 1u) continue; /* cached: uniform */
-        float bv = 0.0f; /* strict improvement over 0: src/car.c:104-112 */
-        int bi = 0x7fffffff;
+    __syncthreads();
+    if (tid < 256) {
+        const int w = tid >> 4, p = tid & 15;
+        const float mv = W->lv[0][w][p];
+        const int mi = W->li[0][w][p];
+        int rank = p;
+#pragma unroll /* fully unrolled on purpose: the fifteen searches overlap (unrolled by 3 or 5: no faster, by 1: slower) */
+        for (int o = 1; o < 16; o++) {
+            const int w2 = (w + o) & 15;
+            int pos = 0;
 #pragma unroll
-        for (int j = 0; j < FB_EPL; j++) {
-            const int e = j * 32 + lane;
-            if (((res >> j) & 1u) && !((sel >> j) & 1u) && e < nE) {
-                const float pe = all_scores[e];
-                if (pe > 0.0f && fb_better(pe, e, bv, bi)) {
-                    bv = pe;
-                    bi = e;
-                }
+            for (int st = 8; st > 0; st >>= 1)
+                if (fb_better(W->lv[0][w2][pos + st - 1], W->li[0][w2][pos + st - 1], mv, mi)) pos += st;
+            if (fb_better(W->lv[0][w2][pos], W->li[0][w2][pos], mv, mi)) pos++;
+            rank += pos;
+        }
+        if (rank < 16) {
+            W->lv[1][slot][rank] = mv;
+            W->li[1][slot][rank] = mi;
+        }
+    }
+    __syncthreads();
+}
+
+/* Cache-aware routing over one residency tier (src/car.c:36-264; classify as src/gpu_kernels.hip:7097-7149) on the
+ * renormalised selection in W->ci / W->cv.  The CPU walks the uncached positions in list order and, for each, scans
+ * all experts for the best-scoring resident one that is neither selected nor already taken as a substitute; it is
+ * accepted (and from then on taken) when its score is at least `threshold` times the original's.  A rejected
+ * candidate stays available, so position after position meets the SAME ordered list of resident, unselected experts
+ * and moves one entry down it per acceptance: the list's first top_k entries are all that can ever be used.  The
+ * block forms that list once (every thread offers its expert's probability if it is resident, not selected and
+ * positive; best 16 by (probability descending, lower index first), the CPU's scan order) and one thread walks it.
+ * Substitutions touch only their own slot, so the order in which the CPU applies them (by ratio) does not matter
+ * while its per-token budgets are off, as they are by default.  Called by all threads; returns (in warp 0) the
+ * number of substitutions. */
+__device__ __forceinline__ int fb_select_car(const fb_args_t &A, fb_sel_smem_t *W, const float *all_scores, float my_p,
+                                             uint32_t my_resident_word) {
+    const int tid = threadIdx.x, nE = A.n_experts, k = A.top_k;
+    bool eligible = tid < nE && ((my_resident_word >> (tid & 31)) & 1u) && my_p > 0.0f;
+    for (int r = 0; r < k; r++)
+        if (W->ci[r] == tid) eligible = false;
+    /* warp w holds mask word w: parked in shared memory for the walk below (a global load per position costs a
+     * trip to L2 each) */
+    if ((tid & 31) == 0) W->li[1][3][tid >> 5] = (int)my_resident_word;
+    fb_block_best16(W, eligible ? my_p : -INFINITY, eligible ? tid : 0x7fffffff, 1);
+    int nc = 0;
+    if (tid == 0) {
+        int next = 0;
+        bool any = false;
+        for (int r = 0; r < k && next < 16; r++) {
+            const int orig = W->ci[r];
+            if (((uint32_t)W->li[1][3][orig >> 5] >> (orig & 31)) & 1u) continue; /* cached */
+            const float bv = W->lv[1][1][next];
+            const int bi = W->li[1][1][next];
+            if (bi == 0x7fffffff) break; /* no resident expert left to offer */
+            const float ov = all_scores[orig];
+            const float ratio = (ov > 0.0f) ? __fdiv_rn(bv, ov) : 0.0f;
+            if (ratio >= A.car_threshold) {
+                W->ci[r] = bi;
+                W->cv[r] = A.car_dampen ? __fmul_rn(W->cv[r], ratio) : bv;
+                next++; /* taken: later positions see the next entry */
+                nc++;
+                any = true;
             }
         }
-        fb_warp_best(bv, bi);
-        const float ov = all_scores[orig];
-        const float ratio = (ov > 0.0f) ? __fdiv_rn(bv, ov) : 0.0f;
-        if (bi != 0x7fffffff && ratio >= A.car_threshold) {
-            c_idx[nc] = r;
-            c_best[nc] = bi;
-            c_score[nc] = bv;
-            c_ratio[nc] = ratio;
-            nc++;
-            if ((bi & 31) == lane) sel |= 1u << (bi >> 5); /* reserved at once */
-        }
-    }
-    for (int a = 1; a < nc; a++) { /* stable insertion by ratio descending (src/car.c:168-176) */
-        const int ti = c_idx[a], tb = c_best[a];
-        const float ts = c_score[a], tr = c_ratio[a];
-        int b = a - 1;
-        while (b >= 0 && c_ratio[b] < tr) {
-            c_idx[b + 1] = c_idx[b];
-            c_best[b + 1] = c_best[b];
-            c_score[b + 1] = c_score[b];
-            c_ratio[b + 1] = c_ratio[b];
-            b--;
-        }
-        c_idx[b + 1] = ti;
-        c_best[b + 1] = tb;
-        c_score[b + 1] = ts;
-        c_ratio[b + 1] = tr;
-    }
-    if (lane == 0) {
-        for (int c = 0; c < nc; c++) {
-            const int r = c_idx[c];
-            W->ci[r] = c_best[c];
-            W->cv[r] = A.car_dampen ? __fmul_rn(W->cv[r], c_ratio[c]) : c_score[c];
-        }
-        if (nc > 0 && !A.car_dampen) {
+        if (any && !A.car_dampen) {
             float s2 = 0.0f;
             for (int r = 0; r < k; r++) s2 = __fadd_rn(s2, W->cv[r]);
             if (s2 > 0.0f) {
@@ -152,10 +163,10 @@ static __device__ __noinline__ int fb_select_car(const fb_args_t &A, fb_sel_smem
                 for (int r = 0; r < k; r++) W->cv[r] = __fmul_rn(W->cv[r], i2);
             }
         }
+        W->li[1][2][0] = nc;
     }
-    n_subs = nc;
-    __syncwarp();
-    return n_subs;
+    __syncthreads();
+    return W->li[1][2][0];
 }
 
 /* Must be called by all 512 threads of the block.  Outputs (shared memory): ids[n_slots], scores[n_slots],
@@ -168,39 +179,13 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nE = A.n_experts, k = A.top_k, kk = min(k + 1, nE);
     float lg = (tid < nE) ? __ldcg(A.logits + tid) : -INFINITY;
+    /* cache-aware routing on for this layer?  (the same for every thread; its mask word is requested now) */
+    const bool car_on = A.resident && A.car_threshold > 0.0f && A.car_threshold < 1.0f;
+    const uint32_t res_word = car_on ? __ldg(A.resident + (tid >> 5)) : 0u;
 
+#pragma unroll 1
     for (int pass = 0; pass < 2; pass++) {
-        float v = lg;
-        int id = (tid < nE) ? tid : 0x7fffffff;
-        fb_sort32(v, id, lane);
-        if (lane < 16) {
-            W->lv[0][warp][lane] = v;
-            W->li[0][warp][lane] = id;
-        }
-        __syncthreads();
-        /* merge by rank: candidate p of warp list w has p better entries in its own list; a 5-step binary search
-         * in each of the other 15 sorted lists counts the rest.  Ranks below 16 are the block's best 16, in order. */
-        if (tid < 256) {
-            const int w = tid >> 4, p = tid & 15;
-            const float mv = W->lv[0][w][p];
-            const int mi = W->li[0][w][p];
-            int rank = p;
-#pragma unroll /* fully unrolled on purpose: the fifteen searches overlap; unrolled by three the selection took 0.4 us longer */
-            for (int o = 1; o < 16; o++) {
-                const int w2 = (w + o) & 15;
-                int pos = 0;
-#pragma unroll
-                for (int st = 8; st > 0; st >>= 1)
-                    if (fb_better(W->lv[0][w2][pos + st - 1], W->li[0][w2][pos + st - 1], mv, mi)) pos += st;
-                if (fb_better(W->lv[0][w2][pos], W->li[0][w2][pos], mv, mi)) pos++;
-                rank += pos;
-            }
-            if (rank < 16) {
-                W->lv[1][0][rank] = mv;
-                W->li[1][0][rank] = mi;
-            }
-        }
-        __syncthreads();
+        fb_block_best16(W, lg, (tid < nE) ? tid : 0x7fffffff, 0);
         /* best 16 now in lv[1][0][*] */
         if (pass == 1) break;
         uint32_t flag = 0;
@@ -281,10 +266,16 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
         }
         __syncwarp();
         if (leader && A.freq && lane < k) atomicAdd(A.freq + W->ci[lane], 1u);
+    }
 
-        /* ---- CAR ---- */
-        int n_subs = 0;
-        if (A.resident && A.car_threshold > 0.0f && A.car_threshold < 1.0f) n_subs = fb_select_car(A, W, all_scores, lane);
+    /* ---- CAR (all threads) ---- */
+    int n_subs = 0;
+    if (car_on) {
+        __syncthreads(); /* warp 0 has left the selection before substitution in W->ci / W->cv */
+        n_subs = fb_select_car(A, W, all_scores, p, res_word);
+    }
+
+    if (warp == 0) {
         if (lane < k) {
             int e = W->ci[lane];
             if (e < 0 || e >= nE) {

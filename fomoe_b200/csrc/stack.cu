@@ -254,11 +254,20 @@ __device__ __forceinline__ unsigned long long sk_now() {
  * nanoseconds of %globaltimer, 9 per layer, for profiling only */
 #define SK_STAMP(idx)                                                                             \
     do {                                                                                          \
-        if (trace_p && trace_n < K.trace_cap)                                                     \
+        if (TRACE && trace_p && trace_n < K.trace_cap)                                            \
             trace_p[trace_n++] = ((unsigned long long)(idx) << 56) | (sk_now() & 0x00ffffffffffffffULL); \
     } while (0)
 
-template <bool TP>
+/* TP: tensor-parallel exchange compiled in.  DM: which down-projection formats the instance carries -- the kernel is
+ * instantiated per format family so that a run executes (and keeps in the instruction cache) only the dot products
+ * it needs: the hot path is large, and code that is merely present between the hot instructions cost 1.7 us per layer
+ * on the benchmark's Q4_K/Q6_K stack when all formats shared one instance.  TRACE: the phase stamps (another 0.4 us
+ * per layer when compiled in and switched off). */
+#define SK_DM_WHOLE 0    /* whole super-blocks, Q4_K and Q6_K */
+#define SK_DM_WHOLE_Q5 1 /* ... and Q5_K */
+#define SK_DM_HALF 2     /* half super-blocks (Q4_K, Q6_K): twice as many ranks as activation windows */
+
+template <bool TP, int DM, bool TRACE>
 __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
     extern __shared__ __align__(128) uint8_t dsm[];
     uint8_t *ring = dsm;
@@ -284,7 +293,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
     int trace_n = 0;
     /* where this thread records its stamps: thread 0 of the traced block (of every block when trace_cta < 0) */
     unsigned long long *trace_p = nullptr;
-    if (K.trace && tid == 0 && (K.trace_cta < 0 || cta == K.trace_cta))
+    if (TRACE && K.trace && tid == 0 && (K.trace_cta < 0 || cta == K.trace_cta))
         trace_p = K.trace + (K.trace_cta < 0 ? (size_t)cta * K.trace_cap : 0);
     bool alive = true;
     bool pending_join = false; /* a barrier has been arrived at but not yet waited for */
@@ -547,7 +556,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
              *      long run per block dealt round-robin to 12 warps (two ring stages of one group each). */
             sk_arrive(B, S);
             const int ns = A.n_slots, dbpr = A.down_bpr, drpg = 32 / dbpr;
-            const uint32_t GB = (uint32_t)fb_group_bytes_h(A.down_type, A.down_half);
+            const uint32_t GB = (DM == SK_DM_HALF) ? (A.down_type == FB_TYPE_Q4_K ? FB_Q4K_HGROUP : FB_Q6K_HGROUP)
+                                : (A.down_type == FB_TYPE_Q4_K) ? FB_Q4K_GROUP
+                                : (DM == SK_DM_WHOLE_Q5 && A.down_type == FB_TYPE_Q5_K) ? FB_Q5K_GROUP : FB_Q6K_GROUP;
             const int dtotal = A.down_groups * ns;
             const int d0 = (int)(((long long)cta * dtotal) / G), d1 = (int)(((long long)(cta + 1) * dtotal) / G);
             /* the run [d0, d1): its last row group continues in the next block when d1 is not a multiple of ns;
@@ -609,7 +620,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     const uint32_t st = dring_u + s * FB_Q6K_GROUP + 16 * lane;
                     const uint32_t a_u = fb_smem_u32(&S->q8a[slot * dbpr + lane % dbpr]);
                     float f;
-                    if (A.down_half >= 0 && A.down_type == FB_TYPE_Q4_K) { /* half super-blocks (layout.h) */
+                    if (DM == SK_DM_HALF && A.down_type == FB_TYPE_Q4_K) { /* half super-blocks (layout.h) */
                         const uint4 hd = fb_lds128(st);
                         uint4 q[4];
 #pragma unroll
@@ -617,7 +628,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         __syncwarp();
                         if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
                         f = fb_dot_q4k_half_sm(hd, q, a_u, A.down_half);
-                    } else if (A.down_half >= 0) {
+                    } else if (DM == SK_DM_HALF) {
                         uint4 ql[4], qh[2];
 #pragma unroll
                         for (int k = 0; k < 4; k++) ql[k] = fb_lds128(st + 512 * k);
@@ -637,7 +648,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         __syncwarp();
                         if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
                         f = fb_dot_q4k_sm(hd, q, a_u);
-                    } else if (A.down_type == FB_TYPE_Q5_K) {
+                    } else if (DM == SK_DM_WHOLE_Q5 && A.down_type == FB_TYPE_Q5_K) {
                         const uint4 hd = fb_lds128(st), h0 = fb_lds128(st + 512), h1 = fb_lds128(st + 1024);
                         uint4 q[8];
 #pragma unroll
@@ -796,19 +807,35 @@ extern "C" int fb_stack_supported(const fb_args_t *a, int grid) {
            a->n_embd / FB_QK <= 16 && a->tp_size <= FB_MAX_TP && a->inter_local % FB_QK == 0 && max_rg <= SK_MAX_RG;
 }
 
-extern "C" int fb_launch_stack(const fb_stack_args_t *k, int grid, void *stream) {
-    static unsigned char configured[64]; /* the attribute holds for one device: one flag per device ordinal */
-    const int sm = fb_stack_smem_bytes();
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+template <bool TP, int DM, bool TRACE>
+static int sk_launch2(fb_stack_args_t &kk, int grid, int sm, int dev, void *stream) {
+    static unsigned char configured[64]; /* the attribute holds for one device: one flag per device ordinal and instance */
     if (!configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_stack<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(k_stack<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
+        const cudaError_t e = cudaFuncSetAttribute(k_stack<TP, DM, TRACE>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
         if (e != cudaSuccess) return (int)e;
         configured[dev] = 1;
     }
-    fb_stack_args_t kk = *k;
     void *params[] = {&kk};
-    const void *fn = kk.tp_size > 1 ? (const void *)k_stack<true> : (const void *)k_stack<false>;
-    return (int)cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(SK_THREADS), params, (size_t)sm, (cudaStream_t)stream);
+    return (int)cudaLaunchCooperativeKernel((const void *)k_stack<TP, DM, TRACE>, dim3(grid), dim3(SK_THREADS), params,
+                                            (size_t)sm, (cudaStream_t)stream);
+}
+
+template <bool TP, int DM>
+static int sk_launch(fb_stack_args_t &kk, int grid, int sm, int dev, void *stream) {
+    return (kk.trace && kk.trace_cap > 0) ? sk_launch2<TP, DM, true>(kk, grid, sm, dev, stream)
+                                          : sk_launch2<TP, DM, false>(kk, grid, sm, dev, stream);
+}
+
+extern "C" int fb_launch_stack(const fb_stack_args_t *k, int grid, void *stream) {
+    const int sm = fb_stack_smem_bytes();
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    fb_stack_args_t kk = *k;
+    const bool tp = kk.tp_size > 1;
+    switch (kk.down_mode) {
+        case SK_DM_WHOLE: return tp ? sk_launch<true, SK_DM_WHOLE>(kk, grid, sm, dev, stream) : sk_launch<false, SK_DM_WHOLE>(kk, grid, sm, dev, stream);
+        case SK_DM_WHOLE_Q5: return tp ? sk_launch<true, SK_DM_WHOLE_Q5>(kk, grid, sm, dev, stream) : sk_launch<false, SK_DM_WHOLE_Q5>(kk, grid, sm, dev, stream);
+        case SK_DM_HALF: return tp ? sk_launch<true, SK_DM_HALF>(kk, grid, sm, dev, stream) : (int)cudaErrorInvalidValue;
+    }
+    return (int)cudaErrorInvalidValue;
 }
