@@ -36,6 +36,12 @@ class Config(C.Structure):
                 ("car_threshold", C.c_float), ("car_dampen", C.c_int), ("max_tokens", C.c_int)]
 
 
+class BatchConfig(C.Structure):
+    _fields_ = [("device", C.c_int), ("n_layers", C.c_int), ("n_embd", C.c_int), ("n_inter", C.c_int),
+                ("n_experts", C.c_int), ("top_k", C.c_int), ("has_shared", C.c_int), ("max_tokens", C.c_int),
+                ("rms_eps", C.c_float)]
+
+
 class Work(C.Structure):
     _fields_ = [("expert_data", C.c_void_p), ("score", C.c_float), ("gate_type", C.c_int), ("up_type", C.c_int),
                 ("down_type", C.c_int), ("expert_gate_size", C.c_uint64), ("expert_up_size", C.c_uint64)]
@@ -118,6 +124,21 @@ _SIGS = {
     "fomoe_b200_matvec": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p, _f32p]),
     "fomoe_b200_matvec_noalloc": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "fomoe_b200_quantize_q8k": (C.c_int, [C.c_void_p, _f32p, C.c_int, C.c_void_p]),
+    "fomoe_b200_batch_create": (C.c_void_p, [C.POINTER(BatchConfig)]),
+    "fomoe_b200_batch_destroy": (None, [C.c_void_p]),
+    "fomoe_b200_batch_last_error": (C.c_char_p, [C.c_void_p]),
+    "fomoe_b200_batch_status": (C.c_int, [C.c_void_p]),
+    "fomoe_b200_batch_table_bytes": (C.c_uint64, [C.c_void_p]),
+    "fomoe_b200_batch_kernel_launches": (C.c_uint64, [C.c_void_p]),
+    "fomoe_b200_batch_generate": (C.c_int, [C.c_void_p, C.c_uint64, C.c_int]),
+    "fomoe_b200_batch_upload": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "fomoe_b200_batch_export": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "fomoe_b200_batch_moe_layer": (C.c_int, [C.c_void_p, C.c_int, C.c_int, _f32p, _f32p, _f32p, _i32p, _f32p]),
+    "fomoe_b200_batch_tokens_upload": (C.c_int, [C.c_void_p, C.c_int, _f32p]),
+    "fomoe_b200_batch_stack_run": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, _f32p]),
+    "fomoe_b200_batch_tokens_download": (C.c_int, [C.c_void_p, C.c_int, _f32p]),
+    "fomoe_b200_batch_get_routing": (C.c_int, [C.c_void_p, C.c_int, _i32p, _f32p, _i32p]),
+    "fomoe_b200_batch_synth_logits": (None, [C.c_uint64, C.c_int, C.c_int, C.c_int, C.c_int, _f32p]),
     "fomoe_b200_synth_matrix": (None, [C.c_uint64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "fomoe_b200_synth_f32": (None, [C.c_uint64, C.c_int, C.c_int, C.c_float, C.c_float, C.c_uint64, _f32p]),
 }
@@ -591,3 +612,96 @@ class ExpertEngine:
         a, b, n = C.c_double(0), C.c_double(0), C.c_int(0)
         self._l.b200_expert_get_timing(self._h, C.byref(a), C.byref(b), C.byref(n))
         return a.value, b.value, n.value
+
+
+class BatchedMoe:
+    """Many tokens per call (prefill / batched decode): routed-expert FFN on the tensor cores, Q4_K experts."""
+
+    def __init__(self, n_layers, n_embd, n_inter, n_experts, top_k, has_shared=True, max_tokens=512, device=0,
+                 rms_eps=1e-6):
+        self._l = lib()
+        self.n_layers, self.n_embd, self.n_inter = n_layers, n_embd, n_inter
+        self.n_experts, self.top_k, self.has_shared, self.max_tokens = n_experts, top_k, bool(has_shared), max_tokens
+        cfg = BatchConfig(device, n_layers, n_embd, n_inter, n_experts, top_k, int(bool(has_shared)), max_tokens, rms_eps)
+        self._h = self._l.fomoe_b200_batch_create(C.byref(cfg))
+        if not self._h:
+            raise RuntimeError("fomoe_b200_batch_create failed (no CUDA device, unsupported shape or out of memory)")
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._l.fomoe_b200_batch_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def _ck(self, rc, what):
+        if rc != 0:
+            raise RuntimeError(f"{what}: {self._l.fomoe_b200_batch_last_error(self._h).decode()}")
+
+    def record_bytes(self):
+        return 2 * matrix_bytes(TYPE_Q4_K, self.n_inter, self.n_embd) + matrix_bytes(TYPE_Q4_K, self.n_embd, self.n_inter)
+
+    def table_bytes(self):
+        return int(self._l.fomoe_b200_batch_table_bytes(self._h))
+
+    def kernel_launches(self):
+        return int(self._l.fomoe_b200_batch_kernel_launches(self._h))
+
+    def status(self):
+        return int(self._l.fomoe_b200_batch_status(self._h))
+
+    def generate(self, seed, with_logits=False):
+        self._ck(self._l.fomoe_b200_batch_generate(self._h, seed, int(bool(with_logits))), "batch_generate")
+
+    def upload_expert(self, layer, expert, record):
+        r = np.ascontiguousarray(record).view(np.uint8).reshape(-1)
+        assert r.size == self.record_bytes()
+        self._ck(self._l.fomoe_b200_batch_upload(self._h, layer, expert, r.ctypes.data), "batch_upload")
+
+    def export_expert(self, layer, expert):
+        out = np.empty(self.record_bytes(), dtype=np.uint8)
+        self._ck(self._l.fomoe_b200_batch_export(self._h, layer, expert, out.ctypes.data), "batch_export")
+        return out
+
+    def moe_layer(self, layer, h, logits):
+        """h [T, n_embd], logits [T, n_experts] -> dict(out [T, n_embd], ids [T, k], scores [T, k])."""
+        h = _f32(h).reshape(-1, self.n_embd)
+        lg = _f32(logits).reshape(-1, self.n_experts)
+        T = h.shape[0]
+        assert lg.shape[0] == T
+        out = np.empty_like(h)
+        ids = np.empty((T, self.top_k), dtype=np.int32)
+        sc = np.empty((T, self.top_k), dtype=np.float32)
+        self._ck(self._l.fomoe_b200_batch_moe_layer(self._h, layer, T, _fp(h), _fp(lg), _fp(out), _ip(ids), _fp(sc)),
+                 "batch_moe_layer")
+        return dict(out=out, ids=ids, scores=sc)
+
+    def tokens_upload(self, x):
+        x = _f32(x).reshape(-1, self.n_embd)
+        self._ck(self._l.fomoe_b200_batch_tokens_upload(self._h, x.shape[0], _fp(x)), "batch_tokens_upload")
+
+    def stack_run(self, n_tokens, l0=0, l1=None):
+        """Layers [l0, l1) on the resident tokens; returns CUDA-event milliseconds."""
+        ms = C.c_float(0.0)
+        self._ck(self._l.fomoe_b200_batch_stack_run(self._h, n_tokens, l0, self.n_layers if l1 is None else l1, C.byref(ms)),
+                 "batch_stack_run")
+        return float(ms.value)
+
+    def tokens_download(self, n_tokens):
+        out = np.empty((n_tokens, self.n_embd), dtype=np.float32)
+        self._ck(self._l.fomoe_b200_batch_tokens_download(self._h, n_tokens, _fp(out)), "batch_tokens_download")
+        return out
+
+    def get_routing(self, n_tokens):
+        ids = np.empty((n_tokens, self.top_k), dtype=np.int32)
+        sc = np.empty((n_tokens, self.top_k), dtype=np.float32)
+        cnt = np.empty(self.n_experts + int(self.has_shared), dtype=np.int32)
+        self._ck(self._l.fomoe_b200_batch_get_routing(self._h, n_tokens, _ip(ids), _fp(sc), _ip(cnt)), "batch_get_routing")
+        return ids, sc, cnt
+
+
+def synth_logits(seed, layer, n_tokens, n_experts):
+    """Seeded router logits N(0, 1) of a layer as the batched benchmark configuration draws them: [n_tokens, n_experts]."""
+    out = np.empty((n_tokens, n_experts), dtype=np.float32)
+    lib().fomoe_b200_batch_synth_logits(seed, layer, n_tokens, n_experts, n_tokens, _fp(out))
+    return out

@@ -282,6 +282,54 @@ int fomoe_b200_matvec_noalloc(int type, const void *w_ggml_dev, int rows, int co
                               void *stream);
 int fomoe_b200_quantize_q8k(fomoe_b200_ctx_t *ctx, const float *x, int n, void *q8k_out /* n/256 * 292 B, reference block_q8_K */);
 
+/* ======================================================================================
+ * 4. Batched routed-expert FFN: many tokens per call (prefill, or decode of many sequences) on the tensor cores.
+ *    No counterpart in the reference, whose expert kernels are batch-1 only (src/gpu_kernels.hip:1320-1384) and whose
+ *    operator takes one hidden state (include/gpu.h:70-83); the definition computed is src/cpu_expert.c applied to
+ *    every token.  Q4_K gate, up and down.  Tokens are bucketed by expert on the device; each (expert, 128-row tile)
+ *    is one tcgen05 tile with the weights dequantised to fp16 on their way from HBM.
+ * ====================================================================================== */
+typedef struct fomoe_b200_batch fomoe_b200_batch_t;
+
+typedef struct {
+    int device;
+    int n_layers;
+    int n_embd;      /* multiple of 256 (and so of 128), <= 8192 */
+    int n_inter;     /* multiple of 256, <= 8192 */
+    int n_experts;   /* <= 512 */
+    int top_k;       /* <= 16 */
+    int has_shared;
+    int max_tokens;  /* tokens per call, at most */
+    float rms_eps;
+} fomoe_b200_batch_config_t;
+
+fomoe_b200_batch_t *fomoe_b200_batch_create(const fomoe_b200_batch_config_t *cfg);
+void fomoe_b200_batch_destroy(fomoe_b200_batch_t *b);
+const char *fomoe_b200_batch_last_error(fomoe_b200_batch_t *b);
+int fomoe_b200_batch_status(fomoe_b200_batch_t *b);             /* 0 ok, 1 bad expert id, 2 bounded wait ran out; reading clears */
+uint64_t fomoe_b200_batch_table_bytes(fomoe_b200_batch_t *b);
+uint64_t fomoe_b200_batch_kernel_launches(fomoe_b200_batch_t *b);
+/* Experts, residuals and norm weights of every layer from `seed` (the same bytes as fomoe_b200_synth_matrix makes on
+ * the host); with_logits: also seeded router logits N(0,1) for max_tokens tokens per layer, as the batched
+ * benchmark configuration draws them (fomoe_b200_batch_synth_logits gives the host copy). */
+int fomoe_b200_batch_generate(fomoe_b200_batch_t *b, uint64_t seed, int with_logits);
+/* One expert record in ggml order (gate | up | down, all Q4_K); expert == n_experts is the shared expert. */
+int fomoe_b200_batch_upload(fomoe_b200_batch_t *b, int layer, int expert, const void *record);
+int fomoe_b200_batch_export(fomoe_b200_batch_t *b, int layer, int expert, void *record_out);
+/* One MoE block on n_tokens normalised hidden states h[n_tokens][n_embd] with router logits[n_tokens][n_experts]
+ * given by the caller: softmax, ordered top-k, renormalise, experts + shared expert; out[n_tokens][n_embd];
+ * ids_out / scores_out [n_tokens][top_k] optional. */
+int fomoe_b200_batch_moe_layer(fomoe_b200_batch_t *b, int layer, int n_tokens, const float *h, const float *logits,
+                               float *out, int *ids_out, float *scores_out);
+/* Stack on device-resident tokens: upload x[n_tokens][n_embd]; layers [l0, l1): x += resid_l; h = rmsnorm(x) normw_l;
+ * x += moe_l(h, generated logits of layer l); download.  elapsed_ms: CUDA-event time on the library's stream. */
+int fomoe_b200_batch_tokens_upload(fomoe_b200_batch_t *b, int n_tokens, const float *x);
+int fomoe_b200_batch_stack_run(fomoe_b200_batch_t *b, int n_tokens, int l0, int l1, float *elapsed_ms);
+int fomoe_b200_batch_tokens_download(fomoe_b200_batch_t *b, int n_tokens, float *x_out);
+/* Routing of the most recent layer call, and how many pairs every expert received (n_experts + has_shared counts). */
+int fomoe_b200_batch_get_routing(fomoe_b200_batch_t *b, int n_tokens, int *ids, float *scores, int *counts);
+void fomoe_b200_batch_synth_logits(uint64_t seed, int layer, int max_tokens, int n_experts, int n_tokens, float *out);
+
 /* Host-side synthetic generator (same bytes as fomoe_b200_table_generate puts on the device). */
 void fomoe_b200_synth_matrix(uint64_t seed, int layer, int expert, int matrix, int type, int rows, int cols,
                              void *ggml_out);
