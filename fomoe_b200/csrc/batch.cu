@@ -402,30 +402,51 @@ __device__ __forceinline__ void kb_dequant_atom(const uint4 &qa, const uint4 &qb
     }
 }
 
+/* ---- raw weight ring.  A (row tile, 256-block) unit of a matrix is 18,432 contiguous bytes, fetched by ONE bulk copy
+ * (cp.async.bulk, completion counted in bytes on an mbarrier) into a ring of raw stages two 256-blocks deep, issued by
+ * one producer thread two blocks ahead of the dequantisation: the HBM latency of the weights is off the producers'
+ * path, and no registers are spent on prefetching.  A stage is released as soon as every producer warp has taken its
+ * 144 bytes into registers. */
+struct kb_cursor_t { /* which (work item, 256-block) the copy thread issues next */
+    int it, kb;
+};
+
+/* the CTA's next block after (it, kb); false when the CTA's work ends */
+__device__ __forceinline__ bool kb_cursor_next(kb_cursor_t &c, int kbs, int n_items, int stride) {
+    if (++c.kb == kbs) {
+        c.kb = 0;
+        c.it += stride;
+    }
+    return c.it < n_items;
+}
+
+/* ------------------------------------------------------------------ down projection: one pass in fp16
+ * (its result is not quantised again, so two fp16 roundings per product, about 2e-4 of the output, are inside the
+ * bound).  A = fp16(d*sc*q - dmin*m), B = fp16(q8 * d_block / d_max), the row's d_max applied in the epilogue. */
+#define KBD_STAGES 2
+#define KBD_RAW 2
+#define KBD_STAGE_BYTES (4u * KB_ATOM_BYTES) /* A: 2 atoms; B: 2 atoms of 128 rows */
+
 struct kb_smem_ctl_t {
-    uint64_t full[4], empty[4], acc_full[2], acc_empty[2];
+    uint64_t full[KBD_STAGES], empty[KBD_STAGES], acc_full[2], acc_empty[2], raw_full[KBD_RAW], raw_empty[KBD_RAW];
     uint32_t tmem_base;
     int abort_flag;
     int pair[2][KB_TILE_N], xrow[2][KB_TILE_N];
     float scale[2][KB_TILE_N];
 };
 
-/* NMAT = 2: gate and up tiles of the same rows, SwiGLU epilogue; NMAT = 1: one matrix, plain epilogue.
- * A pipeline step covers 128 k (two 64-wide atoms). */
-template <int NMAT>
-__global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gemm(kb_gemm_args_t P) {
-    constexpr int STAGES = NMAT == 2 ? 2 : 3;
-    constexpr uint32_t A_BYTES = NMAT * 2 * KB_ATOM_BYTES, STAGE_BYTES = A_BYTES + 2 * KB_ATOM_BYTES;
+__global__ void __launch_bounds__(KB_THREADS, 1) k_kb_down(kb_gemm_args_t P) {
     extern __shared__ uint8_t dyn_raw[];
     const uint32_t dyn_u = (fb_smem_u32(dyn_raw) + 1023u) & ~1023u; /* operand tiles: 1024-byte aligned */
-    kb_smem_ctl_t *C = reinterpret_cast<kb_smem_ctl_t *>(dyn_raw + (dyn_u - fb_smem_u32(dyn_raw)) + STAGES * STAGE_BYTES);
+    const uint32_t raw_u = dyn_u + KBD_STAGES * KBD_STAGE_BYTES;
+    kb_smem_ctl_t *C = reinterpret_cast<kb_smem_ctl_t *>(dyn_raw + (raw_u - fb_smem_u32(dyn_raw)) + KBD_RAW * KB_TILE_BYTES);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_items = *P.n_items;
-    const int ksteps = P.K / 128;
+    const int kbs = P.K / 256, ksteps = P.K / 128;
     volatile int *abortp = &C->abort_flag;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) {
+        for (int s = 0; s < KBD_STAGES; s++) {
             fb_mbar_init(fb_smem_u32(&C->full[s]), KB_PROD_THREADS / 32);
             fb_mbar_init(fb_smem_u32(&C->empty[s]), 1);
         }
@@ -433,11 +454,15 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gemm(kb_gemm_args_t P) {
             fb_mbar_init(fb_smem_u32(&C->acc_full[b]), 1);
             fb_mbar_init(fb_smem_u32(&C->acc_empty[b]), 4);
         }
+        for (int r = 0; r < KBD_RAW; r++) {
+            fb_mbar_init(fb_smem_u32(&C->raw_full[r]), 1);
+            fb_mbar_init(fb_smem_u32(&C->raw_empty[r]), KB_PROD_THREADS / 32);
+        }
         C->abort_flag = 0;
         fb_mbar_init_fence();
     }
-    if (warp == 4) { /* tensor memory: all 512 columns (two accumulator buffers of NMAT x 128) */
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fb_smem_u32(&C->tmem_base)), "r"(512u)
+    if (warp == 4) { /* tensor memory: two accumulator buffers of 128 columns */
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fb_smem_u32(&C->tmem_base)), "r"(256u)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -448,11 +473,25 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gemm(kb_gemm_args_t P) {
     bool ok = true;
 
     if (warp >= KB_PROD_WARP0) {
-        /* ---------------- producers: dequantise A, copy B */
-        const int pt = tid - KB_PROD_WARP0 * 32;        /* 0..255 */
-        const int mat = NMAT == 2 ? (pt >> 7) : 0, row = pt & 127;
-        const int sel = NMAT == 2 ? 0 : (pt >> 7);      /* one matrix: which atom of the step this thread does */
-        uint32_t step = 0, cnt = 0;
+        /* ---------------- producers: dequantise A, copy B.  Thread (row, sel): row of the tile, and which of a step's
+         * two atoms it dequantises. */
+        const int pt = tid - KB_PROD_WARP0 * 32, row = pt & 127, sel = pt >> 7;
+        const bool copier = pt == 0;
+        uint32_t step = 0, cnt = 0, rb = 0; /* pipeline steps, tiles, 256-blocks so far */
+        kb_cursor_t cur = {(int)blockIdx.x, -1};
+        auto issue = [&](uint32_t blk) { /* copy thread: fetch the cursor's next block into raw stage blk % KBD_RAW */
+            if (!kb_cursor_next(cur, kbs, n_items, gridDim.x)) return;
+            const kb_item_t J = P.items[cur.it];
+            const uint32_t r = blk % KBD_RAW, bar = fb_smem_u32(&C->raw_full[r]);
+            fb_mbar_expect_tx(bar, KB_TILE_BYTES);
+            fb_bulk_g2s(raw_u + r * KB_TILE_BYTES,
+                        P.w_layer + (uint64_t)J.e * P.rec_bytes + P.mat_off[0] + ((uint64_t)J.m * kbs + cur.kb) * KB_TILE_BYTES,
+                        KB_TILE_BYTES, bar);
+        };
+        if (copier) {
+            issue(0);
+            issue(1);
+        }
         for (int it = blockIdx.x;; it += gridDim.x, cnt++) {
             /* All 256 producers meet here once per tile and leave together: a producer whose wait ran out arrives
              * with `false`, and nobody is left waiting at a barrier the others have abandoned. */
@@ -494,22 +533,26 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gemm(kb_gemm_args_t P) {
                 C->scale[ab][pt] = sc;
             }
             asm volatile("bar.sync 1, %0;" ::"n"(KB_PROD_THREADS) : "memory");
-            const uint8_t *wm = P.w_layer + (uint64_t)I.e * P.rec_bytes + P.mat_off[mat];
-            const int kbs = P.K / 256;
-            const uint4 *unit = reinterpret_cast<const uint4 *>(wm + ((uint64_t)I.m * kbs) * KB_TILE_BYTES) + row;
             const int n_b = I.n * 16; /* 16-byte pieces of B per step: n rows x 2 atoms x 8 */
-            for (int kb = 0; kb < kbs && ok; kb++, unit += KB_TILE_BYTES / 16) {
-                const uint4 hdr = __ldg(unit);
-                uint4 q[8];
-                if (NMAT == 2) {
+            for (int kb = 0; kb < kbs && ok; kb++, rb++) {
+                const uint32_t r = rb % KBD_RAW;
+                if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->raw_full[r]), (rb / KBD_RAW) & 1, abortp))) {
+                    C->abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                const uint32_t u_u = raw_u + r * KB_TILE_BYTES + 16u * row;
+                const uint4 hdr = fb_lds128(u_u);
+                uint4 q[4]; /* the two chunks this thread dequantises: sel and 2 + sel */
 #pragma unroll
-                    for (int p = 0; p < 8; p++) q[p] = __ldg(unit + 128 * (p + 1));
-                } else {
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        q[4 * h + 2 * sel] = __ldg(unit + 128 * (4 * h + 2 * sel + 1));
-                        q[4 * h + 2 * sel + 1] = __ldg(unit + 128 * (4 * h + 2 * sel + 2));
-                    }
+                for (int h = 0; h < 2; h++) {
+                    q[2 * h] = fb_lds128(u_u + 2048u * (4 * h + 2 * sel + 1));
+                    q[2 * h + 1] = fb_lds128(u_u + 2048u * (4 * h + 2 * sel + 2));
+                }
+                __syncwarp();
+                if (lane == 0) fb_mbar_arrive(fb_smem_u32(&C->raw_empty[r]));
+                if (copier) { /* once every warp has taken this block, its stage takes the block after next */
+                    if (kb_wait(fb_smem_u32(&C->raw_empty[r]), (rb / KBD_RAW) & 1, abortp)) issue(rb + KBD_RAW);
                 }
                 const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
                 const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
@@ -518,31 +561,41 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gemm(kb_gemm_args_t P) {
                 const uint32_t mn_w[2] = {hdr.z & 0x3f3f3f3fu, ((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4)};
 #pragma unroll
                 for (int half = 0; half < 2; half++, step++) {
-                    const int s = step % STAGES;
-                    if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->empty[s]), ((step / STAGES) & 1) ^ 1, abortp))) {
+                    const int s = step % KBD_STAGES;
+                    /* this thread's activation pieces of the step: requested before the stage is waited for */
+                    uint4 bv[8];
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int i = pt + u * KB_PROD_THREADS;
+                        if (i < n_b) {
+                            const int rr = i >> 4, a = (i >> 3) & 1, ch = i & 7;
+                            bv[u] = __ldg(reinterpret_cast<const uint4 *>(P.xh + (size_t)C->xrow[ab][rr] * P.K + kb * 256 + half * 128 + a * 64) + ch);
+                        }
+                    }
+                    if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->empty[s]), ((step / KBD_STAGES) & 1) ^ 1, abortp))) {
                         C->abort_flag = 1; /* the whole warp stops producing; the tile barrier above ends the role */
                         ok = false;
                         break;
                     }
-                    const uint32_t st_u = dyn_u + s * STAGE_BYTES;
-#pragma unroll
-                    for (int a = 0; a < 2; a++) {
-                        if (NMAT == 1 && a != sel) continue;
-                        const int cc = 2 * half + a; /* chunk = atom: sub-blocks 2cc (low nibbles), 2cc+1 (high) */
+                    const uint32_t st_u = dyn_u + s * KBD_STAGE_BYTES;
+                    {
+                        const int a = sel; /* chunk = atom: sub-blocks 2cc (low nibbles), 2cc+1 (high) */
                         const float sl = (float)((sc_w[half] >> (16 * a)) & 0xff), sh = (float)((sc_w[half] >> (16 * a + 8)) & 0xff);
                         const float ml = (float)((mn_w[half] >> (16 * a)) & 0xff), mh = (float)((mn_w[half] >> (16 * a + 8)) & 0xff);
                         const __half2 s_lo = __float2half2_rn(__fmul_rn(d, sl)), b_lo = __float2half2_rn(-__fmul_rn(dmin, ml));
                         const __half2 s_hi = __float2half2_rn(__fmul_rn(d, sh)), b_hi = __float2half2_rn(-__fmul_rn(dmin, mh));
-                        kb_dequant_atom(q[2 * cc], q[2 * cc + 1], s_lo, b_lo, s_hi, b_hi, st_u + (mat * 2 + a) * KB_ATOM_BYTES, row);
+                        kb_dequant_atom(q[2 * half], q[2 * half + 1], s_lo, b_lo, s_hi, b_hi, st_u + a * KB_ATOM_BYTES, row);
                     }
-                    /* activations of this step: row r of the pair table, 2 atoms x 8 pieces of 16 bytes */
-                    const uint32_t b_u = st_u + A_BYTES;
-                    for (int i = pt; i < n_b; i += KB_PROD_THREADS) {
-                        const int r = i >> 4, a = (i >> 3) & 1, ch = i & 7;
-                        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(P.xh + (size_t)C->xrow[ab][r] * P.K + kb * 256 + half * 128 + a * 64) + ch);
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(b_u + a * KB_ATOM_BYTES + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u + (((uint32_t)ch ^ (uint32_t)(r & 7)) << 4)),
-                                     "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                                     : "memory");
+                    const uint32_t b_u = st_u + 2 * KB_ATOM_BYTES;
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int i = pt + u * KB_PROD_THREADS;
+                        if (i < n_b) {
+                            const int rr = i >> 4, a = (i >> 3) & 1, ch = i & 7;
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(b_u + a * KB_ATOM_BYTES + (uint32_t)(rr >> 3) * 1024u + (uint32_t)(rr & 7) * 128u + (((uint32_t)ch ^ (uint32_t)(rr & 7)) << 4)),
+                                         "r"(bv[u].x), "r"(bv[u].y), "r"(bv[u].z), "r"(bv[u].w)
+                                         : "memory");
+                        }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); /* generic-proxy stores -> the tensor core's reads */
                     __syncwarp();
@@ -557,26 +610,20 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gemm(kb_gemm_args_t P) {
             for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, cnt++) {
                 const kb_item_t I = P.items[it];
                 const int ab = cnt & 1;
-                const int n16 = (I.n + 15) & ~15;
-                const uint32_t idesc = kb_idesc(n16);
+                const uint32_t idesc = kb_idesc((I.n + 15) & ~15);
                 if (!kb_wait(fb_smem_u32(&C->acc_empty[ab]), ((cnt >> 1) & 1) ^ 1, abortp)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (int ks = 0; ks < ksteps && ok; ks++, step++) {
-                    const int s = step % STAGES;
-                    if (!kb_wait(fb_smem_u32(&C->full[s]), (step / STAGES) & 1, abortp)) { ok = false; break; }
+                    const int s = step % KBD_STAGES;
+                    if (!kb_wait(fb_smem_u32(&C->full[s]), (step / KBD_STAGES) & 1, abortp)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t st_u = dyn_u + s * STAGE_BYTES, b_u = st_u + A_BYTES;
+                    const uint32_t st_u = dyn_u + s * KBD_STAGE_BYTES, b_u = st_u + 2 * KB_ATOM_BYTES;
 #pragma unroll
                     for (int a = 0; a < 2; a++)
 #pragma unroll
-                        for (int k16 = 0; k16 < 4; k16++) {
-                            const uint64_t bdesc = kb_smem_desc(b_u + a * KB_ATOM_BYTES + k16 * 32);
-#pragma unroll
-                            for (int m = 0; m < NMAT; m++)
-                                kb_mma(tmem + (uint32_t)(ab * NMAT + m) * KB_TILE_N,
-                                       kb_smem_desc(st_u + (m * 2 + a) * KB_ATOM_BYTES + k16 * 32), bdesc, idesc,
-                                       (ks | a | k16) ? 1u : 0u);
-                        }
+                        for (int k16 = 0; k16 < 4; k16++)
+                            kb_mma(tmem + (uint32_t)ab * KB_TILE_N, kb_smem_desc(st_u + a * KB_ATOM_BYTES + k16 * 32),
+                                   kb_smem_desc(b_u + a * KB_ATOM_BYTES + k16 * 32), idesc, (ks | a | k16) ? 1u : 0u);
                     kb_commit(fb_smem_u32(&C->empty[s])); /* the stage is free once these MMAs have read it */
                 }
                 if (ok) kb_commit(fb_smem_u32(&C->acc_full[ab]));
@@ -592,24 +639,15 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gemm(kb_gemm_args_t P) {
             if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->acc_full[ab]), (cnt >> 1) & 1, abortp))) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int grow = I.m * KB_TILE_M + warp * 32 + lane;
-            const uint32_t t0 = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(ab * NMAT) * KB_TILE_N;
+            const uint32_t t0 = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)ab * KB_TILE_N;
             for (int c0 = 0; c0 < I.n; c0 += 16) {
-                uint32_t g[16], u[16];
+                uint32_t g[16];
                 kb_tmem_ld16(t0 + c0, g);
-                if (NMAT == 2) kb_tmem_ld16(t0 + KB_TILE_N + c0, u);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    if (c0 + j < I.n) {
-                        const float sc = C->scale[ab][c0 + j];
-                        float v = __fmul_rn(__uint_as_float(g[j]), sc);
-                        if (NMAT == 2) { /* silu(gate) * up, src/cpu_expert.c:103-106 */
-                            const float up = __fmul_rn(__uint_as_float(u[j]), sc);
-                            v = __fmul_rn(__fdiv_rn(v, __fadd_rn(1.0f, expf(-v))), up);
-                        }
-                        P.out[(size_t)C->pair[ab][c0 + j] * P.M + grow] = v;
-                    }
-                }
+                for (int j = 0; j < 16; j++)
+                    if (c0 + j < I.n)
+                        P.out[(size_t)C->pair[ab][c0 + j] * P.M + grow] = __fmul_rn(__uint_as_float(g[j]), C->scale[ab][c0 + j]);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -624,7 +662,7 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gemm(kb_gemm_args_t P) {
     __syncthreads();
     if (warp == 4) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
     }
 }
 
@@ -632,30 +670,36 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gemm(kb_gemm_args_t P) {
  *
  * The activations of the down projection are quantised to int8 from the OUTPUT of this pass, so a relative error of
  * 2e-4 here moves several of the 1024 int8 values of a row by one step and costs 2e-3 of the layer output (measured
- * with the one-pass fp16 form above on both projections).  This pass therefore keeps the reference's integer
- * arithmetic (src/quant.c:405-476) on the tensor cores: A = sc_j * q (at most 945) and B = the int8 activation are
- * exact in fp16, a 256-block's sum of products is an exact integer in the fp32 accumulator (below 2^24 in all but
- * adversarial data, 2^25 at most), and each 256-block's accumulator is read out and scaled on the CUDA cores:
+ * with the one-pass fp16 form on both projections).  This pass therefore keeps the reference's integer arithmetic
+ * (src/quant.c:405-476) on the tensor cores: A = sc_j * q (at most 945) and B = the int8 activation are exact in
+ * fp16, a 256-block's sum of products is an exact integer in the fp32 accumulator (below 2^24 in all but adversarial
+ * data, 2^25 at most), and each 256-block's accumulator is read out and scaled on the CUDA cores:
  *     sum += (yd * d) * isum - (yd * dmin) * sum_j m_j * bs_j
  * with bs_j the activation's sub-block sums.  Accumulators are double-buffered per 256-block in tensor memory, so the
  * epilogue of one block overlaps the MMAs of the next; at most 32 pairs per pass keep the running sums (2 x 32 per
- * weight row) in registers.  Roles and pipeline as in k_kb_gemm. */
-#define KBG_STAGES 3
+ * weight row) in registers.  Roles and pipeline as in k_kb_down. */
+#define KBG_STAGES 2
+#define KBG_RAW 2
 #define KBG_B_ATOM ((uint32_t)KB_GU_N * 128u)
 #define KBG_A_BYTES (4u * KB_ATOM_BYTES)
 #define KBG_STAGE_BYTES (KBG_A_BYTES + 2u * KBG_B_ATOM)
 
 struct kbg_ctl_t {
-    uint64_t full[KBG_STAGES], empty[KBG_STAGES], blk_full[2], blk_empty[2], item_done[2];
+    uint64_t full[KBG_STAGES], empty[KBG_STAGES], blk_full[2], blk_empty[2], item_done[2], raw_full[KBG_RAW], raw_empty[KBG_RAW];
     uint32_t tmem_base;
     int abort_flag;
     int pair[2][KB_GU_N], xrow[2][KB_GU_N];
+    /* activation side of a 256-block's scaling, per pair: {d, the eight sub-block sums, pad}; written by the producers
+     * with the block's operand tiles, read by the epilogue.  Four blocks deep: the producers run at most two blocks
+     * ahead of the MMAs, and the MMAs at most two ahead of the epilogue. */
+    alignas(16) float xt[4][KB_GU_N][12]; /* read as float4: 16-byte aligned inside the struct */
 };
 
 __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
     extern __shared__ uint8_t dyn_raw[];
     const uint32_t dyn_u = (fb_smem_u32(dyn_raw) + 1023u) & ~1023u;
-    kbg_ctl_t *C = reinterpret_cast<kbg_ctl_t *>(dyn_raw + (dyn_u - fb_smem_u32(dyn_raw)) + KBG_STAGES * KBG_STAGE_BYTES);
+    const uint32_t raw_u = dyn_u + KBG_STAGES * KBG_STAGE_BYTES; /* raw stage: gate unit, then up unit */
+    kbg_ctl_t *C = reinterpret_cast<kbg_ctl_t *>(dyn_raw + (raw_u - fb_smem_u32(dyn_raw)) + KBG_RAW * 2 * KB_TILE_BYTES);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_items = *P.n_items;
     const int kbs = P.K / 256;
@@ -670,6 +714,10 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
             fb_mbar_init(fb_smem_u32(&C->blk_full[b]), 1);
             fb_mbar_init(fb_smem_u32(&C->blk_empty[b]), 4);
             fb_mbar_init(fb_smem_u32(&C->item_done[b]), 4);
+        }
+        for (int r = 0; r < KBG_RAW; r++) {
+            fb_mbar_init(fb_smem_u32(&C->raw_full[r]), 1);
+            fb_mbar_init(fb_smem_u32(&C->raw_empty[r]), KB_PROD_THREADS / 32);
         }
         C->abort_flag = 0;
         fb_mbar_init_fence();
@@ -686,9 +734,25 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
     bool ok = true;
 
     if (warp >= KB_PROD_WARP0) {
-        /* ---------------- producers */
+        /* ---------------- producers: thread (mat, row) */
         const int pt = tid - KB_PROD_WARP0 * 32, mat = pt >> 7, row = pt & 127;
-        uint32_t step = 0, cnt = 0;
+        const bool copier = pt == 0;
+        uint32_t step = 0, cnt = 0, rb = 0;
+        kb_cursor_t cur = {(int)blockIdx.x, -1};
+        auto issue = [&](uint32_t blk) {
+            if (!kb_cursor_next(cur, kbs, n_items, gridDim.x)) return;
+            const kb_item_t J = P.items[cur.it];
+            const uint32_t r = blk % KBG_RAW, bar = fb_smem_u32(&C->raw_full[r]);
+            const uint8_t *rec = P.w_layer + (uint64_t)J.e * P.rec_bytes;
+            const uint64_t off = ((uint64_t)J.m * kbs + cur.kb) * KB_TILE_BYTES;
+            fb_mbar_expect_tx(bar, 2 * KB_TILE_BYTES);
+            fb_bulk_g2s(raw_u + r * 2 * KB_TILE_BYTES, rec + P.mat_off[0] + off, KB_TILE_BYTES, bar);
+            fb_bulk_g2s(raw_u + r * 2 * KB_TILE_BYTES + KB_TILE_BYTES, rec + P.mat_off[1] + off, KB_TILE_BYTES, bar);
+        };
+        if (copier) {
+            issue(0);
+            issue(1);
+        }
         for (int it = blockIdx.x;; it += gridDim.x, cnt++) {
             const bool more = it < n_items;
             const int ab = cnt & 1;
@@ -724,19 +788,49 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
                 C->xrow[ab][pt] = xr;
             }
             asm volatile("bar.sync 1, %0;" ::"n"(KB_PROD_THREADS) : "memory");
-            const uint8_t *wm = P.w_layer + (uint64_t)I.e * P.rec_bytes + P.mat_off[mat];
-            const uint4 *unit = reinterpret_cast<const uint4 *>(wm + ((uint64_t)I.m * kbs) * KB_TILE_BYTES) + row;
-            const int n_b = I.n * 16;
+            const int n_b = I.n * 16; /* at most 512: two pieces per thread */
             const __half2 zero2 = __float2half2_rn(0.0f);
-            for (int kb = 0; kb < kbs && ok; kb++, unit += KB_TILE_BYTES / 16) {
-                const uint4 hdr = __ldg(unit);
+            for (int kb = 0; kb < kbs && ok; kb++, rb++) {
+                const uint32_t r = rb % KBG_RAW;
+                if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->raw_full[r]), (rb / KBG_RAW) & 1, abortp))) {
+                    C->abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                const uint32_t u_u = raw_u + (r * 2 + mat) * KB_TILE_BYTES + 16u * row;
+                const uint4 hdr = fb_lds128(u_u);
                 uint4 q[8];
 #pragma unroll
-                for (int p = 0; p < 8; p++) q[p] = __ldg(unit + 128 * (p + 1));
+                for (int p = 0; p < 8; p++) q[p] = fb_lds128(u_u + 2048u * (p + 1));
+                __syncwarp();
+                if (lane == 0) fb_mbar_arrive(fb_smem_u32(&C->raw_empty[r]));
+                if (copier) {
+                    if (kb_wait(fb_smem_u32(&C->raw_empty[r]), (rb / KBG_RAW) & 1, abortp)) issue(rb + KBG_RAW);
+                }
                 const uint32_t sc_w[2] = {hdr.y & 0x3f3f3f3fu, (hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4)};
+                /* this block's scale and sub-block sums of every pair: 9 values per pair, one or two per thread */
+                float xv[2] = {0.0f, 0.0f};
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    const int i = pt + u * KB_PROD_THREADS;
+                    if (i < I.n * 9) {
+                        const int col = i / 9, f = i - col * 9;
+                        const size_t xb = (size_t)C->xrow[ab][col] * kbs + kb;
+                        xv[u] = f ? __ldg(P.xbs + xb * 8 + (f - 1)) : __ldg(P.xscale + xb);
+                    }
+                }
 #pragma unroll
                 for (int half = 0; half < 2; half++, step++) {
                     const int s = step % KBG_STAGES;
+                    uint4 bv[2];
+#pragma unroll
+                    for (int u = 0; u < 2; u++) {
+                        const int i = pt + u * KB_PROD_THREADS;
+                        if (i < n_b) {
+                            const int rr = i >> 4, a = (i >> 3) & 1, ch = i & 7;
+                            bv[u] = __ldg(reinterpret_cast<const uint4 *>(P.xh + (size_t)C->xrow[ab][rr] * P.K + kb * 256 + half * 128 + a * 64) + ch);
+                        }
+                    }
                     if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->empty[s]), ((step / KBG_STAGES) & 1) ^ 1, abortp))) {
                         C->abort_flag = 1;
                         ok = false;
@@ -751,12 +845,22 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
                         kb_dequant_atom(q[2 * cc], q[2 * cc + 1], s_lo, zero2, s_hi, zero2, st_u + (mat * 2 + a) * KB_ATOM_BYTES, row);
                     }
                     const uint32_t b_u = st_u + KBG_A_BYTES;
-                    for (int i = pt; i < n_b; i += KB_PROD_THREADS) {
-                        const int r = i >> 4, a = (i >> 3) & 1, ch = i & 7;
-                        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(P.xh + (size_t)C->xrow[ab][r] * P.K + kb * 256 + half * 128 + a * 64) + ch);
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(b_u + a * KBG_B_ATOM + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u + (((uint32_t)ch ^ (uint32_t)(r & 7)) << 4)),
-                                     "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                                     : "memory");
+#pragma unroll
+                    for (int u = 0; u < 2; u++) {
+                        const int i = pt + u * KB_PROD_THREADS;
+                        if (i < n_b) {
+                            const int rr = i >> 4, a = (i >> 3) & 1, ch = i & 7;
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(b_u + a * KBG_B_ATOM + (uint32_t)(rr >> 3) * 1024u + (uint32_t)(rr & 7) * 128u + (((uint32_t)ch ^ (uint32_t)(rr & 7)) << 4)),
+                                         "r"(bv[u].x), "r"(bv[u].y), "r"(bv[u].z), "r"(bv[u].w)
+                                         : "memory");
+                        }
+                    }
+                    if (half == 0) {
+#pragma unroll
+                        for (int u = 0; u < 2; u++) {
+                            const int i = pt + u * KB_PROD_THREADS;
+                            if (i < I.n * 9) C->xt[rb & 3][i / 9][i % 9] = xv[u];
+                        }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
@@ -815,15 +919,21 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
                 /* this row's block headers: d, dmin and the eight 6-bit mins of gate and up */
                 const uint4 hg = __ldg(reinterpret_cast<const uint4 *>(wg + ((uint64_t)I.m * kbs + kb) * KB_TILE_BYTES) + trow);
                 const uint4 hu = __ldg(reinterpret_cast<const uint4 *>(wu + ((uint64_t)I.m * kbs + kb) * KB_TILE_BYTES) + trow);
-                if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->blk_full[buf]), (bc >> 1) & 1, abortp))) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t t0 = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * 2) * KB_GU_N;
                 const float dg = __half2float(__ushort_as_half((unsigned short)(hg.x & 0xffff)));
                 const float ng = __half2float(__ushort_as_half((unsigned short)(hg.x >> 16)));
                 const float du = __half2float(__ushort_as_half((unsigned short)(hu.x & 0xffff)));
                 const float nu = __half2float(__ushort_as_half((unsigned short)(hu.x >> 16)));
                 const uint32_t mgw[2] = {hg.z & 0x3f3f3f3fu, ((hg.w >> 4) & 0x0f0f0f0fu) | (((hg.z >> 6) & 0x03030303u) << 4)};
                 const uint32_t muw[2] = {hu.z & 0x3f3f3f3fu, ((hu.w >> 4) & 0x0f0f0f0fu) | (((hu.z >> 6) & 0x03030303u) << 4)};
+                float mg[8], mu[8]; /* dmin * m_j: one multiplication fewer per pair below */
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    mg[i] = (float)((mgw[i >> 2] >> (8 * (i & 3))) & 0xff);
+                    mu[i] = (float)((muw[i >> 2] >> (8 * (i & 3))) & 0xff);
+                }
+                if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->blk_full[buf]), (bc >> 1) & 1, abortp))) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t t0 = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * 2) * KB_GU_N;
 #pragma unroll
                 for (int c0 = 0; c0 < KB_GU_N; c0 += 16) { /* 16 pairs at a time: the sums, their scaling */
                     if (c0 < I.n) {
@@ -834,16 +944,15 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
 #pragma unroll
                         for (int j = 0; j < 16; j++) {
                             if (c0 + j < I.n) {
-                                const int xr = C->xrow[ab][c0 + j];
-                                const float yd = __ldg(P.xscale + (size_t)xr * kbs + kb);
-                                const float4 b0 = __ldg(reinterpret_cast<const float4 *>(P.xbs + ((size_t)xr * kbs + kb) * 8));
-                                const float4 b1 = __ldg(reinterpret_cast<const float4 *>(P.xbs + ((size_t)xr * kbs + kb) * 8) + 1);
-                                const float bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                                const float4 *xt = reinterpret_cast<const float4 *>(C->xt[bc & 3][c0 + j]);
+                                const float4 t0v = xt[0], t1v = xt[1], t2v = xt[2];
+                                const float yd = t0v.x;
+                                const float bs[8] = {t0v.y, t0v.z, t0v.w, t1v.x, t1v.y, t1v.z, t1v.w, t2v.x};
                                 float msg = 0.0f, msu = 0.0f; /* exact: integers far below 2^24 */
 #pragma unroll
                                 for (int i = 0; i < 8; i++) {
-                                    msg = __fmaf_rn((float)((mgw[i >> 2] >> (8 * (i & 3))) & 0xff), bs[i], msg);
-                                    msu = __fmaf_rn((float)((muw[i >> 2] >> (8 * (i & 3))) & 0xff), bs[i], msu);
+                                    msg = __fmaf_rn(mg[i], bs[i], msg);
+                                    msu = __fmaf_rn(mu[i], bs[i], msu);
                                 }
                                 accg[c0 + j] = __fmaf_rn(__fmul_rn(yd, dg), __uint_as_float(ig[j]), accg[c0 + j]);
                                 accg[c0 + j] = __fmaf_rn(-__fmul_rn(yd, ng), msg, accg[c0 + j]);
@@ -961,13 +1070,13 @@ extern "C" int kb_launch_down(const kb_gemm_args_t *a, int grid, void *stream) {
     static unsigned char configured[64]; /* the attribute holds for one device */
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-    const int sm = 1024 + 3 * 4 * (int)KB_ATOM_BYTES + (int)sizeof(kb_smem_ctl_t);
+    const int sm = 1024 + KBD_STAGES * (int)KBD_STAGE_BYTES + KBD_RAW * (int)KB_TILE_BYTES + (int)sizeof(kb_smem_ctl_t);
     if (!configured[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(k_kb_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
+        const cudaError_t e = cudaFuncSetAttribute(k_kb_down, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
         if (e != cudaSuccess) return (int)e;
         configured[dev] = 1;
     }
-    k_kb_gemm<1><<<grid, KB_THREADS, sm, (cudaStream_t)stream>>>(*a);
+    k_kb_down<<<grid, KB_THREADS, sm, (cudaStream_t)stream>>>(*a);
     return (int)cudaGetLastError();
 }
 
@@ -975,7 +1084,7 @@ extern "C" int kb_launch_gateup(const kb_gemm_args_t *a, int grid, void *stream)
     static unsigned char configured[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-    const int sm = 1024 + KBG_STAGES * (int)KBG_STAGE_BYTES + (int)sizeof(kbg_ctl_t);
+    const int sm = 1024 + KBG_STAGES * (int)KBG_STAGE_BYTES + KBG_RAW * 2 * (int)KB_TILE_BYTES + (int)sizeof(kbg_ctl_t);
     if (!configured[dev]) {
         const cudaError_t e = cudaFuncSetAttribute(k_kb_gateup, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
         if (e != cudaSuccess) return (int)e;
