@@ -138,6 +138,7 @@ _SIGS = {
     "fomoe_b200_batch_stack_run": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, _f32p]),
     "fomoe_b200_batch_tokens_download": (C.c_int, [C.c_void_p, C.c_int, _f32p]),
     "fomoe_b200_batch_get_routing": (C.c_int, [C.c_void_p, C.c_int, _i32p, _f32p, _i32p]),
+    "fomoe_b200_batch_wait_profile": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint64)]),
     "fomoe_b200_batch_synth_logits": (None, [C.c_uint64, C.c_int, C.c_int, C.c_int, C.c_int, _f32p]),
     "fomoe_b200_synth_matrix": (None, [C.c_uint64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "fomoe_b200_synth_f32": (None, [C.c_uint64, C.c_int, C.c_int, C.c_float, C.c_float, C.c_uint64, _f32p]),
@@ -690,6 +691,13 @@ class BatchedMoe:
     def tokens_download(self, n_tokens):
         out = np.empty((n_tokens, self.n_embd), dtype=np.float32)
         self._ck(self._l.fomoe_b200_batch_tokens_download(self._h, n_tokens, _fp(out)), "batch_tokens_download")
+        return out
+
+    def wait_profile(self, on):
+        """on=True: start counting block 0's wait cycles per role; on=False: -> uint64[16] (see the C header)."""
+        out = np.zeros(16, dtype=np.uint64)
+        self._ck(self._l.fomoe_b200_batch_wait_profile(self._h, int(bool(on)), out.ctypes.data_as(C.POINTER(C.c_uint64))),
+                 "batch_wait_profile")
         return out
 
     def get_routing(self, n_tokens):

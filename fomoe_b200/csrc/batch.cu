@@ -43,12 +43,14 @@
 #include <stdint.h>
 
 #include "batch_launch.h"
+#include "dots.cuh"
 #include "launch.h"
 #include "route.cuh"
 #include "stream.cuh"
 #include "synth.h"
 
-#define KB_THREADS 416
+#define KB_THREADS 448
+#define KB_COPY_WARP 13 /* one thread of it fetches the raw weight units */
 #define KB_PROD_WARP0 5
 #define KB_PROD_THREADS 256
 #define KB_ATOM_BYTES 16384u /* 128 rows x 64 fp16 */
@@ -111,7 +113,7 @@ __global__ void k_kb_gen_f32(float *dst, uint64_t n, uint64_t key, float mean, f
 
 __global__ void __launch_bounds__(KBQ_THREADS) k_kb_rows(float *x, const float *src, const float *resid, const float *normw,
                                                         float rms_eps, int n, float *h_out, uint16_t *xh, float *xscale,
-                                                        float *xbs, int exact) {
+                                                        int16_t *xbs, int exact) {
     __shared__ float s_red[KBQ_THREADS / 32];
     __shared__ float s_scale, s_dmax;
     __shared__ float s_d[KBQ_MAX_K / 256];
@@ -180,7 +182,7 @@ __global__ void __launch_bounds__(KBQ_THREADS) k_kb_rows(float *x, const float *
         for (int i = tid; i < nb * 8; i += KBQ_THREADS) {
             int sum = 0;
             for (int k = 0; k < 32; k++) sum += s_q[i * 32 + k];
-            xbs[(size_t)row * nb * 8 + i] = (float)sum;
+            xbs[(size_t)row * nb * 8 + i] = (int16_t)sum; /* at most 32 * 127 */
         }
     }
     __syncthreads();
@@ -327,6 +329,15 @@ __device__ __forceinline__ bool kb_wait(uint32_t bar, uint32_t parity, volatile 
     return false;
 }
 
+/* the same, adding the cycles waited to prof[slot] when profiling is on (block 0, one lane per warp) */
+__device__ __forceinline__ bool kb_wait_p(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned long long *prof, int slot) {
+    if (!prof) return kb_wait(bar, parity, abort_flag);
+    const long long t0 = clock64();
+    const bool r = kb_wait(bar, parity, abort_flag);
+    if ((threadIdx.x & 31) == 0) atomicAdd(prof + slot, (unsigned long long)(clock64() - t0));
+    return r;
+}
+
 /* shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart */
 __device__ __forceinline__ uint64_t kb_smem_desc(uint32_t saddr) {
     uint64_t d = 0;
@@ -444,6 +455,11 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_down(kb_gemm_args_t P) {
     const int n_items = *P.n_items;
     const int kbs = P.K / 256, ksteps = P.K / 128;
     volatile int *abortp = &C->abort_flag;
+    /* profiling aid: cycles block 0's roles wait -- [0] copy thread for a free raw stage, [1] producers for the pair
+     * table's buffer, [2] for raw weights, [3] for a free operand stage, [4] MMA thread for a free accumulator,
+     * [5] for a filled stage, [6] epilogue for a finished tile (sums over the waiting warps), [7] the block's run time */
+    unsigned long long *prof = (blockIdx.x == 0) ? P.prof : nullptr;
+    const long long t_start = clock64();
 
     if (tid == 0) {
         for (int s = 0; s < KBD_STAGES; s++) {
@@ -472,33 +488,33 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_down(kb_gemm_args_t P) {
     const uint32_t tmem = C->tmem_base;
     bool ok = true;
 
-    if (warp >= KB_PROD_WARP0) {
+    if (warp == KB_COPY_WARP) {
+        /* ---------------- copy thread: every 256-block of this CTA's tiles, in order, two blocks ahead of its use */
+        if (lane == 0) {
+            kb_cursor_t cur = {(int)blockIdx.x, -1};
+            for (uint32_t blk = 0; kb_cursor_next(cur, kbs, n_items, gridDim.x); blk++) {
+                const uint32_t r = blk % KBD_RAW, bar = fb_smem_u32(&C->raw_full[r]);
+                if (blk >= KBD_RAW && !kb_wait_p(fb_smem_u32(&C->raw_empty[r]), ((blk / KBD_RAW) - 1) & 1, abortp, prof, 0)) { ok = false; break; }
+                const kb_item_t J = P.items[cur.it];
+                fb_mbar_expect_tx(bar, KB_TILE_BYTES);
+                fb_bulk_g2s(raw_u + r * KB_TILE_BYTES,
+                            P.w_layer + (uint64_t)J.e * P.rec_bytes + P.mat_off[0] + ((uint64_t)J.m * kbs + cur.kb) * KB_TILE_BYTES,
+                            KB_TILE_BYTES, bar);
+            }
+        }
+        __syncwarp();
+    } else if (warp >= KB_PROD_WARP0) {
         /* ---------------- producers: dequantise A, copy B.  Thread (row, sel): row of the tile, and which of a step's
          * two atoms it dequantises. */
         const int pt = tid - KB_PROD_WARP0 * 32, row = pt & 127, sel = pt >> 7;
-        const bool copier = pt == 0;
         uint32_t step = 0, cnt = 0, rb = 0; /* pipeline steps, tiles, 256-blocks so far */
-        kb_cursor_t cur = {(int)blockIdx.x, -1};
-        auto issue = [&](uint32_t blk) { /* copy thread: fetch the cursor's next block into raw stage blk % KBD_RAW */
-            if (!kb_cursor_next(cur, kbs, n_items, gridDim.x)) return;
-            const kb_item_t J = P.items[cur.it];
-            const uint32_t r = blk % KBD_RAW, bar = fb_smem_u32(&C->raw_full[r]);
-            fb_mbar_expect_tx(bar, KB_TILE_BYTES);
-            fb_bulk_g2s(raw_u + r * KB_TILE_BYTES,
-                        P.w_layer + (uint64_t)J.e * P.rec_bytes + P.mat_off[0] + ((uint64_t)J.m * kbs + cur.kb) * KB_TILE_BYTES,
-                        KB_TILE_BYTES, bar);
-        };
-        if (copier) {
-            issue(0);
-            issue(1);
-        }
         for (int it = blockIdx.x;; it += gridDim.x, cnt++) {
             /* All 256 producers meet here once per tile and leave together: a producer whose wait ran out arrives
              * with `false`, and nobody is left waiting at a barrier the others have abandoned. */
             const bool more = it < n_items;
             const int ab = cnt & 1;
             /* (the epilogue of the tile before last still reads this buffer's pair table) */
-            bool w = ok && (!more || kb_wait(fb_smem_u32(&C->acc_empty[ab]), ((cnt >> 1) & 1) ^ 1, abortp));
+            bool w = ok && (!more || kb_wait_p(fb_smem_u32(&C->acc_empty[ab]), ((cnt >> 1) & 1) ^ 1, abortp, prof, 1));
             if (!w) C->abort_flag = 1;
             {
                 uint32_t all;
@@ -536,7 +552,7 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_down(kb_gemm_args_t P) {
             const int n_b = I.n * 16; /* 16-byte pieces of B per step: n rows x 2 atoms x 8 */
             for (int kb = 0; kb < kbs && ok; kb++, rb++) {
                 const uint32_t r = rb % KBD_RAW;
-                if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->raw_full[r]), (rb / KBD_RAW) & 1, abortp))) {
+                if (!__all_sync(0xffffffffu, kb_wait_p(fb_smem_u32(&C->raw_full[r]), (rb / KBD_RAW) & 1, abortp, prof, 2))) {
                     C->abort_flag = 1;
                     ok = false;
                     break;
@@ -551,9 +567,6 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_down(kb_gemm_args_t P) {
                 }
                 __syncwarp();
                 if (lane == 0) fb_mbar_arrive(fb_smem_u32(&C->raw_empty[r]));
-                if (copier) { /* once every warp has taken this block, its stage takes the block after next */
-                    if (kb_wait(fb_smem_u32(&C->raw_empty[r]), (rb / KBD_RAW) & 1, abortp)) issue(rb + KBD_RAW);
-                }
                 const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
                 const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
                 /* 6-bit scales and mins of the 8 sub-blocks (src/quant.c:72-80), four to a word */
@@ -572,7 +585,7 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_down(kb_gemm_args_t P) {
                             bv[u] = __ldg(reinterpret_cast<const uint4 *>(P.xh + (size_t)C->xrow[ab][rr] * P.K + kb * 256 + half * 128 + a * 64) + ch);
                         }
                     }
-                    if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->empty[s]), ((step / KBD_STAGES) & 1) ^ 1, abortp))) {
+                    if (!__all_sync(0xffffffffu, kb_wait_p(fb_smem_u32(&C->empty[s]), ((step / KBD_STAGES) & 1) ^ 1, abortp, prof, 3))) {
                         C->abort_flag = 1; /* the whole warp stops producing; the tile barrier above ends the role */
                         ok = false;
                         break;
@@ -611,11 +624,11 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_down(kb_gemm_args_t P) {
                 const kb_item_t I = P.items[it];
                 const int ab = cnt & 1;
                 const uint32_t idesc = kb_idesc((I.n + 15) & ~15);
-                if (!kb_wait(fb_smem_u32(&C->acc_empty[ab]), ((cnt >> 1) & 1) ^ 1, abortp)) { ok = false; break; }
+                if (!kb_wait_p(fb_smem_u32(&C->acc_empty[ab]), ((cnt >> 1) & 1) ^ 1, abortp, prof, 4)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (int ks = 0; ks < ksteps && ok; ks++, step++) {
                     const int s = step % KBD_STAGES;
-                    if (!kb_wait(fb_smem_u32(&C->full[s]), (step / KBD_STAGES) & 1, abortp)) { ok = false; break; }
+                    if (!kb_wait_p(fb_smem_u32(&C->full[s]), (step / KBD_STAGES) & 1, abortp, prof, 5)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st_u = dyn_u + s * KBD_STAGE_BYTES, b_u = st_u + 2 * KB_ATOM_BYTES;
 #pragma unroll
@@ -636,7 +649,7 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_down(kb_gemm_args_t P) {
         for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, cnt++) {
             const kb_item_t I = P.items[it];
             const int ab = cnt & 1;
-            if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->acc_full[ab]), (cnt >> 1) & 1, abortp))) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, kb_wait_p(fb_smem_u32(&C->acc_full[ab]), (cnt >> 1) & 1, abortp, prof, 6))) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int grow = I.m * KB_TILE_M + warp * 32 + lane;
             const uint32_t t0 = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)ab * KB_TILE_N;
@@ -658,6 +671,7 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_down(kb_gemm_args_t P) {
         C->abort_flag = 1;
         atomicExch(P.status, FB_ST_WAIT_TIMEOUT);
     }
+    if (prof && tid == 0) atomicAdd(prof + 7, (unsigned long long)(clock64() - t_start));
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 4) {
@@ -692,7 +706,7 @@ struct kbg_ctl_t {
     /* activation side of a 256-block's scaling, per pair: {d, the eight sub-block sums, pad}; written by the producers
      * with the block's operand tiles, read by the epilogue.  Four blocks deep: the producers run at most two blocks
      * ahead of the MMAs, and the MMAs at most two ahead of the epilogue. */
-    alignas(16) float xt[4][KB_GU_N][12]; /* read as float4: 16-byte aligned inside the struct */
+    alignas(16) uint4 xt[4][KB_GU_N][2];  /* {d as float bits, -, -, -}, {eight int16 sums} */
 };
 
 __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
@@ -704,6 +718,10 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
     const int n_items = *P.n_items;
     const int kbs = P.K / 256;
     volatile int *abortp = &C->abort_flag;
+    /* profiling aid, as in k_kb_down, slots 8..15: copy thread, producers (pair table / raw weights / operand stage),
+     * MMA thread (accumulator buffer / filled stage), epilogue (a block's sums), the block's run time */
+    unsigned long long *prof = (blockIdx.x == 0 && P.prof) ? P.prof + 8 : nullptr;
+    const long long t_start = clock64();
 
     if (tid == 0) {
         for (int s = 0; s < KBG_STAGES; s++) {
@@ -733,30 +751,30 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
     const uint32_t tmem = C->tmem_base;
     bool ok = true;
 
-    if (warp >= KB_PROD_WARP0) {
+    if (warp == KB_COPY_WARP) {
+        /* ---------------- copy thread: gate and up unit of every 256-block, two blocks ahead */
+        if (lane == 0) {
+            kb_cursor_t cur = {(int)blockIdx.x, -1};
+            for (uint32_t blk = 0; kb_cursor_next(cur, kbs, n_items, gridDim.x); blk++) {
+                const uint32_t r = blk % KBG_RAW, bar = fb_smem_u32(&C->raw_full[r]);
+                if (blk >= KBG_RAW && !kb_wait_p(fb_smem_u32(&C->raw_empty[r]), ((blk / KBG_RAW) - 1) & 1, abortp, prof, 0)) { ok = false; break; }
+                const kb_item_t J = P.items[cur.it];
+                const uint8_t *rec = P.w_layer + (uint64_t)J.e * P.rec_bytes;
+                const uint64_t off = ((uint64_t)J.m * kbs + cur.kb) * KB_TILE_BYTES;
+                fb_mbar_expect_tx(bar, 2 * KB_TILE_BYTES);
+                fb_bulk_g2s(raw_u + r * 2 * KB_TILE_BYTES, rec + P.mat_off[0] + off, KB_TILE_BYTES, bar);
+                fb_bulk_g2s(raw_u + r * 2 * KB_TILE_BYTES + KB_TILE_BYTES, rec + P.mat_off[1] + off, KB_TILE_BYTES, bar);
+            }
+        }
+        __syncwarp();
+    } else if (warp >= KB_PROD_WARP0) {
         /* ---------------- producers: thread (mat, row) */
         const int pt = tid - KB_PROD_WARP0 * 32, mat = pt >> 7, row = pt & 127;
-        const bool copier = pt == 0;
         uint32_t step = 0, cnt = 0, rb = 0;
-        kb_cursor_t cur = {(int)blockIdx.x, -1};
-        auto issue = [&](uint32_t blk) {
-            if (!kb_cursor_next(cur, kbs, n_items, gridDim.x)) return;
-            const kb_item_t J = P.items[cur.it];
-            const uint32_t r = blk % KBG_RAW, bar = fb_smem_u32(&C->raw_full[r]);
-            const uint8_t *rec = P.w_layer + (uint64_t)J.e * P.rec_bytes;
-            const uint64_t off = ((uint64_t)J.m * kbs + cur.kb) * KB_TILE_BYTES;
-            fb_mbar_expect_tx(bar, 2 * KB_TILE_BYTES);
-            fb_bulk_g2s(raw_u + r * 2 * KB_TILE_BYTES, rec + P.mat_off[0] + off, KB_TILE_BYTES, bar);
-            fb_bulk_g2s(raw_u + r * 2 * KB_TILE_BYTES + KB_TILE_BYTES, rec + P.mat_off[1] + off, KB_TILE_BYTES, bar);
-        };
-        if (copier) {
-            issue(0);
-            issue(1);
-        }
         for (int it = blockIdx.x;; it += gridDim.x, cnt++) {
             const bool more = it < n_items;
             const int ab = cnt & 1;
-            bool w = ok && (!more || kb_wait(fb_smem_u32(&C->item_done[ab]), ((cnt >> 1) & 1) ^ 1, abortp));
+            bool w = ok && (!more || kb_wait_p(fb_smem_u32(&C->item_done[ab]), ((cnt >> 1) & 1) ^ 1, abortp, prof, 1));
             if (!w) C->abort_flag = 1;
             {
                 uint32_t all;
@@ -792,7 +810,7 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
             const __half2 zero2 = __float2half2_rn(0.0f);
             for (int kb = 0; kb < kbs && ok; kb++, rb++) {
                 const uint32_t r = rb % KBG_RAW;
-                if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->raw_full[r]), (rb / KBG_RAW) & 1, abortp))) {
+                if (!__all_sync(0xffffffffu, kb_wait_p(fb_smem_u32(&C->raw_full[r]), (rb / KBG_RAW) & 1, abortp, prof, 2))) {
                     C->abort_flag = 1;
                     ok = false;
                     break;
@@ -804,20 +822,14 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
                 for (int p = 0; p < 8; p++) q[p] = fb_lds128(u_u + 2048u * (p + 1));
                 __syncwarp();
                 if (lane == 0) fb_mbar_arrive(fb_smem_u32(&C->raw_empty[r]));
-                if (copier) {
-                    if (kb_wait(fb_smem_u32(&C->raw_empty[r]), (rb / KBG_RAW) & 1, abortp)) issue(rb + KBG_RAW);
-                }
                 const uint32_t sc_w[2] = {hdr.y & 0x3f3f3f3fu, (hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4)};
-                /* this block's scale and sub-block sums of every pair: 9 values per pair, one or two per thread */
-                float xv[2] = {0.0f, 0.0f};
-#pragma unroll
-                for (int u = 0; u < 2; u++) {
-                    const int i = pt + u * KB_PROD_THREADS;
-                    if (i < I.n * 9) {
-                        const int col = i / 9, f = i - col * 9;
-                        const size_t xb = (size_t)C->xrow[ab][col] * kbs + kb;
-                        xv[u] = f ? __ldg(P.xbs + xb * 8 + (f - 1)) : __ldg(P.xscale + xb);
-                    }
+                /* this block's scale and sub-block sums of every pair: one pair per thread (the first n threads) */
+                uint4 xv = make_uint4(0, 0, 0, 0);
+                float xd = 0.0f;
+                if (pt < I.n) {
+                    const size_t xb = (size_t)C->xrow[ab][pt] * kbs + kb;
+                    xv = __ldg(reinterpret_cast<const uint4 *>(P.xbs + xb * 8));
+                    xd = __ldg(P.xscale + xb);
                 }
 #pragma unroll
                 for (int half = 0; half < 2; half++, step++) {
@@ -831,7 +843,7 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
                             bv[u] = __ldg(reinterpret_cast<const uint4 *>(P.xh + (size_t)C->xrow[ab][rr] * P.K + kb * 256 + half * 128 + a * 64) + ch);
                         }
                     }
-                    if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->empty[s]), ((step / KBG_STAGES) & 1) ^ 1, abortp))) {
+                    if (!__all_sync(0xffffffffu, kb_wait_p(fb_smem_u32(&C->empty[s]), ((step / KBG_STAGES) & 1) ^ 1, abortp, prof, 3))) {
                         C->abort_flag = 1;
                         ok = false;
                         break;
@@ -855,12 +867,9 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
                                          : "memory");
                         }
                     }
-                    if (half == 0) {
-#pragma unroll
-                        for (int u = 0; u < 2; u++) {
-                            const int i = pt + u * KB_PROD_THREADS;
-                            if (i < I.n * 9) C->xt[rb & 3][i / 9][i % 9] = xv[u];
-                        }
+                    if (half == 0 && pt < I.n) {
+                        C->xt[rb & 3][pt][0] = make_uint4(__float_as_uint(xd), 0, 0, 0);
+                        C->xt[rb & 3][pt][1] = xv;
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
@@ -877,11 +886,11 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
                 const uint32_t idesc = kb_idesc((I.n + 15) & ~15);
                 for (int kb = 0; kb < kbs && ok; kb++, bc++) {
                     const int buf = bc & 1;
-                    if (!kb_wait(fb_smem_u32(&C->blk_empty[buf]), ((bc >> 1) & 1) ^ 1, abortp)) { ok = false; break; }
+                    if (!kb_wait_p(fb_smem_u32(&C->blk_empty[buf]), ((bc >> 1) & 1) ^ 1, abortp, prof, 4)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     for (int half = 0; half < 2 && ok; half++, step++) {
                         const int s = step % KBG_STAGES;
-                        if (!kb_wait(fb_smem_u32(&C->full[s]), (step / KBG_STAGES) & 1, abortp)) { ok = false; break; }
+                        if (!kb_wait_p(fb_smem_u32(&C->full[s]), (step / KBG_STAGES) & 1, abortp, prof, 5)) { ok = false; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint32_t st_u = dyn_u + s * KBG_STAGE_BYTES, b_u = st_u + KBG_A_BYTES;
 #pragma unroll
@@ -925,13 +934,7 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
                 const float nu = __half2float(__ushort_as_half((unsigned short)(hu.x >> 16)));
                 const uint32_t mgw[2] = {hg.z & 0x3f3f3f3fu, ((hg.w >> 4) & 0x0f0f0f0fu) | (((hg.z >> 6) & 0x03030303u) << 4)};
                 const uint32_t muw[2] = {hu.z & 0x3f3f3f3fu, ((hu.w >> 4) & 0x0f0f0f0fu) | (((hu.z >> 6) & 0x03030303u) << 4)};
-                float mg[8], mu[8]; /* dmin * m_j: one multiplication fewer per pair below */
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    mg[i] = (float)((mgw[i >> 2] >> (8 * (i & 3))) & 0xff);
-                    mu[i] = (float)((muw[i >> 2] >> (8 * (i & 3))) & 0xff);
-                }
-                if (!__all_sync(0xffffffffu, kb_wait(fb_smem_u32(&C->blk_full[buf]), (bc >> 1) & 1, abortp))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, kb_wait_p(fb_smem_u32(&C->blk_full[buf]), (bc >> 1) & 1, abortp, prof, 6))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t t0 = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * 2) * KB_GU_N;
 #pragma unroll
@@ -944,20 +947,20 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
 #pragma unroll
                         for (int j = 0; j < 16; j++) {
                             if (c0 + j < I.n) {
-                                const float4 *xt = reinterpret_cast<const float4 *>(C->xt[bc & 3][c0 + j]);
-                                const float4 t0v = xt[0], t1v = xt[1], t2v = xt[2];
-                                const float yd = t0v.x;
-                                const float bs[8] = {t0v.y, t0v.z, t0v.w, t1v.x, t1v.y, t1v.z, t1v.w, t2v.x};
-                                float msg = 0.0f, msu = 0.0f; /* exact: integers far below 2^24 */
-#pragma unroll
-                                for (int i = 0; i < 8; i++) {
-                                    msg = __fmaf_rn(mg[i], bs[i], msg);
-                                    msu = __fmaf_rn(mu[i], bs[i], msu);
-                                }
+                                const float yd = __uint_as_float(C->xt[bc & 3][c0 + j][0].x);
+                                const uint4 bs = C->xt[bc & 3][c0 + j][1]; /* int16 pairs (bs_0, bs_1) .. (bs_6, bs_7) */
+                                /* sum_j m_j * bs_j in exact integers, two terms per instruction (int16 pair x byte pair) */
+                                int msg = fb_dp2a_lo_su(bs.x, mgw[0], 0), msu = fb_dp2a_lo_su(bs.x, muw[0], 0);
+                                msg = fb_dp2a_hi_su(bs.y, mgw[0], msg);
+                                msu = fb_dp2a_hi_su(bs.y, muw[0], msu);
+                                msg = fb_dp2a_lo_su(bs.z, mgw[1], msg);
+                                msu = fb_dp2a_lo_su(bs.z, muw[1], msu);
+                                msg = fb_dp2a_hi_su(bs.w, mgw[1], msg);
+                                msu = fb_dp2a_hi_su(bs.w, muw[1], msu);
                                 accg[c0 + j] = __fmaf_rn(__fmul_rn(yd, dg), __uint_as_float(ig[j]), accg[c0 + j]);
-                                accg[c0 + j] = __fmaf_rn(-__fmul_rn(yd, ng), msg, accg[c0 + j]);
+                                accg[c0 + j] = __fmaf_rn(-__fmul_rn(yd, ng), (float)msg, accg[c0 + j]);
                                 accu[c0 + j] = __fmaf_rn(__fmul_rn(yd, du), __uint_as_float(iu[j]), accu[c0 + j]);
-                                accu[c0 + j] = __fmaf_rn(-__fmul_rn(yd, nu), msu, accu[c0 + j]);
+                                accu[c0 + j] = __fmaf_rn(-__fmul_rn(yd, nu), (float)msu, accu[c0 + j]);
                             }
                         }
                     }
@@ -982,6 +985,7 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
         C->abort_flag = 1;
         atomicExch(P.status, FB_ST_WAIT_TIMEOUT);
     }
+    if (prof && tid == 0) atomicAdd(prof + 7, (unsigned long long)(clock64() - t_start));
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 4) {
@@ -1034,14 +1038,14 @@ extern "C" int kb_launch_gen_f32(float *dst, uint64_t n, uint64_t seed, uint32_t
 }
 
 extern "C" int kb_launch_prologue(float *x, const float *resid, const float *normw, float rms_eps, int n_tokens, int n_embd,
-                                  float *h_out, uint16_t *xh, float *xscale, float *xbs, void *stream) {
+                                  float *h_out, uint16_t *xh, float *xscale, int16_t *xbs, void *stream) {
     if (n_embd > KBQ_MAX_K || n_embd % 256) return (int)cudaErrorInvalidValue;
     k_kb_rows<<<n_tokens, KBQ_THREADS, (size_t)n_embd * 5, (cudaStream_t)stream>>>(x, nullptr, resid, normw, rms_eps, n_embd,
                                                                                   h_out, xh, xscale, xbs, 1);
     return (int)cudaGetLastError();
 }
 
-extern "C" int kb_launch_quant(const float *src, int rows, int n, int exact, uint16_t *xh, float *xscale, float *xbs,
+extern "C" int kb_launch_quant(const float *src, int rows, int n, int exact, uint16_t *xh, float *xscale, int16_t *xbs,
                                void *stream) {
     if (n > KBQ_MAX_K || n % 256 || (exact && !xbs)) return (int)cudaErrorInvalidValue;
     k_kb_rows<<<rows, KBQ_THREADS, (size_t)n * 5, (cudaStream_t)stream>>>(nullptr, src, nullptr, nullptr, 0.0f, n, nullptr, xh,

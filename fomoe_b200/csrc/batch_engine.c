@@ -26,11 +26,13 @@ struct fomoe_b200_batch {
     float **resid, **normw;
     float *logits;         /* [n_layers][max_tokens][n_experts] or NULL */
     /* work buffers for max_tokens tokens */
-    float *x, *h, *lg, *scores, *act, *dots, *xs_h, *xs_a, *bs_h;
+    float *x, *h, *lg, *scores, *act, *dots, *xs_h, *xs_a;
+    int16_t *bs_h;
     uint16_t *xh_h, *xh_a;
     int *ids, *counts, *pairs, *n_items, *status;
     kb_item_t *items_gu, *items_dn;
     uint8_t *stage;
+    unsigned long long *prof; /* wait-cycle counters of the GEMM kernels' block 0 while profiling, or NULL */
     uint64_t launches;
     char err[256];
 };
@@ -75,7 +77,7 @@ void fomoe_b200_batch_destroy(fomoe_b200_batch_t *b) {
     cudaFree(b->logits); cudaFree(b->x); cudaFree(b->h); cudaFree(b->lg); cudaFree(b->scores); cudaFree(b->act);
     cudaFree(b->dots); cudaFree(b->xs_h); cudaFree(b->xs_a); cudaFree(b->bs_h); cudaFree(b->xh_h); cudaFree(b->xh_a); cudaFree(b->ids);
     cudaFree(b->counts); cudaFree(b->pairs); cudaFree(b->n_items); cudaFree(b->status); cudaFree(b->items_gu);
-    cudaFree(b->items_dn); cudaFree(b->stage);
+    cudaFree(b->items_dn); cudaFree(b->stage); cudaFree(b->prof);
     if (b->ev0) cudaEventDestroy(b->ev0);
     if (b->ev1) cudaEventDestroy(b->ev1);
     if (b->stream) cudaStreamDestroy(b->stream);
@@ -139,7 +141,7 @@ fomoe_b200_batch_t *fomoe_b200_batch_create(const fomoe_b200_batch_config_t *cfg
         balloc(b, (void **)&b->ids, sizeof(int) * (uint64_t)T * cfg->top_k) ||
         balloc(b, (void **)&b->act, sizeof(float) * npairs * ni) || balloc(b, (void **)&b->dots, sizeof(float) * npairs * ne) ||
         balloc(b, (void **)&b->xh_h, sizeof(uint16_t) * (uint64_t)T * ne) || balloc(b, (void **)&b->xs_h, sizeof(float) * (uint64_t)T * (ne / 256)) ||
-        balloc(b, (void **)&b->bs_h, sizeof(float) * (uint64_t)T * (ne / 256) * 8) ||
+        balloc(b, (void **)&b->bs_h, sizeof(int16_t) * (uint64_t)T * (ne / 256) * 8) ||
         balloc(b, (void **)&b->xh_a, sizeof(uint16_t) * npairs * ni) || balloc(b, (void **)&b->xs_a, sizeof(float) * npairs) ||
         balloc(b, (void **)&b->counts, sizeof(int) * (nrec + 1)) || balloc(b, (void **)&b->pairs, sizeof(int) * npairs) ||
         balloc(b, (void **)&b->n_items, sizeof(int) * 2) || balloc(b, (void **)&b->status, sizeof(int)) ||
@@ -235,6 +237,7 @@ static int enqueue_layer(fomoe_b200_batch_t *b, int layer, int T, const float *l
     a.n_tokens = T;
     a.pairs = b->pairs;
     a.status = b->status;
+    a.prof = b->prof;
     /* gate + up + SwiGLU */
     a.mat_off[0] = 0;
     a.mat_off[1] = b->mat_gu;
@@ -330,6 +333,24 @@ int fomoe_b200_batch_get_routing(fomoe_b200_batch_t *b, int n_tokens, int *ids, 
     if (scores) BCK(b, cudaMemcpy(scores, b->scores, sizeof(float) * (size_t)n_tokens * b->cfg.top_k, cudaMemcpyDeviceToHost));
     if (counts)
         BCK(b, cudaMemcpy(counts, b->counts, sizeof(int) * (size_t)(b->cfg.n_experts + (b->cfg.has_shared ? 1 : 0)), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+/* Profiling aid: on = 1 starts counting the cycles block 0 of the two GEMM kernels spends waiting, per role (out[0..7]
+ * down pass, out[8..15] gate/up pass; see batch.cu for the slots); on = 0 reads the counters into out[16] and stops. */
+int fomoe_b200_batch_wait_profile(fomoe_b200_batch_t *b, int on, unsigned long long *out) {
+    if (!b) return -1;
+    BCK(b, cudaSetDevice(b->cfg.device));
+    BCK(b, cudaStreamSynchronize(b->stream));
+    if (on) {
+        if (!b->prof && balloc(b, (void **)&b->prof, sizeof(unsigned long long) * 16)) return -1;
+        BCK(b, cudaMemset(b->prof, 0, sizeof(unsigned long long) * 16));
+        return 0;
+    }
+    if (!b->prof || !out) return -1;
+    BCK(b, cudaMemcpy(out, b->prof, sizeof(unsigned long long) * 16, cudaMemcpyDeviceToHost));
+    cudaFree(b->prof);
+    b->prof = NULL;
     return 0;
 }
 

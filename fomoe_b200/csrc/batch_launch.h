@@ -45,7 +45,7 @@ typedef struct {
      * down pass:            xh = q8 * d_block / d_max of the row, xscale[row] = d_max, xbs unused. */
     const uint16_t *xh;       /* [rows][K] */
     const float *xscale;
-    const float *xbs;
+    const int16_t *xbs;
     int x_by_token;           /* 1: pair p reads row p / top_k (routed) or p - T top_k (shared); 0: row p */
     int top_k, n_tokens;
     /* work */
@@ -54,6 +54,8 @@ typedef struct {
     const int *n_items;       /* device word */
     float *out;               /* [pairs][M]: SwiGLU activations (two matrices) or down outputs (one) */
     int *status;
+    /* optional profiling aid (NULL = off): block 0 adds the cycles its roles spent waiting, see batch.cu */
+    unsigned long long *prof;
 } kb_gemm_args_t;
 
 int kb_launch_gen(uint8_t *dst, uint64_t rec_bytes, int n_recs, uint64_t mat_off, int M, int K, uint64_t seed,
@@ -64,10 +66,10 @@ int kb_launch_export(uint8_t *dst_ggml, const uint8_t *src, int M, int K, void *
 /* x += resid (optional); h = rmsnorm(x) * normw (optional: else h = x); Q8_K of h per 256 (src/quant.c:343-375) written as
  * fp16 rows in K' order with one scale per row.  h_out (optional) receives h in fp32. */
 int kb_launch_prologue(float *x, const float *resid, const float *normw, float rms_eps, int n_tokens, int n_embd,
-                       float *h_out, uint16_t *xh, float *xscale, float *xbs, void *stream);
+                       float *h_out, uint16_t *xh, float *xscale, int16_t *xbs, void *stream);
 /* the same quantiser on [rows][n] fp32 rows.  exact = 1: the form the gate/up pass reads (xbs must be given);
  * exact = 0: the form the down pass reads */
-int kb_launch_quant(const float *src, int rows, int n, int exact, uint16_t *xh, float *xscale, float *xbs, void *stream);
+int kb_launch_quant(const float *src, int rows, int n, int exact, uint16_t *xh, float *xscale, int16_t *xbs, void *stream);
 /* softmax over all experts, ordered top-k (value descending, lower index first), renormalised weights */
 int kb_launch_route(const float *logits, int n_tokens, int n_experts, int top_k, int *ids, float *scores,
                     int *status, void *stream);

@@ -328,6 +328,10 @@ int fomoe_b200_batch_stack_run(fomoe_b200_batch_t *b, int n_tokens, int l0, int 
 int fomoe_b200_batch_tokens_download(fomoe_b200_batch_t *b, int n_tokens, float *x_out);
 /* Routing of the most recent layer call, and how many pairs every expert received (n_experts + has_shared counts). */
 int fomoe_b200_batch_get_routing(fomoe_b200_batch_t *b, int n_tokens, int *ids, float *scores, int *counts);
+/* Profiling aid: on = 1 starts counting the clock cycles block 0 of the two grouped-GEMM kernels spends waiting, per
+ * role; on = 0 copies the 16 counters out (0..7 down pass, 8..15 gate/up pass: copy thread, producers x3, MMA thread
+ * x2, epilogue, the block's whole run time) and stops. */
+int fomoe_b200_batch_wait_profile(fomoe_b200_batch_t *b, int on, unsigned long long *out);
 void fomoe_b200_batch_synth_logits(uint64_t seed, int layer, int max_tokens, int n_experts, int n_tokens, float *out);
 
 /* Host-side synthetic generator (same bytes as fomoe_b200_table_generate puts on the device). */
