@@ -22,6 +22,7 @@ LIB_PATH = os.environ.get("FOMOE_B200_LIB") or os.path.join(_HERE, "libfomoe_b20
 TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K = 12, 13, 14
 STREAM_ROUTER, STREAM_RESID, STREAM_NORMW, STREAM_HIDDEN = 3, 4, 5, 6
 M_GATE, M_UP, M_DOWN = 0, 1, 2
+TYPE_Q8_0, TYPE_MXFP4 = 8, 39
 ROUTER_STD, RESID_STD, NORMW_MEAN, NORMW_STD = 0.02, 1.0, 1.0, 0.1
 BLOCK_BYTES = {TYPE_Q4_K: 144, TYPE_Q5_K: 176, TYPE_Q6_K: 210}
 
@@ -78,6 +79,9 @@ _SIGS = {
     "fomoe_b200_destroy": (None, [C.c_void_p]),
     "fomoe_b200_last_error": (C.c_char_p, [C.c_void_p]),
     "fomoe_b200_status": (C.c_int, [C.c_void_p]),
+    "fomoe_b200_proj_matvec_f32": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p, _f32p]),
+    "fomoe_b200_shared_ffn_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
+                                            C.c_int, C.c_int, _f32p, _f32p]),
     "fomoe_b200_record_bytes": (C.c_uint64, [C.c_void_p, C.c_int]),
     "fomoe_b200_table_bytes": (C.c_uint64, [C.c_void_p]),
     "fomoe_b200_table_generate": (C.c_int, [C.c_void_p, C.c_uint64]),
@@ -213,10 +217,10 @@ def synth_glue(seed, layer, n_embd):
             synth_f32(seed, layer, STREAM_NORMW, NORMW_MEAN, NORMW_STD, n_embd))
 
 
-def synth_expert_record(seed, layer, expert, down_type, n_embd, inter):
+def synth_expert_record(seed, layer, expert, down_type, n_embd, inter, gate_type=TYPE_Q4_K):
     """One expert in the reference's record order (include/expert_store.h:9-40): gate | up | down, ggml bytes."""
-    return np.concatenate([synth_matrix(seed, layer, expert, M_GATE, TYPE_Q4_K, inter, n_embd),
-                           synth_matrix(seed, layer, expert, M_UP, TYPE_Q4_K, inter, n_embd),
+    return np.concatenate([synth_matrix(seed, layer, expert, M_GATE, gate_type, inter, n_embd),
+                           synth_matrix(seed, layer, expert, M_UP, gate_type, inter, n_embd),
                            synth_matrix(seed, layer, expert, M_DOWN, down_type, n_embd, inter)])
 
 
@@ -225,14 +229,15 @@ class MoeDecoder:
 
     def __init__(self, n_layers, n_embd=4096, n_inter=1024, n_experts=512, top_k=10, has_shared=True,
                  down_types=None, device=0, tp_rank=0, tp_size=1, rms_eps=1e-6, car_threshold=1.0,
-                 car_dampen=False, max_tokens=1):
+                 car_dampen=False, max_tokens=1, gate_type=TYPE_Q4_K):
         self._l = lib()
         self.n_layers, self.n_embd, self.n_inter = n_layers, n_embd, n_inter
+        self.gate_type = gate_type
         self.n_experts, self.top_k, self.has_shared = n_experts, top_k, bool(has_shared)
         self.tp_rank, self.tp_size, self.device = tp_rank, tp_size, device
         self.down_types = list(down_types) if down_types is not None else [TYPE_Q6_K] * n_layers
         self._dt = (C.c_int * n_layers)(*self.down_types)
-        cfg = Config(device, n_layers, n_embd, n_inter, n_experts, top_k, int(bool(has_shared)), TYPE_Q4_K,
+        cfg = Config(device, n_layers, n_embd, n_inter, n_experts, top_k, int(bool(has_shared)), gate_type,
                      C.cast(self._dt, _i32p), tp_rank, tp_size, rms_eps, car_threshold, int(bool(car_dampen)),
                      max_tokens)
         self._h = self._l.fomoe_b200_create(C.byref(cfg))
@@ -265,6 +270,22 @@ class MoeDecoder:
         assert r.size == self.record_bytes(layer), (r.size, self.record_bytes(layer))
         self._ck(self._l.fomoe_b200_table_upload(self._h, layer, expert, r.ctypes.data), "table_upload")
 
+    def proj_matvec_f32(self, qtype, w, rows, cols, x):
+        """y = W x on fp32 activations, W in 32-value blocks (TYPE_Q8_0 / TYPE_MXFP4), ggml order."""
+        w = np.ascontiguousarray(w).view(np.uint8).reshape(-1)
+        y = np.empty(rows, dtype=np.float32)
+        self._ck(self._l.fomoe_b200_proj_matvec_f32(self._h, qtype, w.ctypes.data, rows, cols, _fp(_f32(x)), _fp(y)),
+                 "proj_matvec_f32")
+        return y
+
+    def shared_ffn_f32(self, h, gate, gate_type, up, up_type, down, down_type, n_embd, inter):
+        """The reference's shared_expert_ffn (src/inference.c:361-374) for Q8_0 / MXFP4 projections."""
+        g, u, d = (np.ascontiguousarray(a).view(np.uint8).reshape(-1) for a in (gate, up, down))
+        out = np.empty(n_embd, dtype=np.float32)
+        self._ck(self._l.fomoe_b200_shared_ffn_f32(self._h, g.ctypes.data, gate_type, u.ctypes.data, up_type, d.ctypes.data,
+                                                   down_type, n_embd, inter, _fp(_f32(h)), _fp(out)), "shared_ffn_f32")
+        return out
+
     @property
     def half_mode(self):
         """Twice as many ranks as 256-wide windows: two ranks share a window (see the C header)."""
@@ -274,7 +295,7 @@ class MoeDecoder:
         il = 256 if self.half_mode else self.n_inter // self.tp_size
         if matrix == M_DOWN:
             return self.down_types[layer], self.n_embd, 128 if self.half_mode else il
-        return TYPE_Q4_K, il, self.n_embd
+        return self.gate_type, il, self.n_embd
 
     def export_shard(self, layer, expert, matrix):
         """This rank's shard of one matrix, ggml block order, row-major over (rows, column blocks)."""

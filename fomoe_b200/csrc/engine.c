@@ -242,7 +242,7 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
     if (cfg->device < 0 || cfg->device >= ndev || cfg->n_layers < 1 || cfg->n_embd % FB_QK || cfg->n_embd > 8192 ||
         cfg->n_embd < FB_QK || cfg->n_inter % FB_QK || cfg->n_inter < FB_QK || N > FB_MAX_TP || cfg->n_experts < 1 ||
         cfg->n_experts > FB_MAX_EXPERTS || cfg->top_k < 1 || cfg->top_k > FB_MAX_TOPK || cfg->top_k > cfg->n_experts ||
-        cfg->gate_type != FB_TYPE_Q4_K || cfg->tp_rank < 0 || cfg->tp_rank >= N) {
+        (cfg->gate_type != FB_TYPE_Q4_K && cfg->gate_type != FB_TYPE_Q6_K) || cfg->tp_rank < 0 || cfg->tp_rank >= N) {
         set_err(c, "unsupported configuration");
         free(c);
         return NULL;
@@ -281,7 +281,7 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
     c->n_slots = cfg->top_k + (cfg->has_shared ? 1 : 0);
     c->gate_groups = (int)fb_n_groups((uint64_t)c->inter_local * c->gate_bpr);
     c->down_groups = (int)fb_n_groups((uint64_t)cfg->n_embd * c->down_bpr);
-    c->gate_bytes = fb_shard_bytes(FB_TYPE_Q4_K, (uint64_t)c->inter_local * c->gate_bpr);
+    c->gate_bytes = fb_shard_bytes(cfg->gate_type, (uint64_t)c->inter_local * c->gate_bpr);
     c->max_tokens = cfg->max_tokens > 0 ? cfg->max_tokens : 1;
     c->down_types = (int *)malloc(sizeof(int) * (size_t)cfg->n_layers);
     for (int l = 0; l < cfg->n_layers; l++) {
@@ -1010,6 +1010,7 @@ static void fill_args(const fomoe_b200_ctx_t *c, int layer, fb_args_t *a) {
     a->tp_size = c->cfg.tp_size;
     a->gate_bpr = c->gate_bpr;
     a->down_bpr = c->down_bpr;
+    a->gate_type = c->cfg.gate_type;
     a->gate_groups = c->gate_groups;
     a->down_groups = c->down_groups;
     a->up_off = c->gate_bytes;
@@ -1068,7 +1069,7 @@ static int enqueue_experts(fomoe_b200_ctx_t *c, const fb_args_t *a) {
         CKL(c, fb_launch_down_f32(a, grid_tasks(c, a->n_slots * a->down_groups), c->stream));
         return 0;
     }
-    if (c->variant != 1 || a->n_slots > 15) {
+    if (c->variant != 1 || a->n_slots > 15 || a->gate_type != FB_TYPE_Q4_K) {
         CKL(c, fb_launch_gate_up(a, grid_tasks(c, a->n_slots * a->gate_groups), c->stream));
         CKL(c, fb_launch_down(a, grid_tasks(c, a->n_slots * a->down_groups), c->stream));
         return 0;
@@ -1508,6 +1509,74 @@ done:
     return rc;
 }
 
+/* ------------------------------------------------------------------ projections in 32-value blocks */
+static uint64_t p32_bytes(int type, int rows, int cols) {
+    return (uint64_t)rows * (uint64_t)(cols / 32) * (type == FB_TYPE_Q8_0 ? 34u : 17u);
+}
+static int p32_type_ok(int type) { return type == FB_TYPE_Q8_0 || type == FB_TYPE_MXFP4; }
+
+/* device view of `bytes` bytes at p: p itself when it is memory of this GPU, else a temporary copy (*tmp, to free) */
+static const uint8_t *dev_view(fomoe_b200_ctx_t *c, const void *p, uint64_t bytes, void **tmp) {
+    struct cudaPointerAttributes at;
+    *tmp = NULL;
+    if (cudaPointerGetAttributes(&at, p) == cudaSuccess && at.type == cudaMemoryTypeDevice && at.device == c->cfg.device)
+        return (const uint8_t *)p;
+    cudaGetLastError();
+    if (cudaMalloc(tmp, bytes) != cudaSuccess) {
+        *tmp = NULL;
+        return NULL;
+    }
+    if (cudaMemcpyAsync(*tmp, p, bytes, cudaMemcpyDefault, c->stream) != cudaSuccess) return NULL;
+    return (const uint8_t *)*tmp;
+}
+
+int fomoe_b200_proj_matvec_f32(fomoe_b200_ctx_t *c, int type, const void *w, int rows, int cols, const float *x, float *y) {
+    if (!c || !w || !x || !y || rows < 1 || cols < 32 || cols % 32 || !p32_type_ok(type)) return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    void *tw = NULL, *tx = NULL, *ty = NULL;
+    int rc = -1;
+    const uint8_t *dw = dev_view(c, w, p32_bytes(type, rows, cols), &tw);
+    const float *dx = (const float *)dev_view(c, x, sizeof(float) * (uint64_t)cols, &tx);
+    if (!dw || !dx || cudaMalloc(&ty, sizeof(float) * (size_t)rows) != cudaSuccess) goto done;
+    c->launches++;
+    if (fb_launch_p32_matvec(type, dw, rows, cols, dx, (float *)ty, c->stream)) goto done;
+    if (cudaMemcpyAsync(y, ty, sizeof(float) * (size_t)rows, cudaMemcpyDefault, c->stream) || cudaStreamSynchronize(c->stream))
+        goto done;
+    rc = 0;
+done:
+    if (rc) set_err(c, "proj_matvec_f32 failed: %s", cudaGetErrorString(cudaGetLastError()));
+    cudaFree(tw); cudaFree(tx); cudaFree(ty);
+    return rc;
+}
+
+int fomoe_b200_shared_ffn_f32(fomoe_b200_ctx_t *c, const void *gate, int gate_type, const void *up, int up_type,
+                              const void *down, int down_type, int n_embd, int n_inter, const float *h, float *out) {
+    if (!c || !gate || !up || !down || !h || !out || n_embd < 32 || n_embd % 32 || n_inter < 32 || n_inter % 32 ||
+        !p32_type_ok(gate_type) || !p32_type_ok(up_type) || !p32_type_ok(down_type))
+        return -1;
+    CK(c, cudaSetDevice(c->cfg.device));
+    void *tg = NULL, *tu = NULL, *td = NULL, *th = NULL, *ta = NULL, *to = NULL;
+    int rc = -1;
+    const uint8_t *dg = dev_view(c, gate, p32_bytes(gate_type, n_inter, n_embd), &tg);
+    const uint8_t *du = dev_view(c, up, p32_bytes(up_type, n_inter, n_embd), &tu);
+    const uint8_t *dd = dev_view(c, down, p32_bytes(down_type, n_embd, n_inter), &td);
+    const float *dh = (const float *)dev_view(c, h, sizeof(float) * (uint64_t)n_embd, &th);
+    if (!dg || !du || !dd || !dh || cudaMalloc(&ta, sizeof(float) * (size_t)n_inter) != cudaSuccess ||
+        cudaMalloc(&to, sizeof(float) * (size_t)n_embd) != cudaSuccess)
+        goto done;
+    c->launches += 2;
+    if (fb_launch_p32_gate_up(gate_type, dg, up_type, du, n_inter, n_embd, dh, (float *)ta, c->stream) ||
+        fb_launch_p32_matvec(down_type, dd, n_embd, n_inter, (const float *)ta, (float *)to, c->stream))
+        goto done;
+    if (cudaMemcpyAsync(out, to, sizeof(float) * (size_t)n_embd, cudaMemcpyDefault, c->stream) || cudaStreamSynchronize(c->stream))
+        goto done;
+    rc = 0;
+done:
+    if (rc) set_err(c, "shared_ffn_f32 failed: %s", cudaGetErrorString(cudaGetLastError()));
+    cudaFree(tg); cudaFree(tu); cudaFree(td); cudaFree(th); cudaFree(ta); cudaFree(to);
+    return rc;
+}
+
 int fomoe_b200_quantize_q8k(fomoe_b200_ctx_t *c, const float *x, int n, void *out) {
     if (!c || !x || !out || n % FB_QK || n < FB_QK) return -1;
     CK(c, cudaSetDevice(c->cfg.device));
@@ -1586,8 +1655,8 @@ typedef struct {
 /* One engine per shape serves every down type: its record slots are sized for the largest block format (Q6_K) and
  * the type of a call's records travels with the call.  (The 397B model alternates Q6_K and Q4_K down projections
  * from layer to layer; an engine per type, rebuilt on every change, would allocate and free on every layer.) */
-static int op_engine_get(op_engine_t *o, int n_embd, int inter) {
-    if (o->eng && o->n_embd == n_embd && o->inter == inter) return 0;
+static int op_engine_get(op_engine_t *o, int n_embd, int inter, int gate_type) {
+    if (o->eng && o->n_embd == n_embd && o->inter == inter && o->eng->cfg.gate_type == gate_type) return 0;
     if (o->eng) fomoe_b200_destroy(o->eng);
     o->eng = NULL;
     fomoe_b200_config_t cfg;
@@ -1601,7 +1670,7 @@ static int op_engine_get(op_engine_t *o, int n_embd, int inter) {
     cfg.n_experts = OP_MAX_WORK;
     cfg.top_k = FB_MAX_TOPK;
     cfg.has_shared = 0;
-    cfg.gate_type = FB_TYPE_Q4_K;
+    cfg.gate_type = gate_type; /* one type per model in practice: a change rebuilds the engine */
     cfg.down_types = &down_type;
     cfg.tp_rank = 0;
     cfg.tp_size = 1;
@@ -1711,7 +1780,7 @@ void gpu_get_pingpong_relay_stats(gpu_ctx_t *ctx, uint64_t *handoffs, uint64_t *
 }
 
 static int op_types_ok(int gate_type, int up_type, int down_type) {
-    return gate_type == FB_TYPE_Q4_K && up_type == FB_TYPE_Q4_K &&
+    return (gate_type == FB_TYPE_Q4_K || gate_type == FB_TYPE_Q6_K) && up_type == gate_type &&
            (down_type == FB_TYPE_Q4_K || down_type == FB_TYPE_Q5_K || down_type == FB_TYPE_Q6_K);
 }
 
@@ -1726,7 +1795,7 @@ int gpu_expert_ffn(gpu_ctx_t *ctx, const float *h, void **expert_buffers, const 
     if (expert_gate_size != ggml_matrix_bytes(gate_type, expert_intermediate, n_embd) ||
         expert_up_size != ggml_matrix_bytes(up_type, expert_intermediate, n_embd))
         return -1;
-    if (op_engine_get(&ctx->op, n_embd, expert_intermediate)) return -1;
+    if (op_engine_get(&ctx->op, n_embd, expert_intermediate, gate_type)) return -1;
     fomoe_b200_ctx_t *c = ctx->op.eng;
     int ids[OP_MAX_EXPERTS];
     for (int e = 0; e < n_experts; e++) ids[e] = e;
@@ -1785,11 +1854,42 @@ void b200_expert_reset(b200_expert_ctx_t *x) {
 static int expert_batch(b200_expert_ctx_t *x, const float *input, const b200_expert_work_t *work, int n, int accumulate) {
     for (int i = 0; i < n; i++)
         if (!op_types_ok(work[i].gate_type, work[i].up_type, work[i].down_type) ||
-            work[i].down_type != work[0].down_type || !work[i].expert_data)
+            work[i].down_type != work[0].down_type || work[i].gate_type != work[0].gate_type || !work[i].expert_data)
             return -1;
-    const int had = x->op.eng != NULL;
-    if (op_engine_get(&x->op, x->n_embd, x->inter)) return -1;
+    int had = x->op.eng != NULL;
+    float *carry = NULL;
+    if (had && x->op.eng->cfg.gate_type != work[0].gate_type) {
+        /* the engine is rebuilt for the other gate/up format: what has been accumulated moves over, the quantised
+         * input does not */
+        if (x->dirty && accumulate) {
+            carry = (float *)malloc(sizeof(float) * (size_t)x->n_embd);
+            if (!carry) return -1;
+            cudaSetDevice(x->op.eng->cfg.device);
+            cudaStreamSynchronize(x->op.eng->stream);
+            if (cudaMemcpy(carry, x->op.eng->moe_out, sizeof(float) * (size_t)x->n_embd, cudaMemcpyDeviceToHost) != cudaSuccess) {
+                free(carry);
+                return -1;
+            }
+        }
+        had = 0;
+        x->input_valid = 0;
+        if (!input) {
+            free(carry);
+            return -1;
+        }
+    }
+    if (op_engine_get(&x->op, x->n_embd, x->inter, work[0].gate_type)) {
+        free(carry);
+        return -1;
+    }
     fomoe_b200_ctx_t *c = x->op.eng;
+    if (carry) {
+        cudaMemcpyAsync(c->moe_out, carry, sizeof(float) * (size_t)x->n_embd, cudaMemcpyHostToDevice, c->stream);
+        cudaStreamSynchronize(c->stream);
+        free(carry);
+        had = 1;
+        x->dirty = 1;
+    }
     if (!had || !x->dirty) cudaMemsetAsync(c->moe_out, 0, sizeof(float) * (size_t)x->n_embd, c->stream);
     int ids[OP_MAX_WORK];
     float sc[OP_MAX_WORK];

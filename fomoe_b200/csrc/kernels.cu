@@ -181,6 +181,7 @@ __global__ void k_set_slots(fb_args_t A) {
 }
 
 /* ------------------------------------------------------------------ gate / up / SwiGLU */
+template <int GT>
 __global__ void __launch_bounds__(256) k_gate_up(fb_args_t A) {
     extern __shared__ uint4 smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
@@ -198,16 +199,36 @@ __global__ void __launch_bounds__(256) k_gate_up(fb_args_t A) {
     for (int t = blockIdx.x * wpb + warp; t < total; t += gridDim.x * wpb) {
         const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
         const uint8_t *rec = A.slot_rec[slot];
-        const uint4 *pg = reinterpret_cast<const uint4 *>(rec + (uint64_t)g * FB_Q4K_GROUP) + lane;
-        const uint4 *pu = reinterpret_cast<const uint4 *>(rec + A.up_off + (uint64_t)g * FB_Q4K_GROUP) + lane;
-        uint4 hg = ldg_stream(pg), hu = ldg_stream(pu);
-        uint4 qg[8], qu[8];
+        float fg, fu;
+        if (GT == FB_TYPE_Q6_K) { /* src/quant.c:478-607 on both matrices, one after the other */
+            float f2[2];
+#pragma unroll 1
+            for (int which = 0; which < 2; which++) {
+                const uint8_t *gb = rec + (which ? A.up_off : 0) + (uint64_t)g * FB_Q6K_GROUP;
+                const uint4 *p = reinterpret_cast<const uint4 *>(gb) + lane;
+                uint4 ql[8], qh[4];
 #pragma unroll
-        for (int i = 0; i < 8; i++) qg[i] = ldg_stream(pg + 32 * (i + 1));
+                for (int i = 0; i < 8; i++) ql[i] = ldg_stream(p + 32 * i);
 #pragma unroll
-        for (int i = 0; i < 8; i++) qu[i] = ldg_stream(pu + 32 * (i + 1));
-        float fg = fb_dot_q4k(hg, qg, a);
-        float fu = fb_dot_q4k(hu, qu, a);
+                for (int i = 0; i < 4; i++) qh[i] = ldg_stream(p + 32 * (8 + i));
+                const uint4 sc = ldg_stream(p + 32 * 12);
+                const uint32_t d16 = __ldg(reinterpret_cast<const unsigned short *>(gb + FB_Q6K_OFF_D) + lane);
+                f2[which] = fb_dot_q6k(ql, qh, sc, d16, a);
+            }
+            fg = f2[0];
+            fu = f2[1];
+        } else {
+            const uint4 *pg = reinterpret_cast<const uint4 *>(rec + (uint64_t)g * FB_Q4K_GROUP) + lane;
+            const uint4 *pu = reinterpret_cast<const uint4 *>(rec + A.up_off + (uint64_t)g * FB_Q4K_GROUP) + lane;
+            uint4 hg = ldg_stream(pg), hu = ldg_stream(pu);
+            uint4 qg[8], qu[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) qg[i] = ldg_stream(pg + 32 * (i + 1));
+#pragma unroll
+            for (int i = 0; i < 8; i++) qu[i] = ldg_stream(pu + 32 * (i + 1));
+            fg = fb_dot_q4k(hg, qg, a);
+            fu = fb_dot_q4k(hu, qu, a);
+        }
         fg = fb_span_sum(fg, bpr);
         fu = fb_span_sum(fu, bpr);
         const int row = g * rpg + lane / bpr;
@@ -559,11 +580,13 @@ extern "C" int fb_launch_set_slots(const fb_args_t *a, void *stream) {
 
 extern "C" int fb_launch_gate_up(const fb_args_t *a, int grid, void *stream) {
     const size_t sm = (size_t)a->gate_bpr * sizeof(fb_q8_entry_t);
-    k_gate_up<<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
+    if (a->gate_type == FB_TYPE_Q6_K) k_gate_up<FB_TYPE_Q6_K><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
+    else k_gate_up<FB_TYPE_Q4_K><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
     return (int)cudaGetLastError();
 }
 
 extern "C" int fb_launch_gate_up_ring(const fb_args_t *a, int grid, void *stream) {
+    if (a->gate_type != FB_TYPE_Q4_K) return (int)cudaErrorInvalidValue; /* the rings are sized for Q4_K groups */
     const size_t sm = (size_t)GU_WARPS * GU_STAGES * GU_STAGE_BYTES + (size_t)GU_WARPS * GU_STAGES * 8;
     static unsigned char configured[FB_MAX_DEVICES];
     int dev;

@@ -114,6 +114,7 @@ __device__ __forceinline__ float dot_q6k_f32(const uint4 (&ql)[8], const uint4 (
 }
 
 /* gate/up + SwiGLU: tasks and row mapping as k_gate_up (kernels.cu); the hidden state sits in shared memory as floats */
+template <int GT>
 __global__ void __launch_bounds__(256) k_gate_up_f32(fb_args_t A) {
     extern __shared__ float hs[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
@@ -129,12 +130,25 @@ __global__ void __launch_bounds__(256) k_gate_up_f32(fb_args_t A) {
         float f[2];
 #pragma unroll
         for (int which = 0; which < 2; which++) {
-            const uint4 *p = reinterpret_cast<const uint4 *>(rec + (which ? A.up_off : 0) + (uint64_t)g * FB_Q4K_GROUP) + lane;
-            const uint4 hd = ldg_w(p);
-            uint4 q[8];
+            if (GT == FB_TYPE_Q6_K) {
+                const uint8_t *gb = rec + (which ? A.up_off : 0) + (uint64_t)g * FB_Q6K_GROUP;
+                const uint4 *p = reinterpret_cast<const uint4 *>(gb) + lane;
+                uint4 ql[8], qh[4];
 #pragma unroll
-            for (int i = 0; i < 8; i++) q[i] = ldg_w(p + 32 * (i + 1));
-            f[which] = fb_span_sum(dot_q45k_f32<false>(hd, hd, hd, q, y), bpr);
+                for (int i = 0; i < 8; i++) ql[i] = ldg_w(p + 32 * i);
+#pragma unroll
+                for (int i = 0; i < 4; i++) qh[i] = ldg_w(p + 32 * (8 + i));
+                const uint4 sc = ldg_w(p + 32 * 12);
+                const uint32_t d16 = __ldg(reinterpret_cast<const unsigned short *>(gb + FB_Q6K_OFF_D) + lane);
+                f[which] = fb_span_sum(dot_q6k_f32(ql, qh, sc, d16, y), bpr);
+            } else {
+                const uint4 *p = reinterpret_cast<const uint4 *>(rec + (which ? A.up_off : 0) + (uint64_t)g * FB_Q4K_GROUP) + lane;
+                const uint4 hd = ldg_w(p);
+                uint4 q[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) q[i] = ldg_w(p + 32 * (i + 1));
+                f[which] = fb_span_sum(dot_q45k_f32<false>(hd, hd, hd, q, y), bpr);
+            }
         }
         const int row = g * rpg + lane / bpr;
         if (lane % bpr == 0 && row < A.inter_local) {
@@ -223,12 +237,15 @@ extern "C" int fb_launch_gate_up_f32(const fb_args_t *a, int grid, void *stream)
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
     if (!configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_gate_up_f32, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(k_gate_up_f32<FB_TYPE_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(k_gate_up_f32<FB_TYPE_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
         if (e != cudaSuccess) return (int)e;
         configured[dev] = 1;
     }
     if (sm > 128 * 1024) return (int)cudaErrorInvalidValue;
-    k_gate_up_f32<<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
+    if (a->gate_type == FB_TYPE_Q6_K) k_gate_up_f32<FB_TYPE_Q6_K><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
+    else k_gate_up_f32<FB_TYPE_Q4_K><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
     return (int)cudaGetLastError();
 }
 

@@ -50,6 +50,7 @@ typedef struct {
     int n_embd, n_inter, inter_local, n_experts, top_k, n_slots, has_shared;
     int tp_rank, tp_size;
     int gate_bpr, down_bpr;       /* 256-column blocks per row in this rank's gate/up and down shards */
+    int gate_type;                /* FB_TYPE_Q4_K, or FB_TYPE_Q6_K (per-phase kernels with plain loads only) */
     int gate_groups, down_groups; /* 32-block groups per shard */
     uint64_t up_off, down_off;    /* byte offsets of the up and down shards inside an expert record */
     float rms_eps, car_threshold;
@@ -177,6 +178,10 @@ int fb_launch_dequant(float *dst, const uint8_t *shard, fb_shard_geom_t g, void 
 int fb_launch_matvec(float *out, const uint8_t *shard, fb_shard_geom_t g, const fb_q8_entry_t *q8, int grid,
                      void *stream);
 int fb_launch_quantize(fb_q8_entry_t *dst, const float *src, int n_blocks, void *stream);
+/* projections in 32-value blocks (Q8_0, MXFP4) on fp32 activations, weights in ggml order: proj32.cu */
+int fb_launch_p32_matvec(int type, const uint8_t *w, int rows, int cols, const float *x, float *y, void *stream);
+int fb_launch_p32_gate_up(int gate_type, const uint8_t *gate, int up_type, const uint8_t *up, int inter, int n_embd,
+                          const float *h, float *act, void *stream);
 
 #ifdef __cplusplus
 }

@@ -44,6 +44,8 @@
 #define FB_TYPE_Q4_K 12
 #define FB_TYPE_Q5_K 13
 #define FB_TYPE_Q6_K 14
+#define FB_TYPE_Q8_0 8    /* 32-value blocks, fp32 activations only: proj32.cu */
+#define FB_TYPE_MXFP4 39
 #define FB_QK 256
 #define FB_Q4K_BLOCK 144u
 #define FB_Q5K_BLOCK 176u

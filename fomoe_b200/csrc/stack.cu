@@ -803,6 +803,7 @@ extern "C" int fb_stack_supported(const fb_args_t *a, int grid) {
     const int run = (dtotal + grid - 1) / grid;                       /* longest run of down tasks of one block */
     const int max_rg = (run + a->n_slots - 2) / a->n_slots + 2;       /* row groups such a run can touch */
     if (a->down_half >= 0 && a->down_type != FB_TYPE_Q4_K && a->down_type != FB_TYPE_Q6_K) return 0;
+    if (a->gate_type != FB_TYPE_Q4_K) return 0;
     return a->n_embd <= 4096 && a->n_slots <= SK_DN_SLOTS && a->n_slots * a->down_bpr <= SK_MAX_Q8A &&
            a->n_embd / FB_QK <= 16 && a->tp_size <= FB_MAX_TP && a->inter_local % FB_QK == 0 && max_rg <= SK_MAX_RG;
 }

@@ -63,7 +63,7 @@ void gpu_get_pingpong_relay_stats(gpu_ctx_t *ctx, uint64_t *handoffs, uint64_t *
  * Same arguments as reference gpu.h:70-83.  expert_buffers[e] points at one expert record
  * in ggml byte order (gate | up | down back to back).  Returns 0, or -1 for shapes/types
  * outside the supported set (the reference's limits, src/gpu_kernels.hip:8393-8403, plus:
- * gate/up must be Q4_K, down Q4_K, Q5_K or Q6_K), in which case the caller falls back
+ * gate and up must share one type, Q4_K or Q6_K; down Q4_K, Q5_K or Q6_K), in which case the caller falls back
  * (src/inference.c:551).  Activations are quantised to Q8_K as in src/cpu_expert.c.
  * expert_buffers[e] may be host memory (staged: two staging buffers filled on a copy stream, the host does not
  * wait between records) or memory of the current GPU (regrouped where it lies, no staging). */
@@ -110,7 +110,8 @@ typedef struct {
     int n_experts;           /* routed experts per layer, <= 512 */
     int top_k;               /* experts used per token, <= 15 */
     int has_shared;          /* 1: one shared expert per layer (record index n_experts) */
-    int gate_type;           /* gate and up type: FOMOE_TYPE_Q4_K */
+    int gate_type;           /* gate and up type: FOMOE_TYPE_Q4_K, or FOMOE_TYPE_Q6_K (served by the per-phase kernels;
+                                the persistent stack kernel and the bulk-copy variants take Q4_K) */
     const int *down_types;   /* [n_layers] FOMOE_TYPE_Q4_K / FOMOE_TYPE_Q5_K / FOMOE_TYPE_Q6_K; NULL = all Q6_K */
     int tp_rank, tp_size;    /* tensor parallelism over the intermediate dimension, tp_size <= 8.  With W = n_inter/256
                                 windows: tp_size dividing W gives every rank W/tp_size whole windows; tp_size == 2 W
@@ -268,6 +269,21 @@ int fomoe_b200_peek(fomoe_b200_ctx_t *ctx, int what, void *out, uint64_t bytes);
 /* Microbenchmark / parity helpers: y[rows] = W[rows x cols] . Q8_K(x), W given in ggml order. */
 int fomoe_b200_matvec(fomoe_b200_ctx_t *ctx, int type, const void *w_ggml, int rows, int cols, const float *x,
                       float *y);
+/* Projections stored in 32-value blocks -- Q8_0 (type 8) and MXFP4 (type 39), the types some models keep their
+ * shared expert in -- on fp32 activations, the only form the reference has for them (src/quant.c:266-337 through
+ * mat_vec_mul, src/tensor.c:158-171; its GPU kernel: src/gpu_kernels.hip:2070-2103).  Weights in ggml order; a
+ * weight or activation pointer may be host memory (copied for the call) or memory of the context's GPU (used where
+ * it lies); results go to the host.
+ *   proj_matvec_f32: y[rows] = W[rows x cols] x.
+ *   shared_ffn_f32:  out[n_embd] = down (silu(gate h) * (up h)), the reference's shared_expert_ffn
+ *                    (src/inference.c:361-374); each matrix with its own type.
+ * Return 0, or -1 for other types / shapes that are not multiples of 32. */
+#define FOMOE_TYPE_Q8_0 8
+#define FOMOE_TYPE_MXFP4 39
+int fomoe_b200_proj_matvec_f32(fomoe_b200_ctx_t *ctx, int type, const void *w_ggml, int rows, int cols, const float *x,
+                               float *y);
+int fomoe_b200_shared_ffn_f32(fomoe_b200_ctx_t *ctx, const void *gate, int gate_type, const void *up, int up_type,
+                              const void *down, int down_type, int n_embd, int n_inter, const float *h, float *out);
 /* y[rows] = W[rows x cols] . Q8_K(x) with NO allocation of any kind.  (No counterpart in the reference: added for
  * callers that cannot call cudaMalloc while they run, such as a serving loop whose device memory was all handed out
  * at start-up or a latency-critical path that must not take cudaMalloc's device synchronisation.)

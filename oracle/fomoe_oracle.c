@@ -38,10 +38,19 @@ float orc_fp16_to_fp32(uint16_t h) {
     return out;
 }
 
+#ifndef ORC_Q8_0_FMA
+#define ORC_Q8_0_FMA 0
+#endif
+#ifndef ORC_MXFP4_FMA
+#define ORC_MXFP4_FMA 1
+#endif
+
 uint64_t orc_row_bytes(int type, int k) {
     if (type == ORC_TYPE_Q4_K) return (uint64_t)(k / ORC_QK_K) * sizeof(orc_block_q4_K);
     if (type == ORC_TYPE_Q5_K) return (uint64_t)(k / ORC_QK_K) * sizeof(orc_block_q5_K);
     if (type == ORC_TYPE_Q6_K) return (uint64_t)(k / ORC_QK_K) * sizeof(orc_block_q6_K);
+    if (type == ORC_TYPE_Q8_0) return (uint64_t)(k / 32) * 34u;
+    if (type == ORC_TYPE_MXFP4) return (uint64_t)(k / 32) * 17u;
     return 0;
 }
 
@@ -339,14 +348,115 @@ float orc_vec_dot_q6_K_f32(const void *xv, const float *y, int64_t n) {
     return sumf;
 }
 
+/* ---- 32-value blocks on fp32 activations: Q8_0 {fp16 d; int8 qs[32]} (include/quant_types.h:41-46) and MXFP4
+ * {uint8 e8m0 s; uint8 qs[16]} (48-53).  src/quant.c:266-288 and 290-337: one sum per block, `sumf += scale * sum`.
+ * ORC_Q8_0_FMA / ORC_MXFP4_FMA say whether the reference build fuses the multiply-adds of these loops (it does for
+ * MXFP4, whose table look-ups keep the loop scalar, and not for Q8_0, whose products are vectorised first); each
+ * form is pinned bit for bit against the compiled reference by the tests. ---- */
+static const float mxfp4_table[16] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f,
+                                      -0.0f, -0.5f, -1.0f, -1.5f, -2.0f, -3.0f, -4.0f, -6.0f};
+static float e8m0_scale(uint8_t s) { return s == 0xFF ? 0.0f : ldexpf(1.0f, (int)s - 127); }
+
+void orc_dequantize_row_q8_0(const void *xv, float *y, int64_t k) {
+    const uint8_t *x = (const uint8_t *)xv;
+    for (int64_t i = 0; i < k / 32; i++) {
+        uint16_t dh;
+        memcpy(&dh, x + 34 * i, 2);
+        const float d = orc_fp16_to_fp32(dh);
+        for (int j = 0; j < 32; j++) y[32 * i + j] = d * (float)(int8_t)x[34 * i + 2 + j];
+    }
+}
+
+void orc_dequantize_row_mxfp4(const void *xv, float *y, int64_t k) {
+    const uint8_t *x = (const uint8_t *)xv;
+    for (int64_t i = 0; i < k / 32; i++) {
+        const float scale = e8m0_scale(x[17 * i]);
+        for (int j = 0; j < 16; j++) {
+            const uint8_t b = x[17 * i + 1 + j];
+            y[32 * i + j] = mxfp4_table[b & 0x0F] * scale;
+            y[32 * i + j + 16] = mxfp4_table[b >> 4] * scale;
+        }
+    }
+}
+
+float orc_vec_dot_q8_0_f32(const void *xv, const float *y, int64_t n) {
+    const uint8_t *x = (const uint8_t *)xv;
+    float sumf = 0.0f;
+    for (int64_t i = 0; i < n / 32; i++) {
+        uint16_t dh;
+        memcpy(&dh, x + 34 * i, 2);
+        const float d = orc_fp16_to_fp32(dh);
+        float sum = 0.0f;
+        for (int j = 0; j < 32; j++) {
+            const float w = (float)(int8_t)x[34 * i + 2 + j];
+#if ORC_Q8_0_FMA
+            sum = fmaf(w, y[32 * i + j], sum);
+#else
+            sum = sum + w * y[32 * i + j];
+#endif
+        }
+#if ORC_Q8_0_FMA
+        sumf = fmaf(d, sum, sumf);
+#else
+        sumf = sumf + d * sum;
+#endif
+    }
+    return sumf;
+}
+
+float orc_vec_dot_mxfp4_f32(const void *xv, const float *y, int64_t n) {
+    const uint8_t *x = (const uint8_t *)xv;
+    float sumf = 0.0f;
+    for (int64_t i = 0; i < n / 32; i++) {
+        const float scale = e8m0_scale(x[17 * i]);
+        float sum = 0.0f;
+        for (int j = 0; j < 16; j++) {
+            const uint8_t b = x[17 * i + 1 + j];
+#if ORC_MXFP4_FMA
+            sum = fmaf(mxfp4_table[b & 0x0F], y[32 * i + j], sum);
+            sum = fmaf(mxfp4_table[b >> 4], y[32 * i + j + 16], sum);
+#else
+            sum = sum + mxfp4_table[b & 0x0F] * y[32 * i + j];
+            sum = sum + mxfp4_table[b >> 4] * y[32 * i + j + 16];
+#endif
+        }
+#if ORC_MXFP4_FMA
+        sumf = fmaf(scale, sum, sumf);
+#else
+        sumf = sumf + scale * sum;
+#endif
+    }
+    return sumf;
+}
+
 static void matvec_f32(float *out, const void *mat, int type, const float *x, int M, int K) {
     uint64_t rb = orc_row_bytes(type, K);
     const uint8_t *m = (const uint8_t *)mat;
     for (int i = 0; i < M; i++) {
         const void *row = m + (uint64_t)i * rb;
         out[i] = type == ORC_TYPE_Q4_K ? orc_vec_dot_q4_K_f32(row, x, K)
-               : type == ORC_TYPE_Q5_K ? orc_vec_dot_q5_K_f32(row, x, K) : orc_vec_dot_q6_K_f32(row, x, K);
+               : type == ORC_TYPE_Q5_K ? orc_vec_dot_q5_K_f32(row, x, K)
+               : type == ORC_TYPE_Q8_0 ? orc_vec_dot_q8_0_f32(row, x, K)
+               : type == ORC_TYPE_MXFP4 ? orc_vec_dot_mxfp4_f32(row, x, K) : orc_vec_dot_q6_K_f32(row, x, K);
     }
+}
+
+void orc_mat_vec_mul_f32act(float *out, const void *mat, int type, const float *x, int M, int K) {
+    matvec_f32(out, mat, type, x, M, K);
+}
+
+/* ---- src/inference.c:361-374: the shared expert on fp32 activations, each matrix with its own type ---- */
+void orc_shared_ffn_f32(float *out, const float *h, const void *gate, int gate_type, const void *up, int up_type,
+                        const void *down, int down_type, int n_embd, int inter) {
+    float *g = (float *)malloc(sizeof(float) * (size_t)inter);
+    float *u = (float *)malloc(sizeof(float) * (size_t)inter);
+    matvec_f32(g, gate, gate_type, h, inter, n_embd);
+    for (int r = 0; r < inter; r++) g[r] = g[r] / (1.0f + expf(-g[r]));
+    matvec_f32(u, up, up_type, h, inter, n_embd);
+    for (int r = 0; r < inter; r++) g[r] = g[r] * u[r];
+    matvec_f32(out, down, down_type, g, n_embd, inter);
+    free(g);
+    free(u);
 }
 
 /* ---- src/inference.c:556-575 (routed experts: silu(gate) * up, down, out += score * down; the reference build

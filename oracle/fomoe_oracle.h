@@ -22,6 +22,8 @@ extern "C" {
 #define ORC_TYPE_Q4_K 12 /* include/quant_types.h:56-64 */
 #define ORC_TYPE_Q5_K 13
 #define ORC_TYPE_Q6_K 14
+#define ORC_TYPE_Q8_0 8
+#define ORC_TYPE_MXFP4 39
 
 /* Block layouts, include/quant_types.h:17-41 and include/quant.h:94-98. */
 typedef struct {
@@ -63,6 +65,13 @@ float orc_vec_dot_q6_K_q8_K(const void *x, const void *y, int nb);         /* sr
 /* fp32-activation dots, the reference's second definition of the same products (its CPU forward pass without
  * cpu_expert and, up to summation order, its GPU kernels) */
 float orc_vec_dot_q4_K_f32(const void *x, const float *y, int64_t n);      /* src/quant.c:109-143 */
+void orc_dequantize_row_q8_0(const void *x, float *y, int64_t k);           /* src/quant.c:266-274 */
+void orc_dequantize_row_mxfp4(const void *x, float *y, int64_t k);          /* src/quant.c:299-318 */
+float orc_vec_dot_q8_0_f32(const void *x, const float *y, int64_t n);       /* src/quant.c:276-288 */
+float orc_vec_dot_mxfp4_f32(const void *x, const float *y, int64_t n);      /* src/quant.c:320-337 */
+void orc_mat_vec_mul_f32act(float *out, const void *mat, int type, const float *x, int M, int K); /* src/tensor.c:102-171 */
+void orc_shared_ffn_f32(float *out, const float *h, const void *gate, int gate_type, const void *up, int up_type,
+                        const void *down, int down_type, int n_embd, int inter); /* src/inference.c:361-374 */
 float orc_vec_dot_q5_K_f32(const void *x, const float *y, int64_t n);      /* src/quant.c:249-262 */
 float orc_vec_dot_q6_K_f32(const void *x, const float *y, int64_t n);      /* src/quant.c:177-212 */
 void orc_moe_block_f32(float *out, const float *h, const void *const *experts, const float *scores, int k,

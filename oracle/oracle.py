@@ -20,6 +20,7 @@ ORACLE_SO = os.path.join(_HERE, "libfomoe_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libfomoe_ref.so")
 
 TYPE_F32, TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K = 0, 12, 13, 14
+TYPE_Q8_0, TYPE_MXFP4 = 8, 39
 QK_K = 256
 Q4K_BLOCK, Q5K_BLOCK, Q6K_BLOCK, Q8K_BLOCK = 144, 176, 210, 292
 
@@ -37,6 +38,8 @@ def build(force=False):
 
 
 def row_bytes(qtype, k):
+    if qtype in (TYPE_Q8_0, TYPE_MXFP4):
+        return (k // 32) * (34 if qtype == TYPE_Q8_0 else 17)
     return (k // QK_K) * {TYPE_Q4_K: Q4K_BLOCK, TYPE_Q5_K: Q5K_BLOCK, TYPE_Q6_K: Q6K_BLOCK}[qtype]
 
 
@@ -197,6 +200,34 @@ class Oracle(_Common):
         lib.orc_expert_ffn.argtypes = [_f32p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int, C.c_int,
                                        C.c_uint64, C.c_uint64, C.c_int, C.c_int, _f32p]
         lib.orc_expert_ffn.restype = None
+        lib.orc_mat_vec_mul_f32act.argtypes = [_f32p, C.c_void_p, C.c_int, _f32p, C.c_int, C.c_int]
+        lib.orc_mat_vec_mul_f32act.restype = None
+        lib.orc_shared_ffn_f32.argtypes = [_f32p, _f32p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
+                                           C.c_int, C.c_int]
+        lib.orc_shared_ffn_f32.restype = None
+        for nm in ("orc_dequantize_row_q8_0", "orc_dequantize_row_mxfp4"):
+            getattr(lib, nm).argtypes = [C.c_void_p, _f32p, C.c_int64]
+            getattr(lib, nm).restype = None
+
+    def mat_vec_mul_f32act(self, mat, qtype, x, M, K):
+        """The fp32-activation matvec of src/tensor.c:102-171 for every quantised type, Q8_0 and MXFP4 included."""
+        m, x = _u8(mat), _f32(x)
+        out = np.empty(M, dtype=np.float32)
+        self.lib.orc_mat_vec_mul_f32act(_fp(out), _vp(m), qtype, _fp(x), M, K)
+        return out
+
+    def dequantize32(self, blocks, qtype, k):
+        b = _u8(blocks)
+        y = np.empty(k, dtype=np.float32)
+        getattr(self.lib, "orc_dequantize_row_q8_0" if qtype == TYPE_Q8_0 else "orc_dequantize_row_mxfp4")(_vp(b), _fp(y), k)
+        return y
+
+    def shared_ffn_f32(self, h, gate, gate_type, up, up_type, down, down_type, n_embd, inter):
+        """src/inference.c:361-374 on fp32 activations."""
+        g, u, d = _u8(gate), _u8(up), _u8(down)
+        out = np.empty(n_embd, dtype=np.float32)
+        self.lib.orc_shared_ffn_f32(_fp(out), _fp(_f32(h)), _vp(g), gate_type, _vp(u), up_type, _vp(d), down_type, n_embd, inter)
+        return out
 
     def shared_gate(self, h, w):
         h, w = _f32(h), _f32(w)
@@ -252,6 +283,27 @@ class Ref(_Common):
         lib.refdrv_set_threads.argtypes = [C.c_int]
         lib.fp32_to_fp16.argtypes = [C.c_float]
         lib.fp32_to_fp16.restype = C.c_uint16
+        for nm in ("dequantize_row_q8_0", "dequantize_row_mxfp4"):
+            getattr(lib, nm).argtypes = [C.c_void_p, _f32p, C.c_int64]
+            getattr(lib, nm).restype = None
+
+    def dequantize32(self, blocks, qtype, k):
+        b = _u8(blocks)
+        y = np.empty(k, dtype=np.float32)
+        getattr(self.lib, "dequantize_row_q8_0" if qtype == TYPE_Q8_0 else "dequantize_row_mxfp4")(_vp(b), _fp(y), k)
+        return y
+
+    def shared_ffn_f32(self, h, gate, gate_type, up, up_type, down, down_type, n_embd, inter):
+        """The reference's shared_expert_ffn (src/inference.c:361-374) composed from its own mat_vec_mul: silu, multiply."""
+        g = self.mat_vec_mul_f32act(gate, gate_type, h, inter, n_embd)
+        self.lib.silu.argtypes = [_f32p, C.c_int64]
+        self.lib.silu.restype = None
+        self.lib.vec_mul.argtypes = [_f32p, _f32p, _f32p, C.c_int64]
+        self.lib.vec_mul.restype = None
+        self.lib.silu(_fp(g), inter)
+        u = self.mat_vec_mul_f32act(up, up_type, h, inter, n_embd)
+        self.lib.vec_mul(_fp(g), _fp(g), _fp(u), inter)
+        return self.mat_vec_mul_f32act(down, down_type, g, n_embd, inter)
 
     def write_store(self, path, layers):
         """Write an expert store (.qmoe) with the reference's own writer.  layers: list of (down_type, records),

@@ -86,3 +86,42 @@ def test_matvec_extreme_scales(fb, dec, oracle):
     q4[:, 0:4] = np.frombuffer(np.array([0.02, 0.01], dtype=np.float16).tobytes(), dtype=np.uint8)
     q4[1, 4:] = 0xFF
     assert H.rel_l2(dec.matvec(H.Q4, q4, rows, cols, x), oracle.matvec_q8(q4, H.Q4, x, rows, cols)) < TOL
+
+
+@pytest.mark.parametrize("qtype,rows,cols", [(H.Q8_0, 1024, 4096), (H.MXFP4, 1024, 4096), (H.Q8_0, 7, 96),
+                                              (H.MXFP4, 33, 32), (H.MXFP4, 4096, 1024)])
+def test_blocks32_matvec_f32(fb, oracle, qtype, rows, cols):
+    """Q8_0 / MXFP4 projections on fp32 activations against src/quant.c:276-288, 320-337: fp32 reassociation only
+    (every weight is exact in fp32), so 1e-5 relative L2; special blocks (NaN exponent, smallest exponent, zero
+    scale, extreme quants) included; a matrix already in device memory gives the same bits as a host one."""
+    d = fb.MoeDecoder(1, 256, 256, 4, 1, False, [H.Q4])
+    m = H.blocks32_matrix(qtype, rows, cols, 100 + rows)
+    x = np.random.default_rng(rows).standard_normal(cols).astype(np.float32)
+    got = d.proj_matvec_f32(qtype, m, rows, cols, x)
+    want = oracle.mat_vec_mul_f32act(m, qtype, x, rows, cols)
+    assert np.isfinite(got).all()
+    err = H.rel_l2(got, want)
+    print(f"type {qtype} {rows}x{cols}: rel-L2 {err:.2e}")
+    assert err < 1e-5
+    assert d.status() == 0
+    d.close()
+
+
+def test_shared_ffn_f32_blocks32(fb, oracle):
+    """The reference's shared_expert_ffn (src/inference.c:361-374) with MXFP4 gate/up + Q8_0 down and with Q8_0
+    gate/up + MXFP4 down, at the 397B shared-expert shape."""
+    n_embd, inter = 4096, 1024
+    d = fb.MoeDecoder(1, 256, 256, 4, 1, False, [H.Q4])
+    h = H.hidden(fb, 5, 0, n_embd)
+    for gt, dt in ((H.MXFP4, H.Q8_0), (H.Q8_0, H.MXFP4)):
+        g, u = H.blocks32_matrix(gt, inter, n_embd, 11, special=False), H.blocks32_matrix(gt, inter, n_embd, 12, special=False)
+        dn = H.blocks32_matrix(dt, n_embd, inter, 13, special=False)
+        got = d.shared_ffn_f32(h, g, gt, u, gt, dn, dt, n_embd, inter)
+        want = oracle.shared_ffn_f32(h, g, gt, u, gt, dn, dt, n_embd, inter)
+        err = H.rel_l2(got, want)
+        print(f"shared FFN gate/up type {gt}, down type {dt}: rel-L2 {err:.2e}")
+        assert np.isfinite(got).all() and err < 1e-5
+    with pytest.raises(RuntimeError):                      # K-quant types are not served by this entry
+        d.proj_matvec_f32(H.Q4, np.zeros(144 * 8, dtype=np.uint8), 8, 256, h[:256])
+    d.close()
+

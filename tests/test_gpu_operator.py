@@ -135,3 +135,53 @@ def test_down_type_alternates_without_rebuilding(fb, oracle):
             + 0.2 * oracle.moe_block(h, [e6[1]], one, None, H.Q4, H.Q4, H.Q6, gs, gs, n_embd, inter))
     assert H.rel_l2(eng.result(), want) < 3e-4
     eng.close()
+
+
+@pytest.mark.parametrize("down_type,n", [(H.Q6, 10), (H.Q4, 3)])
+def test_gpu_expert_ffn_q6k_gate_up(fb, oracle, ref, down_type, n):
+    """Q6_K gate and up projections (the reference's kernel for them: src/gpu_kernels.hip:1391) through the operator,
+    against cpu_expert's definition (src/quant.c:478-607 for all three matrices when down is Q6_K too): the oracle
+    and the compiled reference agree bit for bit, the device within the usual bound; mixed gate/up types are refused;
+    a Q4_K call on the same context afterwards still works."""
+    n_embd, inter, seed = 4096, 1024, 67
+    op = fb.GpuOperator()
+    ex = [H.expert_record(fb, seed, 0, e, down_type, n_embd, inter, H.Q6) for e in range(n)]
+    h = H.hidden(fb, seed, 0, n_embd)
+    sc = np.random.default_rng(2).dirichlet(np.ones(n)).astype(np.float32)
+    gs = fb.matrix_bytes(H.Q6, inter, n_embd)
+    assert ex[0].size == 2 * gs + fb.matrix_bytes(down_type, n_embd, inter)
+    rc, out = op.expert_ffn(h, ex, sc, n_embd, inter, gs, gs, ex[0].size, H.Q6, H.Q6, down_type)
+    assert rc == 0
+    want = oracle.moe_block(h, ex, sc, None, H.Q6, H.Q6, down_type, gs, gs, n_embd, inter)
+    assert (H.bits(want) == H.bits(ref.moe_block(h, ex, sc, None, H.Q6, H.Q6, down_type, gs, gs, n_embd, inter))).all()
+    err = H.rel_l2(out, want)
+    print(f"Q6_K gate/up, down type {down_type}, {n} experts: rel-L2 {err:.2e}")
+    assert err < 3e-4
+    rc, _ = op.expert_ffn(h, ex, sc, n_embd, inter, gs, gs, ex[0].size, H.Q6, H.Q4, down_type)
+    assert rc == -1
+    ex4 = _experts(fb, seed, 2, H.Q6, n_embd, inter)
+    g4 = fb.matrix_bytes(H.Q4, inter, n_embd)
+    rc, out4 = op.expert_ffn(h, ex4, sc[:2], n_embd, inter, g4, g4, ex4[0].size, H.Q4, H.Q4, H.Q6)
+    assert rc == 0
+    assert H.rel_l2(out4, oracle.moe_block(h, ex4, sc[:2], None, H.Q4, H.Q4, H.Q6, g4, g4, n_embd, inter)) < 3e-4
+    op.close()
+
+
+def test_expert_engine_twin_changes_gate_type_mid_accumulation(fb, oracle):
+    """cpu_expert_ffn accumulates score * FFN(x) call by call (src/cpu_expert.c:114-115) whatever the experts' types:
+    a Q4_K-gate expert, then a Q6_K-gate expert, then Q4_K again, on one context."""
+    n_embd, inter, seed = 1024, 512, 71
+    eng = fb.ExpertEngine(n_embd, inter)
+    x = H.hidden(fb, seed, 0, n_embd)
+    want = np.zeros(n_embd, dtype=np.float32)
+    eng.reset()
+    for i, (gt, dt, score) in enumerate([(H.Q4, H.Q6, 0.5), (H.Q6, H.Q6, 0.3), (H.Q4, H.Q4, 0.2)]):
+        rec = H.expert_record(fb, seed, 0, i, dt, n_embd, inter, gt)
+        gs = fb.matrix_bytes(gt, inter, n_embd)
+        eng.ffn(rec, x, score, gt, gt, dt, gs, gs)
+        one = oracle.moe_block(x, [rec], np.asarray([score], dtype=np.float32), None, gt, gt, dt, gs, gs, n_embd, inter)
+        want = (want + one).astype(np.float32)
+    got = eng.result()
+    assert H.rel_l2(got, want) < 3e-4
+    eng.close()
+

@@ -156,3 +156,33 @@ def test_q8k_activation_path_differs_from_fp32_path(fb, ref):
     a = ref.matvec_q8(w, H.Q4, x, 64, 4096)
     b = ref.mat_vec_mul_f32act(w, H.Q4, x, 64, 4096)
     assert 1e-4 < H.rel_l2(a, b) < 1e-1
+
+
+@pytest.mark.parametrize("qtype", [H.Q8_0, H.MXFP4])
+def test_blocks32_dequant_and_dot_pin(oracle, ref, qtype):
+    """Q8_0 and MXFP4 (src/quant.c:266-337): dequantised rows and the fp32-activation matvec of the restatement equal
+    the compiled reference bit for bit, special blocks included."""
+    rows, cols = 48, 2048
+    m = H.blocks32_matrix(qtype, rows, cols, 17 + qtype)
+    rb = (cols // 32) * (34 if qtype == H.Q8_0 else 17)
+    for r in (0, 1, rows - 1):
+        a, b = oracle.dequantize32(m[r * rb:(r + 1) * rb], qtype, cols), ref.dequantize32(m[r * rb:(r + 1) * rb], qtype, cols)
+        assert (H.bits(a) == H.bits(b)).all()
+    x = np.random.default_rng(3).standard_normal(cols).astype(np.float32)
+    got, want = oracle.mat_vec_mul_f32act(m, qtype, x, rows, cols), ref.mat_vec_mul_f32act(m, qtype, x, rows, cols)
+    assert (H.bits(got) == H.bits(want)).all()
+    assert np.isfinite(want).all() and np.abs(want).max() > 0
+
+
+def test_shared_ffn_f32_pin(oracle, ref):
+    """The shared expert on fp32 activations (src/inference.c:361-374) with MXFP4 gate/up and Q8_0 down, and the
+    other way round: restatement == the reference's own mat_vec_mul / silu / vec_mul composition, bit for bit."""
+    n_embd, inter = 1024, 512
+    h = np.random.default_rng(9).standard_normal(n_embd).astype(np.float32)
+    for gt, dt in ((H.MXFP4, H.Q8_0), (H.Q8_0, H.MXFP4)):
+        g, u = H.blocks32_matrix(gt, inter, n_embd, 1), H.blocks32_matrix(gt, inter, n_embd, 2)
+        d = H.blocks32_matrix(dt, n_embd, inter, 3)
+        a = oracle.shared_ffn_f32(h, g, gt, u, gt, d, dt, n_embd, inter)
+        b = ref.shared_ffn_f32(h, g, gt, u, gt, d, dt, n_embd, inter)
+        assert (H.bits(a) == H.bits(b)).all() and np.abs(a).max() > 0
+
