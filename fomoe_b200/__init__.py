@@ -82,6 +82,10 @@ _SIGS = {
     "fomoe_b200_proj_matvec_f32": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p, _f32p]),
     "fomoe_b200_shared_ffn_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
                                             C.c_int, C.c_int, _f32p, _f32p]),
+    "fomoe_b200_get_config": (C.c_void_p, [C.c_void_p]),
+    "fomoe_b200_load_gguf": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
+    "fomoe_b200_gguf_tensor": (C.c_int, [C.c_char_p, C.c_char_p, _i32p, C.POINTER(C.c_int64), C.POINTER(C.c_uint64),
+                                         C.c_void_p, C.c_uint64]),
     "fomoe_b200_record_bytes": (C.c_uint64, [C.c_void_p, C.c_int]),
     "fomoe_b200_table_bytes": (C.c_uint64, [C.c_void_p]),
     "fomoe_b200_table_generate": (C.c_int, [C.c_void_p, C.c_uint64]),
@@ -224,6 +228,21 @@ def synth_expert_record(seed, layer, expert, down_type, n_embd, inter, gate_type
                            synth_matrix(seed, layer, expert, M_DOWN, down_type, n_embd, inter)])
 
 
+def gguf_tensor(path, name, read=True):
+    """(ggml type, dims fastest-first, bytes or None) of one tensor of a GGUF file, by the library's own reader; None
+    when the tensor is not there."""
+    t, nb = C.c_int(0), C.c_uint64(0)
+    dims = (C.c_int64 * 4)()
+    if lib().fomoe_b200_gguf_tensor(str(path).encode(), name.encode(), C.byref(t), dims, C.byref(nb), None, 0):
+        return None
+    data = None
+    if read and nb.value:
+        data = np.empty(nb.value, dtype=np.uint8)
+        if lib().fomoe_b200_gguf_tensor(str(path).encode(), name.encode(), None, None, None, data.ctypes.data, nb.value):
+            return None
+    return t.value, [int(d) for d in dims], data
+
+
 class MoeDecoder:
     """Resident expert table + router/CAR + SwiGLU experts + decode stack on one GPU (one TP rank)."""
 
@@ -269,6 +288,13 @@ class MoeDecoder:
         r = np.ascontiguousarray(record).view(np.uint8).reshape(-1)
         assert r.size == self.record_bytes(layer), (r.size, self.record_bytes(layer))
         self._ck(self._l.fomoe_b200_table_upload(self._h, layer, expert, r.ctypes.data), "table_upload")
+
+    def load_gguf(self, path, first_block=0):
+        """Router, experts, shared expert and norm weight of every layer from a GGUF model file; layers loaded."""
+        n = self._l.fomoe_b200_load_gguf(self._h, str(path).encode(), first_block)
+        if n < 0:
+            raise RuntimeError("load_gguf failed (see stderr)")
+        return n
 
     def proj_matvec_f32(self, qtype, w, rows, cols, x):
         """y = W x on fp32 activations, W in 32-value blocks (TYPE_Q8_0 / TYPE_MXFP4), ggml order."""

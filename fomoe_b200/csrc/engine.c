@@ -422,6 +422,7 @@ uint64_t fomoe_b200_record_bytes(fomoe_b200_ctx_t *c, int layer) {
 }
 
 uint64_t fomoe_b200_table_bytes(fomoe_b200_ctx_t *c) { return c ? c->table_bytes : 0; }
+const fomoe_b200_config_t *fomoe_b200_get_config(fomoe_b200_ctx_t *c) { return c ? &c->cfg : NULL; }
 uint64_t fomoe_b200_kernel_launches(fomoe_b200_ctx_t *c) { return c ? c->launches : 0; }
 
 uint64_t fomoe_b200_substitutions(fomoe_b200_ctx_t *c) {

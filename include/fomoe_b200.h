@@ -159,6 +159,22 @@ int fomoe_b200_shared_gate_upload(fomoe_b200_ctx_t *ctx, int layer, const float 
  * first_store_layer + n_layers - 1.  Header and per-layer down types must match the configuration; the shared
  * expert (not part of such files) is left alone.  Returns the number of experts loaded or -1. */
 int fomoe_b200_table_load_qmoe(fomoe_b200_ctx_t *ctx, const char *path, int first_store_layer);
+/* The configuration a context was created with (down_types points at the context's own copy). */
+const fomoe_b200_config_t *fomoe_b200_get_config(fomoe_b200_ctx_t *ctx);
+/* Fill a context from a GGUF model file (the container the reference reads its model from, include/gguf.h:6-145),
+ * blocks first_block .. first_block + n_layers - 1: the router (blk.N.ffn_gate_inp.weight, F32/F16/BF16), the routed
+ * experts cut out of the stacked tensors blk.N.ffn_{gate,up,down}_exps.weight (as tools/prepare_experts.c:262-291
+ * cuts them into .qmoe records; types and shapes must be the context's), the shared expert
+ * (blk.N.ffn_{gate,up,down}_shexp.weight, when it is stored in the experts' formats) with its optional scalar gate
+ * (blk.N.ffn_gate_inp_shexp.weight), and the RMSNorm weight in front of the block (blk.N.post_attention_norm.weight
+ * or blk.N.ffn_norm.weight, src/model.c:277-283).  One file (no -0000i-of-N splits).  Returns the number of layers
+ * loaded or -1 (reason on stderr). */
+int fomoe_b200_load_gguf(fomoe_b200_ctx_t *ctx, const char *path, int first_block);
+/* Host-only look-up in a GGUF file (no GPU involved): type (ggml id), dims[4] (fastest first, unused = 1) and byte
+ * size of tensor `name`; with buf != NULL its bytes as well.  0, or -1 when the file or the tensor is not there, the
+ * type is one this library has no use for, or buf is too small. */
+int fomoe_b200_gguf_tensor(const char *path, const char *name, int *type, int64_t *dims, uint64_t *nbytes, void *buf,
+                           uint64_t buf_bytes);
 /* Read this rank's shard of one matrix (0 gate, 1 up, 2 down) back in ggml order / as fp32. */
 int fomoe_b200_table_export(fomoe_b200_ctx_t *ctx, int layer, int expert, int matrix, void *ggml_out);
 int fomoe_b200_table_dequant(fomoe_b200_ctx_t *ctx, int layer, int expert, int matrix, float *out);

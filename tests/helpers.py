@@ -115,3 +115,83 @@ def blocks32_matrix(qtype, rows, cols, seed, special=True):
             m[1 % rows, 1 % nb, 0] = 0
     return m.reshape(-1)
 
+
+def write_gguf(path, kvs, tensors, alignment=32, version=3):
+    """A GGUF file (the container of include/gguf.h:6-145 of the reference, format version 3): kvs = [(key, type id,
+    value)] with type ids 4 u32, 5 i32, 6 f32, 8 string, 9 (element type id, list); tensors = [(name, dims fastest
+    first, ggml type id, bytes)].  general.alignment is written when it differs from 32."""
+    import struct
+
+    def gstr(s):
+        b = s.encode()
+        return struct.pack("<Q", len(b)) + b
+
+    def scalar(t, v):
+        return {4: lambda: struct.pack("<I", v), 5: lambda: struct.pack("<i", v), 6: lambda: struct.pack("<f", v),
+                10: lambda: struct.pack("<Q", v), 7: lambda: struct.pack("<B", int(v)), 8: lambda: gstr(v)}[t]()
+
+    kvs = list(kvs)
+    if alignment != 32:
+        kvs.append(("general.alignment", 4, alignment))
+    out = struct.pack("<IIQQ", 0x46554747, version, len(tensors), len(kvs))
+    for key, t, v in kvs:
+        out += gstr(key) + struct.pack("<I", t)
+        if t == 9:
+            et, items = v
+            out += struct.pack("<IQ", et, len(items)) + b"".join(scalar(et, x) for x in items)
+        else:
+            out += scalar(t, v)
+    offs, off = [], 0
+    for _, _, _, data in tensors:
+        offs.append(off)
+        off = (off + len(data) + alignment - 1) // alignment * alignment
+    for (name, dims, ttype, _), o in zip(tensors, offs):
+        out += gstr(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims)
+        out += struct.pack("<IQ", ttype, o)
+    out += b"\0" * ((len(out) + alignment - 1) // alignment * alignment - len(out))
+    with open(path, "wb") as f:
+        f.write(out)
+        for (_, _, _, data), o in zip(tensors, offs):
+            f.write(bytes(data))
+            pad = (len(data) + alignment - 1) // alignment * alignment - len(data)
+            f.write(b"\0" * pad)
+
+
+def moe_gguf(fb, path, seed, n_layers, n_embd, inter, n_experts, down_types, shared=True, first_block=0, gate_type=12,
+             router_type=0, alignment=32):
+    """A model file holding the MoE tensors of `n_layers` blocks, generated from `seed` like the library's table."""
+    tensors = []
+    for l in range(n_layers):
+        b = first_block + l
+        recs = [expert_record(fb, seed, l, e, down_types[l], n_embd, inter, gate_type) for e in range(n_experts + (1 if shared else 0))]
+        gs = fb.matrix_bytes(gate_type, inter, n_embd)
+        w = router_weights(fb, seed, l, n_experts, n_embd)
+        if router_type == 1:
+            wb = w.astype(np.float16).tobytes()
+        elif router_type == 30:
+            wb = (w.view(np.uint32) >> 16).astype(np.uint16).tobytes()
+        else:
+            wb = w.tobytes()
+        tensors.append((f"blk.{b}.ffn_gate_inp.weight", [n_embd, n_experts], router_type, wb))
+        tensors.append((f"blk.{b}.ffn_gate_exps.weight", [n_embd, inter, n_experts], gate_type,
+                        b"".join(r[:gs].tobytes() for r in recs[:n_experts])))
+        tensors.append((f"blk.{b}.ffn_up_exps.weight", [n_embd, inter, n_experts], gate_type,
+                        b"".join(r[gs:2 * gs].tobytes() for r in recs[:n_experts])))
+        tensors.append((f"blk.{b}.ffn_down_exps.weight", [inter, n_embd, n_experts], down_types[l],
+                        b"".join(r[2 * gs:].tobytes() for r in recs[:n_experts])))
+        if shared:
+            r = recs[n_experts]
+            tensors.append((f"blk.{b}.ffn_gate_shexp.weight", [n_embd, inter], gate_type, r[:gs].tobytes()))
+            tensors.append((f"blk.{b}.ffn_up_shexp.weight", [n_embd, inter], gate_type, r[gs:2 * gs].tobytes()))
+            tensors.append((f"blk.{b}.ffn_down_shexp.weight", [inter, n_embd], down_types[l], r[2 * gs:].tobytes()))
+        _, normw = glue(fb, seed, l, n_embd)
+        tensors.append((f"blk.{b}.post_attention_norm.weight" if l % 2 == 0 else f"blk.{b}.ffn_norm.weight", [n_embd], 0,
+                        normw.tobytes()))
+        tensors.append((f"blk.{b}.attn_q.weight", [n_embd, 64], 1, np.zeros(n_embd * 64, dtype=np.float16).tobytes()))
+    kvs = [("general.architecture", 8, "qwen3moe"), ("qwen3moe.block_count", 4, n_layers + first_block),
+           ("qwen3moe.expert_count", 4, n_experts), ("qwen3moe.attention.layer_norm_rms_epsilon", 6, 1e-6),
+           ("tokenizer.ggml.tokens", 9, (8, ["<s>", "</s>", "a", "b"])), ("tokenizer.ggml.token_type", 9, (5, [1, 1, 0, 0])),
+           ("general.file_type", 4, 15), ("some.flag", 7, True), ("some.big", 10, 1 << 40)]
+    write_gguf(path, kvs, tensors, alignment=alignment)
+    return tensors
+
