@@ -40,7 +40,7 @@ class Config(C.Structure):
 class BatchConfig(C.Structure):
     _fields_ = [("device", C.c_int), ("n_layers", C.c_int), ("n_embd", C.c_int), ("n_inter", C.c_int),
                 ("n_experts", C.c_int), ("top_k", C.c_int), ("has_shared", C.c_int), ("max_tokens", C.c_int),
-                ("rms_eps", C.c_float)]
+                ("rms_eps", C.c_float), ("tp_rank", C.c_int), ("tp_size", C.c_int)]
 
 
 class Work(C.Structure):
@@ -86,6 +86,7 @@ _SIGS = {
     "fomoe_b200_load_gguf": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
     "fomoe_b200_gguf_tensor": (C.c_int, [C.c_char_p, C.c_char_p, _i32p, C.POINTER(C.c_int64), C.POINTER(C.c_uint64),
                                          C.c_void_p, C.c_uint64]),
+    "fomoe_b200_batch_set_allreduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "fomoe_b200_record_bytes": (C.c_uint64, [C.c_void_p, C.c_int]),
     "fomoe_b200_table_bytes": (C.c_uint64, [C.c_void_p]),
     "fomoe_b200_table_generate": (C.c_int, [C.c_void_p, C.c_uint64]),
@@ -666,11 +667,13 @@ class BatchedMoe:
     """Many tokens per call (prefill / batched decode): routed-expert FFN on the tensor cores, Q4_K experts."""
 
     def __init__(self, n_layers, n_embd, n_inter, n_experts, top_k, has_shared=True, max_tokens=512, device=0,
-                 rms_eps=1e-6):
+                 rms_eps=1e-6, tp_rank=0, tp_size=1):
         self._l = lib()
         self.n_layers, self.n_embd, self.n_inter = n_layers, n_embd, n_inter
         self.n_experts, self.top_k, self.has_shared, self.max_tokens = n_experts, top_k, bool(has_shared), max_tokens
-        cfg = BatchConfig(device, n_layers, n_embd, n_inter, n_experts, top_k, int(bool(has_shared)), max_tokens, rms_eps)
+        self.tp_rank, self.tp_size, self._hook = tp_rank, tp_size, None
+        cfg = BatchConfig(device, n_layers, n_embd, n_inter, n_experts, top_k, int(bool(has_shared)), max_tokens, rms_eps,
+                          tp_rank, tp_size)
         self._h = self._l.fomoe_b200_batch_create(C.byref(cfg))
         if not self._h:
             raise RuntimeError("fomoe_b200_batch_create failed (no CUDA device, unsupported shape or out of memory)")
@@ -687,7 +690,22 @@ class BatchedMoe:
             raise RuntimeError(f"{what}: {self._l.fomoe_b200_batch_last_error(self._h).decode()}")
 
     def record_bytes(self):
+        """Bytes of a whole expert record in ggml order (what upload_expert takes)."""
         return 2 * matrix_bytes(TYPE_Q4_K, self.n_inter, self.n_embd) + matrix_bytes(TYPE_Q4_K, self.n_embd, self.n_inter)
+
+    def shard_bytes(self):
+        """Bytes of this rank's shard of a record (what export_expert returns: gate rows | up rows | down columns)."""
+        return self.record_bytes() // self.tp_size
+
+    def set_allreduce(self, fn):
+        """fn(ptr, n, stream) -> 0: sums the n floats at device pointer ptr over the ranks, in place, on that stream."""
+        if fn is None:
+            self._hook = None
+            self._ck(self._l.fomoe_b200_batch_set_allreduce(self._h, None, None), "set_allreduce")
+            return
+        proto = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p)
+        self._hook = proto(lambda user, ptr, n, stream: int(fn(ptr, n, stream) or 0))
+        self._ck(self._l.fomoe_b200_batch_set_allreduce(self._h, self._hook, None), "set_allreduce")
 
     def table_bytes(self):
         return int(self._l.fomoe_b200_batch_table_bytes(self._h))
@@ -707,7 +725,7 @@ class BatchedMoe:
         self._ck(self._l.fomoe_b200_batch_upload(self._h, layer, expert, r.ctypes.data), "batch_upload")
 
     def export_expert(self, layer, expert):
-        out = np.empty(self.record_bytes(), dtype=np.uint8)
+        out = np.empty(self.shard_bytes(), dtype=np.uint8)
         self._ck(self._l.fomoe_b200_batch_export(self._h, layer, expert, out.ctypes.data), "batch_export")
         return out
 

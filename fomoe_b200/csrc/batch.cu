@@ -70,8 +70,10 @@ __device__ __forceinline__ uint8_t *kb_unit(uint8_t *mat, int K, int row, int kb
     return mat + ((uint64_t)(row >> 7) * (K / 256) + kb) * KB_TILE_BYTES;
 }
 
+/* A shard of a matrix: local block (row, kb) is block (row0 + row, kb0 + kb) of the full matrix, whose rows hold
+ * bpr_full blocks; the synthetic generator and the ggml source are indexed by the full matrix's block number. */
 __global__ void k_kb_gen(uint8_t *dst0, uint64_t rec_bytes, uint64_t mat_off, int M, int K, uint64_t seed, uint32_t layer,
-                         uint32_t matrix) {
+                         uint32_t matrix, int row0, int bpr_full, int kb0) {
     const uint32_t e = blockIdx.y;
     uint8_t *mat = dst0 + (uint64_t)e * rec_bytes + mat_off;
     const uint64_t key = fsyn_key(seed, layer, e, matrix);
@@ -79,19 +81,19 @@ __global__ void k_kb_gen(uint8_t *dst0, uint64_t rec_bytes, uint64_t mat_off, in
     for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < n; b += gridDim.x * blockDim.x) {
         const int row = b / bpr, kb = b - row * bpr;
         uint32_t w[36];
-        fsyn_q4k_block(key, (uint64_t)b, w);
+        fsyn_q4k_block(key, (uint64_t)(row0 + row) * bpr_full + (kb0 + kb), w);
         uint4 *u = reinterpret_cast<uint4 *>(kb_unit(mat, K, row, kb)) + (row & 127);
 #pragma unroll
         for (int p = 0; p < 9; p++) u[128 * p] = make_uint4(w[4 * p], w[4 * p + 1], w[4 * p + 2], w[4 * p + 3]);
     }
 }
 
-__global__ void k_kb_repack(uint8_t *mat, const uint8_t *src, int M, int K, int to_ggml) {
+__global__ void k_kb_repack(uint8_t *mat, const uint8_t *src, int M, int K, int to_ggml, int row0, int bpr_full, int kb0) {
     const int bpr = K / 256, n = M * bpr;
     for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < n; b += gridDim.x * blockDim.x) {
         const int row = b / bpr, kb = b - row * bpr;
         uint4 *u = reinterpret_cast<uint4 *>(kb_unit(mat, K, row, kb)) + (row & 127);
-        uint4 *g = reinterpret_cast<uint4 *>(const_cast<uint8_t *>(src) + (uint64_t)b * 144);
+        uint4 *g = reinterpret_cast<uint4 *>(const_cast<uint8_t *>(src) + ((uint64_t)(row0 + row) * bpr_full + (kb0 + kb)) * 144);
         for (int p = 0; p < 9; p++) {
             if (to_ggml) g[p] = u[128 * p];
             else u[128 * p] = g[p];
@@ -994,6 +996,22 @@ __global__ void __launch_bounds__(KB_THREADS, 1) k_kb_gateup(kb_gemm_args_t P) {
     }
 }
 
+/* x += y (the block output after the ranks' partial outputs have been summed) */
+__global__ void k_kb_add(float *x, const float *y, uint64_t n4) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n4; i += (uint64_t)gridDim.x * blockDim.x) {
+        float4 a = reinterpret_cast<float4 *>(x)[i];
+        const float4 b = reinterpret_cast<const float4 *>(y)[i];
+        a.x = __fadd_rn(a.x, b.x); a.y = __fadd_rn(a.y, b.y); a.z = __fadd_rn(a.z, b.z); a.w = __fadd_rn(a.w, b.w);
+        reinterpret_cast<float4 *>(x)[i] = a;
+    }
+}
+
+extern "C" int kb_launch_add(float *x, const float *y, uint64_t n, void *stream) {
+    const uint64_t n4 = n / 4, g = (n4 + 255) / 256;
+    k_kb_add<<<(int)(g > 1184 ? 1184 : (g < 1 ? 1 : g)), 256, 0, (cudaStream_t)stream>>>(x, y, n4);
+    return (int)cudaGetLastError();
+}
+
 /* ------------------------------------------------------------------ combine */
 __global__ void k_kb_combine(const float *dots, const float *scores, int n_tokens, int n_embd, int top_k, int has_shared,
                              float *out, float *x) {
@@ -1010,22 +1028,22 @@ __global__ void k_kb_combine(const float *dots, const float *scores, int n_token
 
 /* ------------------------------------------------------------------ launchers */
 extern "C" int kb_launch_gen(uint8_t *dst, uint64_t rec_bytes, int n_recs, uint64_t mat_off, int M, int K, uint64_t seed,
-                             uint32_t layer, uint32_t matrix, void *stream) {
+                             uint32_t layer, uint32_t matrix, int row0, int bpr_full, int kb0, void *stream) {
     const int n = M * (K / 256);
     dim3 grid((n + 127) / 128 > 256 ? 256 : (n + 127) / 128, n_recs);
-    k_kb_gen<<<grid, 128, 0, (cudaStream_t)stream>>>(dst, rec_bytes, mat_off, M, K, seed, layer, matrix);
+    k_kb_gen<<<grid, 128, 0, (cudaStream_t)stream>>>(dst, rec_bytes, mat_off, M, K, seed, layer, matrix, row0, bpr_full, kb0);
     return (int)cudaGetLastError();
 }
 
-extern "C" int kb_launch_repack(uint8_t *dst, const uint8_t *src_ggml, int M, int K, void *stream) {
+extern "C" int kb_launch_repack(uint8_t *dst, const uint8_t *src_ggml, int M, int K, int row0, int bpr_full, int kb0, void *stream) {
     const int n = M * (K / 256);
-    k_kb_repack<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(dst, src_ggml, M, K, 0);
+    k_kb_repack<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(dst, src_ggml, M, K, 0, row0, bpr_full, kb0);
     return (int)cudaGetLastError();
 }
 
 extern "C" int kb_launch_export(uint8_t *dst_ggml, const uint8_t *src, int M, int K, void *stream) {
     const int n = M * (K / 256);
-    k_kb_repack<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(const_cast<uint8_t *>(src), dst_ggml, M, K, 1);
+    k_kb_repack<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(const_cast<uint8_t *>(src), dst_ggml, M, K, 1, 0, K / 256, 0);
     return (int)cudaGetLastError();
 }
 

@@ -21,7 +21,12 @@ struct fomoe_b200_batch {
     int n_sm;
     cudaStream_t stream;
     cudaEvent_t ev0, ev1;
-    uint64_t mat_gu, mat_dn, rec_bytes, table_bytes; /* bytes of a gate (or up) matrix, a down matrix, a record */
+    int il, tp_rank, tp_size;  /* this rank's share of the intermediate dimension: rows of gate/up, columns of down */
+    uint64_t mat_gu, mat_dn, rec_bytes, table_bytes; /* bytes of this rank's gate (or up) shard, down shard, record */
+    uint64_t full_gu, full_dn;  /* the same for the whole matrices: a ggml record is 2 full_gu + full_dn */
+    float *part;               /* [max_tokens][n_embd]: this rank's partial block output (tensor parallel only) */
+    fomoe_b200_allreduce_fn allreduce;
+    void *allreduce_user;
     uint8_t **table;       /* per layer: (n_experts + has_shared) records gate | up | down, batched layout */
     float **resid, **normw;
     float *logits;         /* [n_layers][max_tokens][n_experts] or NULL */
@@ -77,7 +82,7 @@ void fomoe_b200_batch_destroy(fomoe_b200_batch_t *b) {
     cudaFree(b->logits); cudaFree(b->x); cudaFree(b->h); cudaFree(b->lg); cudaFree(b->scores); cudaFree(b->act);
     cudaFree(b->dots); cudaFree(b->xs_h); cudaFree(b->xs_a); cudaFree(b->bs_h); cudaFree(b->xh_h); cudaFree(b->xh_a); cudaFree(b->ids);
     cudaFree(b->counts); cudaFree(b->pairs); cudaFree(b->n_items); cudaFree(b->status); cudaFree(b->items_gu);
-    cudaFree(b->items_dn); cudaFree(b->stage); cudaFree(b->prof);
+    cudaFree(b->items_dn); cudaFree(b->stage); cudaFree(b->prof); cudaFree(b->part);
     if (b->ev0) cudaEventDestroy(b->ev0);
     if (b->ev1) cudaEventDestroy(b->ev1);
     if (b->stream) cudaStreamDestroy(b->stream);
@@ -103,17 +108,25 @@ fomoe_b200_batch_t *fomoe_b200_batch_create(const fomoe_b200_batch_config_t *cfg
     if (cfg->device < 0 || cfg->device >= ndev || cfg->n_layers < 1 || cfg->n_embd % 256 || cfg->n_embd < 256 ||
         cfg->n_embd > 8192 || cfg->n_embd % KB_TILE_M || cfg->n_inter % 256 || cfg->n_inter < 256 || cfg->n_inter > 8192 ||
         cfg->n_experts < 1 || cfg->n_experts > 512 || cfg->top_k < 1 || cfg->top_k > 16 || cfg->top_k > cfg->n_experts ||
-        cfg->max_tokens < 1) {
+        cfg->max_tokens < 1 || cfg->tp_size < 0 || cfg->tp_size > 8 || cfg->tp_rank < 0 ||
+        cfg->tp_rank >= (cfg->tp_size ? cfg->tp_size : 1) || cfg->n_inter % (256 * (cfg->tp_size ? cfg->tp_size : 1))) {
         berr(b, "unsupported configuration");
         free(b);
         return NULL;
     }
-    const int nl = cfg->n_layers, ne = cfg->n_embd, ni = cfg->n_inter, T = cfg->max_tokens;
+    /* tensor parallel: rank r of N owns gate/up rows [r I/N, (r+1) I/N) and the same columns of down, whole 256-wide
+     * activation windows, exactly as the decode path shards (src/tp.hip:85-124 sums the ranks' outputs) */
+    b->tp_size = cfg->tp_size ? cfg->tp_size : 1;
+    b->tp_rank = cfg->tp_rank;
+    b->il = cfg->n_inter / b->tp_size;
+    const int nl = cfg->n_layers, ne = cfg->n_embd, ni = b->il, T = cfg->max_tokens;
     const int nrec = cfg->n_experts + (cfg->has_shared ? 1 : 0);
     const uint64_t npairs = (uint64_t)T * cfg->top_k + (cfg->has_shared ? T : 0);
     b->mat_gu = (uint64_t)ni * (ne / 256) * 144;
     b->mat_dn = (uint64_t)ne * (ni / 256) * 144;
     b->rec_bytes = 2 * b->mat_gu + b->mat_dn;
+    b->full_gu = b->mat_gu * (uint64_t)b->tp_size;
+    b->full_dn = b->mat_dn * (uint64_t)b->tp_size;
     if (cudaSetDevice(cfg->device) != cudaSuccess) goto fail;
     {
         struct cudaDeviceProp prop;
@@ -147,7 +160,8 @@ fomoe_b200_batch_t *fomoe_b200_batch_create(const fomoe_b200_batch_config_t *cfg
         balloc(b, (void **)&b->n_items, sizeof(int) * 2) || balloc(b, (void **)&b->status, sizeof(int)) ||
         balloc(b, (void **)&b->items_gu, sizeof(kb_item_t) * max_chunks_gu * (ni / KB_TILE_M)) ||
         balloc(b, (void **)&b->items_dn, sizeof(kb_item_t) * max_chunks * (ne / KB_TILE_M)) ||
-        balloc(b, (void **)&b->stage, b->rec_bytes))
+        balloc(b, (void **)&b->stage, 2 * b->full_gu + b->full_dn) ||
+        (b->tp_size > 1 && balloc(b, (void **)&b->part, sizeof(float) * (uint64_t)T * ne)))
         goto fail;
     if (ni % KB_TILE_M) goto fail;
     return b;
@@ -177,9 +191,10 @@ int fomoe_b200_batch_generate(fomoe_b200_batch_t *b, uint64_t seed, int with_log
     const fomoe_b200_batch_config_t *c = &b->cfg;
     const int nrec = c->n_experts + (c->has_shared ? 1 : 0);
     for (int l = 0; l < c->n_layers; l++) {
-        BCKL(b, kb_launch_gen(b->table[l], b->rec_bytes, nrec, 0, c->n_inter, c->n_embd, seed, (uint32_t)l, FSYN_M_GATE, b->stream));
-        BCKL(b, kb_launch_gen(b->table[l], b->rec_bytes, nrec, b->mat_gu, c->n_inter, c->n_embd, seed, (uint32_t)l, FSYN_M_UP, b->stream));
-        BCKL(b, kb_launch_gen(b->table[l], b->rec_bytes, nrec, 2 * b->mat_gu, c->n_embd, c->n_inter, seed, (uint32_t)l, FSYN_M_DOWN, b->stream));
+        const int row0 = b->tp_rank * b->il, kb0 = b->tp_rank * (b->il / 256);
+        BCKL(b, kb_launch_gen(b->table[l], b->rec_bytes, nrec, 0, b->il, c->n_embd, seed, (uint32_t)l, FSYN_M_GATE, row0, c->n_embd / 256, 0, b->stream));
+        BCKL(b, kb_launch_gen(b->table[l], b->rec_bytes, nrec, b->mat_gu, b->il, c->n_embd, seed, (uint32_t)l, FSYN_M_UP, row0, c->n_embd / 256, 0, b->stream));
+        BCKL(b, kb_launch_gen(b->table[l], b->rec_bytes, nrec, 2 * b->mat_gu, c->n_embd, b->il, seed, (uint32_t)l, FSYN_M_DOWN, 0, c->n_inter / 256, kb0, b->stream));
         BCKL(b, kb_launch_gen_f32(b->resid[l], (uint64_t)c->n_embd, seed, (uint32_t)l, FSYN_M_RESID, 0.0f, FOMOE_RESID_STD, b->stream));
         BCKL(b, kb_launch_gen_f32(b->normw[l], (uint64_t)c->n_embd, seed, (uint32_t)l, FSYN_M_NORMW, FOMOE_NORMW_MEAN, FOMOE_NORMW_STD, b->stream));
     }
@@ -199,10 +214,12 @@ int fomoe_b200_batch_upload(fomoe_b200_batch_t *b, int layer, int expert, const 
         return -1;
     BCK(b, cudaSetDevice(b->cfg.device));
     uint8_t *dst = b->table[layer] + (uint64_t)expert * b->rec_bytes;
-    BCK(b, cudaMemcpyAsync(b->stage, record, b->rec_bytes, cudaMemcpyDefault, b->stream));
-    BCKL(b, kb_launch_repack(dst, b->stage, b->cfg.n_inter, b->cfg.n_embd, b->stream));
-    BCKL(b, kb_launch_repack(dst + b->mat_gu, b->stage + b->mat_gu, b->cfg.n_inter, b->cfg.n_embd, b->stream));
-    BCKL(b, kb_launch_repack(dst + 2 * b->mat_gu, b->stage + 2 * b->mat_gu, b->cfg.n_embd, b->cfg.n_inter, b->stream));
+    /* the whole ggml record is staged; this rank's rows (gate, up) and column blocks (down) are cut out of it */
+    const int row0 = b->tp_rank * b->il, kb0 = b->tp_rank * (b->il / 256);
+    BCK(b, cudaMemcpyAsync(b->stage, record, 2 * b->full_gu + b->full_dn, cudaMemcpyDefault, b->stream));
+    BCKL(b, kb_launch_repack(dst, b->stage, b->il, b->cfg.n_embd, row0, b->cfg.n_embd / 256, 0, b->stream));
+    BCKL(b, kb_launch_repack(dst + b->mat_gu, b->stage + b->full_gu, b->il, b->cfg.n_embd, row0, b->cfg.n_embd / 256, 0, b->stream));
+    BCKL(b, kb_launch_repack(dst + 2 * b->mat_gu, b->stage + 2 * b->full_gu, b->cfg.n_embd, b->il, 0, b->cfg.n_inter / 256, kb0, b->stream));
     BCK(b, cudaStreamSynchronize(b->stream));
     return 0;
 }
@@ -213,9 +230,9 @@ int fomoe_b200_batch_export(fomoe_b200_batch_t *b, int layer, int expert, void *
         return -1;
     BCK(b, cudaSetDevice(b->cfg.device));
     const uint8_t *src = b->table[layer] + (uint64_t)expert * b->rec_bytes;
-    BCKL(b, kb_launch_export(b->stage, src, b->cfg.n_inter, b->cfg.n_embd, b->stream));
-    BCKL(b, kb_launch_export(b->stage + b->mat_gu, src + b->mat_gu, b->cfg.n_inter, b->cfg.n_embd, b->stream));
-    BCKL(b, kb_launch_export(b->stage + 2 * b->mat_gu, src + 2 * b->mat_gu, b->cfg.n_embd, b->cfg.n_inter, b->stream));
+    BCKL(b, kb_launch_export(b->stage, src, b->il, b->cfg.n_embd, b->stream));
+    BCKL(b, kb_launch_export(b->stage + b->mat_gu, src + b->mat_gu, b->il, b->cfg.n_embd, b->stream));
+    BCKL(b, kb_launch_export(b->stage + 2 * b->mat_gu, src + 2 * b->mat_gu, b->cfg.n_embd, b->il, b->stream));
     BCK(b, cudaMemcpyAsync(record_out, b->stage, b->rec_bytes, cudaMemcpyDeviceToHost, b->stream));
     BCK(b, cudaStreamSynchronize(b->stream));
     return 0;
@@ -225,7 +242,7 @@ int fomoe_b200_batch_export(fomoe_b200_batch_t *b, int layer, int expert, void *
  * output in `out_dev` (may be NULL) and adds it to `x_dev` (may be NULL) */
 static int enqueue_layer(fomoe_b200_batch_t *b, int layer, int T, const float *lg, float *out_dev, float *x_dev) {
     const fomoe_b200_batch_config_t *c = &b->cfg;
-    const int m_gu = c->n_inter / KB_TILE_M, m_dn = c->n_embd / KB_TILE_M;
+    const int m_gu = b->il / KB_TILE_M, m_dn = c->n_embd / KB_TILE_M;
     BCKL(b, kb_launch_route(lg, T, c->n_experts, c->top_k, b->ids, b->scores, b->status, b->stream));
     BCKL(b, kb_launch_bucket(b->ids, T, c->n_experts, c->top_k, c->has_shared, m_gu, m_dn, b->counts, b->pairs, b->items_gu,
                              b->n_items, b->items_dn, b->n_items + 1, b->stream));
@@ -241,7 +258,7 @@ static int enqueue_layer(fomoe_b200_batch_t *b, int layer, int T, const float *l
     /* gate + up + SwiGLU */
     a.mat_off[0] = 0;
     a.mat_off[1] = b->mat_gu;
-    a.M = c->n_inter;
+    a.M = b->il;
     a.K = c->n_embd;
     a.xh = b->xh_h;
     a.xscale = b->xs_h;
@@ -252,12 +269,12 @@ static int enqueue_layer(fomoe_b200_batch_t *b, int layer, int T, const float *l
     a.out = b->act;
     BCKL(b, kb_launch_gateup(&a, b->n_sm, b->stream));
     const int npairs = T * c->top_k + (c->has_shared ? T : 0);
-    BCKL(b, kb_launch_quant(b->act, npairs, c->n_inter, 0, b->xh_a, b->xs_a, NULL, b->stream));
+    BCKL(b, kb_launch_quant(b->act, npairs, b->il, 0, b->xh_a, b->xs_a, NULL, b->stream));
     /* down */
     a.mat_off[0] = 2 * b->mat_gu;
     a.mat_off[1] = 0;
     a.M = c->n_embd;
-    a.K = c->n_inter;
+    a.K = b->il;
     a.xh = b->xh_a;
     a.xscale = b->xs_a;
     a.xbs = NULL;
@@ -266,7 +283,27 @@ static int enqueue_layer(fomoe_b200_batch_t *b, int layer, int T, const float *l
     a.n_items = b->n_items + 1;
     a.out = b->dots;
     BCKL(b, kb_launch_down(&a, b->n_sm, b->stream));
-    BCKL(b, kb_launch_combine(b->dots, b->scores, T, c->n_embd, c->top_k, c->has_shared, out_dev, x_dev, b->stream));
+    if (b->tp_size == 1) {
+        BCKL(b, kb_launch_combine(b->dots, b->scores, T, c->n_embd, c->top_k, c->has_shared, out_dev, x_dev, b->stream));
+        return 0;
+    }
+    /* tensor parallel: this rank's partial block output, summed over the ranks by the caller's collective (in place,
+     * on this stream), then handed on.  Without a collective installed the partial itself is the result. */
+    BCKL(b, kb_launch_combine(b->dots, b->scores, T, c->n_embd, c->top_k, c->has_shared, b->part, NULL, b->stream));
+    const uint64_t n = (uint64_t)T * c->n_embd;
+    if (b->allreduce && b->allreduce(b->allreduce_user, b->part, (int)n, (void *)b->stream)) {
+        berr(b, "the caller's all-reduce reported a failure at layer %d", layer);
+        return -1;
+    }
+    if (out_dev) BCK(b, cudaMemcpyAsync(out_dev, b->part, sizeof(float) * n, cudaMemcpyDeviceToDevice, b->stream));
+    if (x_dev) BCKL(b, kb_launch_add(x_dev, b->part, n, b->stream));
+    return 0;
+}
+
+int fomoe_b200_batch_set_allreduce(fomoe_b200_batch_t *b, fomoe_b200_allreduce_fn fn, void *user) {
+    if (!b) return -1;
+    b->allreduce = fn;
+    b->allreduce_user = user;
     return 0;
 }
 

@@ -58,9 +58,11 @@ typedef struct {
     unsigned long long *prof;
 } kb_gemm_args_t;
 
+/* M x K is this rank's shard: rows row0.. and 256-column blocks kb0.. of a matrix whose rows hold bpr_full blocks */
 int kb_launch_gen(uint8_t *dst, uint64_t rec_bytes, int n_recs, uint64_t mat_off, int M, int K, uint64_t seed,
-                  uint32_t layer, uint32_t matrix, void *stream);
-int kb_launch_repack(uint8_t *dst, const uint8_t *src_ggml, int M, int K, void *stream);
+                  uint32_t layer, uint32_t matrix, int row0, int bpr_full, int kb0, void *stream);
+int kb_launch_repack(uint8_t *dst, const uint8_t *src_ggml_full, int M, int K, int row0, int bpr_full, int kb0, void *stream);
+int kb_launch_add(float *x, const float *y, uint64_t n, void *stream);
 int kb_launch_export(uint8_t *dst_ggml, const uint8_t *src, int M, int K, void *stream);
 
 /* x += resid (optional); h = rmsnorm(x) * normw (optional: else h = x); Q8_K of h per 256 (src/quant.c:343-375) written as

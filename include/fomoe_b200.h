@@ -333,6 +333,9 @@ typedef struct {
     int has_shared;
     int max_tokens;  /* tokens per call, at most */
     float rms_eps;
+    int tp_rank;     /* tensor parallel over the intermediate dimension, as the decode path shards it: rank r of */
+    int tp_size;     /* tp_size (0 = 1; n_inter a multiple of 256 tp_size) holds rows [r I/N, (r+1) I/N) of gate and up
+                        and the same columns of down */
 } fomoe_b200_batch_config_t;
 
 fomoe_b200_batch_t *fomoe_b200_batch_create(const fomoe_b200_batch_config_t *cfg);
@@ -363,6 +366,13 @@ int fomoe_b200_batch_get_routing(fomoe_b200_batch_t *b, int n_tokens, int *ids, 
 /* Profiling aid: on = 1 starts counting the clock cycles block 0 of the two grouped-GEMM kernels spends waiting, per
  * role; on = 0 copies the 16 counters out (0..7 down pass, 8..15 gate/up pass: copy thread, producers x3, MMA thread
  * x2, epilogue, the block's whole run time) and stops. */
+/* Tensor parallel: every layer ends with the sum of the ranks' partial block outputs, [n_tokens][n_embd] floats
+ * (the reference's tp_allreduce_sum, include/tp.h:53-79, for a whole batch).  The caller supplies the collective
+ * (NCCL, MPI, ...): it is called once per layer with the partial output on the device and the library's stream, must
+ * enqueue an in-place sum over the ranks on that stream and return 0.  Without one installed a tensor-parallel rank
+ * returns its partial output (tests sum them on the host).  upload takes whole ggml records on every rank and keeps
+ * this rank's part; export returns this rank's shard (gate rows | up rows | down columns, ggml block order). */
+int fomoe_b200_batch_set_allreduce(fomoe_b200_batch_t *b, fomoe_b200_allreduce_fn fn, void *user);
 int fomoe_b200_batch_wait_profile(fomoe_b200_batch_t *b, int on, unsigned long long *out);
 void fomoe_b200_batch_synth_logits(uint64_t seed, int layer, int max_tokens, int n_experts, int n_tokens, float *out);
 

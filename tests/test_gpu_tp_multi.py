@@ -73,8 +73,28 @@ def _run_rank(rank, world, port, q):
     d.set_allreduce(None)
     d.set_variant(2)
     st = d.status()
+    # the batched (tensor-core) path, sharded the same way, with NCCL summing the ranks' [tokens x hidden] partial
+    # outputs on the library's stream after every layer
+    bat_out = None
+    if SHAPE["n_inter"] % (256 * world) == 0:
+        bat = fb.BatchedMoe(2, SHAPE["n_embd"], SHAPE["n_inter"], SHAPE["n_experts"], SHAPE["top_k"], True, max_tokens=24,
+                            device=rank, tp_rank=rank, tp_size=world)
+        bat.generate(SEED, with_logits=True)
+
+        def bhook(ptr, n, s):
+            t = torch.as_tensor(_Dev(ptr, n), device=f"cuda:{rank}")
+            with torch.cuda.stream(torch.cuda.ExternalStream(s, device=rank)):
+                dist.all_reduce(t)
+            return 0
+
+        bat.set_allreduce(bhook)
+        bat.tokens_upload(np.stack([H.hidden(fb, SEED, t, SHAPE["n_embd"]) for t in range(24)]))
+        bat.stack_run(24)
+        bat_out = bat.tokens_download(24)
+        st = st or bat.status()
+        bat.close()
     dist.barrier()
-    q.put((rank, out, one, ids, st, out_nccl))
+    q.put((rank, out, one, ids, st, out_nccl, bat_out))
     dist.barrier()
     d.close()
     dist.destroy_process_group()
@@ -115,8 +135,19 @@ def test_tensor_parallel_stack_across_gpus(fb, world, n_inter):
     single.tokens_upload(0, toks)
     single.tokens_run(0, 4)
     want = single.tokens_download(0, 4)
-    for rank, out, one, ids, st, out_nccl in res:
+    bat_want = None
+    if n_inter % (256 * world) == 0:
+        bs = fb.BatchedMoe(2, SHAPE["n_embd"], SHAPE["n_inter"], SHAPE["n_experts"], SHAPE["top_k"], True, max_tokens=24)
+        bs.generate(SEED, with_logits=True)
+        bs.tokens_upload(np.stack([H.hidden(fb, SEED, t, SHAPE["n_embd"]) for t in range(24)]))
+        bs.stack_run(24)
+        bat_want = bs.tokens_download(24)
+        bs.close()
+    for rank, out, one, ids, st, out_nccl, bat_out in res:
         assert st == 0
+        if bat_want is not None:
+            assert (H.bits(bat_out) == H.bits(res[0][6])).all()   # NCCL leaves the same bits on every rank
+            assert max(H.rel_l2(bat_out[t], bat_want[t]) for t in range(24)) < 1e-3
         assert H.rel_l2(out_nccl, out) < 1e-5                   # NCCL between per-phase kernels == fused exchange
         assert (H.bits(out) == H.bits(res[0][1])).all()        # every rank holds the same bits
         assert (H.bits(one) == H.bits(out[1])).all()           # host-to-host call == resident run
