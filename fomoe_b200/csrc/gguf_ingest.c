@@ -133,7 +133,7 @@ static gg_file_t *gg_open(const char *path, char *err, size_t err_len) {
     why = "not a GGUF file (magic / version 2 or 3 expected)";
     if (gg_rd(g, &magic, 4) || gg_rd(g, &version, 4) || magic != GG_MAGIC || (version != 2 && version != 3)) goto fail;
     why = "truncated header";
-    if (gg_rd(g, &g->n_tensors, 8) || gg_rd(g, &n_kv, 8) || g->n_tensors > (1u << 24) || n_kv > (1u << 24)) goto fail;
+    if (gg_rd(g, &g->n_tensors, 8) || gg_rd(g, &n_kv, 8) || g->n_tensors > (1u << 20) || n_kv > (1u << 20)) goto fail;
     g->alignment = 32; /* include/gguf.h:55 */
     why = "malformed key/value section";
     for (uint64_t i = 0; i < n_kv; i++) {
@@ -155,7 +155,7 @@ static gg_file_t *gg_open(const char *path, char *err, size_t err_len) {
         uint64_t n = 1;
         for (uint32_t d = 0; d < GG_MAX_DIMS; d++) t->dims[d] = 1;
         for (uint32_t d = 0; d < t->n_dims; d++) {
-            if (gg_rd(g, &t->dims[d], 8)) goto fail;
+            if (gg_rd(g, &t->dims[d], 8) || t->dims[d] == 0 || t->dims[d] > (1ull << 40) / n) goto fail;
             n *= t->dims[d];
         }
         if (gg_rd(g, &t->type, 4) || gg_rd(g, &t->offset, 8)) goto fail;
@@ -179,7 +179,10 @@ static const gg_tensor_t *gg_find(const gg_file_t *g, const char *name) {
 }
 
 static int gg_read(gg_file_t *g, const gg_tensor_t *t, uint64_t at, void *dst, uint64_t n) {
-    if (at + n > t->nbytes || g->data_offset + t->offset + t->nbytes > g->file_size) return -1;
+    /* every term is checked by itself: a malformed directory must not wrap the sum */
+    if (at > t->nbytes || n > t->nbytes - at || g->data_offset > g->file_size || t->offset > g->file_size - g->data_offset ||
+        t->nbytes > g->file_size - g->data_offset - t->offset)
+        return -1;
     if (fseeko(g->f, (off_t)(g->data_offset + t->offset + at), SEEK_SET)) return -1;
     return gg_rd(g, dst, n);
 }
