@@ -57,6 +57,32 @@ def test_reference_arm_runs_without_the_cuda_library():
     assert "MAPPED_PRODUCT False True" in lines[-1]
 
 
+def test_reference_arm_of_the_batched_configuration():
+    """`bench.py --impl reference --config 4`: the reference's per-token CPU path on the batched configuration's layer,
+    same metric, unit and workload string as the GPU arm's line, host-only inputs (the logits of the host generator
+    equal the ones the library generates on the device)."""
+    import json
+    import subprocess
+    import sys
+    code = ("import sys; sys.argv = ['bench.py', '--impl', 'reference', '--config', '4', '--steps', '2', '--warmup', '0'];\n"
+            "import bench; bench.cpu_baseline4.__defaults__ = (None, 2, 0.05)\n"
+            "bench.main()\n"
+            "maps = open('/proc/self/maps').read()\n"
+            "print('MAPPED_PRODUCT', 'libfomoe_b200.so' in maps, 'libfomoe_synth.so' in maps)\n")
+    out = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = out.stdout.strip().splitlines()
+    line = json.loads(next(l for l in lines if l.startswith("{")))
+    b = _bench()
+    assert line["impl"] == "reference" and line["metric"] == b.C4_METRIC and line["unit"] == b.C4_UNIT
+    assert line["config"] == {"workload": b.c4_workload(48)} and line["value"] > 0
+    assert "MAPPED_PRODUCT False True" in lines[-1]
+    import numpy as np
+    import fomoe_b200
+    from fomoe_b200 import synth
+    assert (fomoe_b200.synth_logits(7, 2, 5, 16).reshape(-1) == synth.f32(7, 2, 8, 0.0, 1.0, 5 * 16)).all()
+
+
 def test_host_generator_library_matches_the_main_library(fb=None):
     import numpy as np
     import fomoe_b200
