@@ -353,14 +353,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             if (TP) {
                 bool got = true;
                 if (l > 0 && K.tp_two_stage) {
-                    for (int c = cta + warp * G; c < n / 32 && got; c += G * SK_WARPS) {
-                        got = sk_reduce_elem(K.tp_recv, K.tp_xsum, K.tp_size, n, 32 * c + lane, gen - 1u, K.abort_flag, K.spin_limit);
-                        if (!__all_sync(FULL, got)) { /* release the threads that are about to poll for this sum */
-                            if (lane == 0) sk_give_up(B);
-                            got = false;
-                        }
-                    }
-                    if (own && got) got = sk_gather8_local(K.tp_xsum, e0, gen - 1u, mo, K.abort_flag, K.spin_limit);
+                    /* the ranks' words were added up by one warp per 32 elements while the previous layer's down
+                     * phase was still streaming (see there): what is left is to fetch the sums */
+                    if (own) got = sk_gather8_local(K.tp_xsum, e0, gen - 1u, mo, K.abort_flag, K.spin_limit);
                 } else if (l > 0 && own)
                     got = sk_gather8(K.tp_recv, K.tp_size, n, e0, gen - 1u, mo, K.abort_flag, K.spin_limit);
                 if (!__syncthreads_and(got ? 1 : 0)) {
@@ -606,7 +601,22 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 }
             }
             __syncthreads();
-            if (warp < SK_DOWN_WARPS) {
+            /* Two-stage receive, first stage: under tensor parallelism the last warp of a block (it has no down
+             * tasks) adds up, in rank order, the words all ranks store for the block's 32 output elements of THIS
+             * layer as they arrive, and publishes the sums for the next layer's join.  It must not take part in the
+             * block barrier before the combine: the words it waits for include the ones this very block's combine
+             * sends.  The other fifteen warps meet at a barrier of their own; all sixteen meet again afterwards. */
+            const bool early_reduce = TP && K.tp_two_stage && l + 1 < K.n_layers;
+            const bool reducer = early_reduce && warp == SK_WARPS - 1;
+            if (reducer) {
+                bool got = true;
+                for (int c = cta; c < n / 32 && got; c += G)
+                    got = sk_reduce_elem(K.tp_recv, K.tp_xsum, K.tp_size, n, 32 * c + lane, gen, K.abort_flag, K.spin_limit);
+                if (!__all_sync(FULL, got)) {
+                    if (lane == 0) sk_give_up(B);
+                    alive = false;
+                }
+            } else if (warp < SK_DOWN_WARPS) {
                 int it = 0;
                 for (int j = warp; j < d1 - d0; j += SK_DOWN_WARPS, it++) {
                     const int s = it & 1;
@@ -680,15 +690,30 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     }
                 }
             }
-            if (!__syncthreads_and(alive ? 1 : 0)) {
-                if (tid == 0) sk_give_up(B);
-                alive = false;
-                break;
+            bool go;
+            if (early_reduce) {
+                go = alive;
+                if (!reducer) {
+                    uint32_t all;
+                    asm volatile(
+                        "{\n"
+                        ".reg .pred p, q;\n"
+                        "setp.ne.b32 p, %1, 0;\n"
+                        "barrier.cta.red.and.pred q, 2, %2, p;\n"
+                        "selp.u32 %0, 1, 0, q;\n"
+                        "}\n"
+                        : "=r"(all)
+                        : "r"((uint32_t)alive), "n"(SK_THREADS - 32)
+                        : "memory");
+                    go = all != 0;
+                }
+            } else {
+                go = __syncthreads_and(alive ? 1 : 0) != 0;
             }
             /* combine: partial += score * down in list order (src/cpu_expert.c:114-115), shared expert added after
              * (src/inference.c:595).  The block that ran a row group's LAST slot owns it; slots that ran in earlier
              * blocks arrive through global memory (those blocks ran them first, so the wait is normally over). */
-            for (int q = warp; q < n_own_rg && alive; q += SK_WARPS) {
+            for (int q = warp; q < n_own_rg && go && !reducer; q += early_reduce ? SK_WARPS - 1 : SK_WARPS) {
                 const int rg = rg_first + q;
                 const int s_lo = max(d0, rg * ns) - rg * ns; /* slots below s_lo ran elsewhere */
                 const int r = rg * drpg + lane;
@@ -746,6 +771,13 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         A.moe_out[r] = acc;
                     }
                 }
+            }
+            /* everybody agrees on whether the layer succeeded (the reducing warp included) */
+            if (early_reduce) go = __syncthreads_and((alive && go) ? 1 : 0) != 0;
+            if (!go) {
+                if (tid == 0) sk_give_up(B);
+                alive = false;
+                break;
             }
             SK_STAMP(8);
             if (!TP) {
