@@ -475,6 +475,53 @@ __device__ __forceinline__ float fb_dot_q4k_half_sm(const uint4 &hdr, const uint
     return __fmaf_rn(d, (float)isum, -__fmul_rn(dmin, (float)msum));
 }
 
+/* Q5_K, one half of a super-block: fb_dot_q5k_sm restricted to chunks 2 half, 2 half + 1 (hdr and the fifth-bit
+ * field h0/h1 are the whole block's, qs the half's four pieces). */
+__device__ __forceinline__ float fb_dot_q5k_half_sm(const uint4 &hdr, const uint4 &h0, const uint4 &h1, const uint4 (&qs)[4],
+                                                    uint32_t a_u, int half) {
+    const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+    const uint32_t scw = half ? ((u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4)) : (u0 & 0x3f3f3f3fu);
+    const uint32_t mw = half ? (((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4)) : (u1 & 0x3f3f3f3fu);
+    const uint32_t ah_u = a_u + 128u * (uint32_t)half;
+    int isum = 0;
+#pragma unroll
+    for (int cc = 0; cc < 2; cc++) {
+        const int c = 2 * half + cc;
+        int lo = 0, hi16 = 0, blo = 0, bhi = 0;
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            const uint4 w = qs[2 * cc + kk];
+            const uint4 hb = kk ? h1 : h0;
+            const uint4 al = fb_lds128_a(ah_u + 16 * (4 * cc + kk));
+            const uint4 ah = fb_lds128_a(ah_u + 16 * (4 * cc + 2 + kk));
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t q = fb_u4c(w, i), h = fb_u4c(hb, i), xl = fb_u4c(al, i), xh = fb_u4c(ah, i);
+                lo = fb_dp4a(q & 0x0f0f0f0fu, xl, lo);
+                hi16 = fb_dp4a_us(q & 0xf0f0f0f0u, xh, hi16);
+                blo = fb_dp4a_us(h & (0x01010101u << (2 * c)), xl, blo);
+                bhi = fb_dp4a_us(h & (0x01010101u << (2 * c + 1)), xh, bhi);
+            }
+        }
+        const int s0 = (scw >> (16 * cc)) & 0xff, s1 = (scw >> (16 * cc + 8)) & 0xff;
+        isum += s0 * (lo + 16 * (blo >> (2 * c))) + s1 * ((hi16 >> 4) + 16 * (bhi >> (2 * c + 1)));
+    }
+    const uint4 b = fb_lds128_a(a_u + 256 + 16u * (uint32_t)half);
+    int msum = 0;
+    {
+        const uint32_t d01 = __byte_perm(mw, 0, 0x1100), d23 = __byte_perm(mw, 0, 0x3322);
+        msum = fb_dp2a_lo_su(b.x, d01, msum);
+        msum = fb_dp2a_hi_su(b.y, d01, msum);
+        msum = fb_dp2a_lo_su(b.z, d23, msum);
+        msum = fb_dp2a_hi_su(b.w, d23, msum);
+    }
+    float yd;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(yd) : "r"(a_u + 288));
+    const float d = __fmul_rn(yd, fb_half_bits_to_float(hdr.x & 0xffff));
+    const float dmin = __fmul_rn(yd, fb_half_bits_to_float(hdr.x >> 16));
+    return __fmaf_rn(d, (float)isum, -__fmul_rn(dmin, (float)msum));
+}
+
 __device__ __forceinline__ float fb_dot_q6k_half_sm(const uint4 (&ql)[4], const uint4 (&qh)[2], const uint2 &sc,
                                                     uint32_t d16, uint32_t a_u, int half) {
     int totA = 0, totB = 0;

@@ -286,10 +286,8 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
     c->down_types = (int *)malloc(sizeof(int) * (size_t)cfg->n_layers);
     for (int l = 0; l < cfg->n_layers; l++) {
         c->down_types[l] = cfg->down_types ? cfg->down_types[l] : FB_TYPE_Q6_K;
-        if ((c->down_types[l] != FB_TYPE_Q4_K && c->down_types[l] != FB_TYPE_Q5_K && c->down_types[l] != FB_TYPE_Q6_K) ||
-            (c->down_half >= 0 && c->down_types[l] == FB_TYPE_Q5_K)) {
-            set_err(c, "layer %d: down type %d unsupported%s", l, c->down_types[l],
-                    c->down_half >= 0 ? " for shards of half super-blocks" : "");
+        if (c->down_types[l] != FB_TYPE_Q4_K && c->down_types[l] != FB_TYPE_Q5_K && c->down_types[l] != FB_TYPE_Q6_K) {
+            set_err(c, "layer %d: down type %d unsupported", l, c->down_types[l]);
             free(c->down_types);
             free(c);
             return NULL;

@@ -32,6 +32,7 @@
 
 /* template selectors of the down kernels for shards of half super-blocks (never stored anywhere) */
 #define FB_TYPE_Q4_K_H 112
+#define FB_TYPE_Q5_K_H 113
 #define FB_TYPE_Q6_K_H 114
 
 /* cudaFuncSetAttribute holds for one device: remember per device ordinal whether it has been done */
@@ -285,6 +286,13 @@ __global__ void __launch_bounds__(256) k_down(fb_args_t A) {
 #pragma unroll
             for (int i = 0; i < 4; i++) q[i] = ldg_stream(p + 32 * (i + 1));
             f = fb_dot_q4k_half_sm(hd, q, fb_smem_u32(a), A.down_half);
+        } else if (TYPE == FB_TYPE_Q5_K_H) {
+            const uint4 *p = reinterpret_cast<const uint4 *>(rec + (uint64_t)rg * FB_Q5K_HGROUP) + lane;
+            const uint4 hd = ldg_stream(p), h0 = ldg_stream(p + 32), h1 = ldg_stream(p + 64);
+            uint4 q[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) q[i] = ldg_stream(p + 32 * (i + 3));
+            f = fb_dot_q5k_half_sm(hd, h0, h1, q, fb_smem_u32(a), A.down_half);
         } else if (TYPE == FB_TYPE_Q6_K_H) {
             const uint8_t *gb = rec + (uint64_t)rg * FB_Q6K_HGROUP;
             const uint4 *p = reinterpret_cast<const uint4 *>(gb) + lane;
@@ -631,6 +639,8 @@ extern "C" int fb_launch_down(const fb_args_t *a, int grid, void *stream) {
             k_down<FB_TYPE_Q4_K_H><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
         else if (a->down_type == FB_TYPE_Q6_K)
             k_down<FB_TYPE_Q6_K_H><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
+        else if (a->down_type == FB_TYPE_Q5_K)
+            k_down<FB_TYPE_Q5_K_H><<<grid, 256, sm, (cudaStream_t)stream>>>(*a);
         else
             return (int)cudaErrorInvalidValue;
     } else if (a->down_type == FB_TYPE_Q4_K)

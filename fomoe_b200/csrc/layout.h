@@ -58,8 +58,10 @@
 #define FB_Q6K_OFF_SC 6144u
 #define FB_Q6K_OFF_D 6656u
 #define FB_Q4K_HALF 80u
+#define FB_Q5K_HALF 112u /* header 16, fifth-bit field 32 (kept whole: a half uses four bits of every byte), quants 64 */
 #define FB_Q6K_HALF 106u
 #define FB_Q4K_HGROUP (FB_Q4K_HALF * FB_GROUP) /* 2560 */
+#define FB_Q5K_HGROUP (FB_Q5K_HALF * FB_GROUP) /* 3584 */
 #define FB_Q6K_HGROUP (FB_Q6K_HALF * FB_GROUP) /* 3392 */
 #define FB_Q6K_HOFF_QH 2048u
 #define FB_Q6K_HOFF_SC 3072u
@@ -79,10 +81,10 @@ FB_HD uint64_t fb_block_bytes(int type) {
     return type == FB_TYPE_Q4_K ? FB_Q4K_BLOCK : type == FB_TYPE_Q5_K ? FB_Q5K_BLOCK : type == FB_TYPE_Q6_K ? FB_Q6K_BLOCK : 0;
 }
 FB_HD uint64_t fb_group_bytes(int type) { return fb_block_bytes(type) * FB_GROUP; }
-/* the same for a shard of half super-blocks (half = 0 or 1; half < 0: whole blocks); Q5_K has no half form */
+/* the same for a shard of half super-blocks (half = 0 or 1; half < 0: whole blocks) */
 FB_HD uint64_t fb_block_bytes_h(int type, int half) {
     if (half < 0) return fb_block_bytes(type);
-    return type == FB_TYPE_Q4_K ? FB_Q4K_HALF : type == FB_TYPE_Q6_K ? FB_Q6K_HALF : 0;
+    return type == FB_TYPE_Q4_K ? FB_Q4K_HALF : type == FB_TYPE_Q5_K ? FB_Q5K_HALF : type == FB_TYPE_Q6_K ? FB_Q6K_HALF : 0;
 }
 FB_HD uint64_t fb_group_bytes_h(int type, int half) { return fb_block_bytes_h(type, half) * FB_GROUP; }
 FB_HD uint64_t fb_n_groups(uint64_t n_blocks) { return (n_blocks + FB_GROUP - 1) / FB_GROUP; }

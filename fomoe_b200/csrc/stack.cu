@@ -551,7 +551,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
              *      long run per block dealt round-robin to 12 warps (two ring stages of one group each). */
             sk_arrive(B, S);
             const int ns = A.n_slots, dbpr = A.down_bpr, drpg = 32 / dbpr;
-            const uint32_t GB = (DM == SK_DM_HALF) ? (A.down_type == FB_TYPE_Q4_K ? FB_Q4K_HGROUP : FB_Q6K_HGROUP)
+            const uint32_t GB = (DM == SK_DM_HALF) ? (A.down_type == FB_TYPE_Q4_K ? FB_Q4K_HGROUP : A.down_type == FB_TYPE_Q5_K ? FB_Q5K_HGROUP : FB_Q6K_HGROUP)
                                 : (A.down_type == FB_TYPE_Q4_K) ? FB_Q4K_GROUP
                                 : (DM == SK_DM_WHOLE_Q5 && A.down_type == FB_TYPE_Q5_K) ? FB_Q5K_GROUP : FB_Q6K_GROUP;
             const int dtotal = A.down_groups * ns;
@@ -638,6 +638,14 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         __syncwarp();
                         if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
                         f = fb_dot_q4k_half_sm(hd, q, a_u, A.down_half);
+                    } else if (DM == SK_DM_HALF && A.down_type == FB_TYPE_Q5_K) {
+                        const uint4 hd = fb_lds128(st), h0 = fb_lds128(st + 512), h1 = fb_lds128(st + 1024);
+                        uint4 q[4];
+#pragma unroll
+                        for (int k = 0; k < 4; k++) q[k] = fb_lds128(st + 512 * (k + 3));
+                        __syncwarp();
+                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        f = fb_dot_q5k_half_sm(hd, h0, h1, q, a_u, A.down_half);
                     } else if (DM == SK_DM_HALF) {
                         uint4 ql[4], qh[2];
 #pragma unroll
@@ -834,7 +842,7 @@ extern "C" int fb_stack_supported(const fb_args_t *a, int grid) {
     const int dtotal = a->down_groups * a->n_slots;
     const int run = (dtotal + grid - 1) / grid;                       /* longest run of down tasks of one block */
     const int max_rg = (run + a->n_slots - 2) / a->n_slots + 2;       /* row groups such a run can touch */
-    if (a->down_half >= 0 && a->down_type != FB_TYPE_Q4_K && a->down_type != FB_TYPE_Q6_K) return 0;
+    if (a->down_half >= 0 && a->down_type != FB_TYPE_Q4_K && a->down_type != FB_TYPE_Q5_K && a->down_type != FB_TYPE_Q6_K) return 0;
     if (a->gate_type != FB_TYPE_Q4_K) return 0;
     return a->n_embd <= 4096 && a->n_slots <= SK_DN_SLOTS && a->n_slots * a->down_bpr <= SK_MAX_Q8A &&
            a->n_embd / FB_QK <= 16 && a->tp_size <= FB_MAX_TP && a->inter_local % FB_QK == 0 && max_rg <= SK_MAX_RG;

@@ -59,6 +59,16 @@ __device__ __forceinline__ void store_q4k_half(uint8_t *shard, int lb, const uin
     for (int k = 0; k < 4; k++) grp[32 * (k + 1)] = make_uint4(q[4 * k], q[4 * k + 1], q[4 * k + 2], q[4 * k + 3]);
 }
 
+__device__ __forceinline__ void store_q5k_half(uint8_t *shard, int lb, const uint32_t w[44], int h) {
+    uint4 *grp = reinterpret_cast<uint4 *>(shard + (uint64_t)(lb >> 5) * FB_Q5K_HGROUP) + (lb & 31);
+    grp[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    grp[32] = make_uint4(w[4], w[5], w[6], w[7]);     /* the fifth-bit field stays whole */
+    grp[64] = make_uint4(w[8], w[9], w[10], w[11]);
+    const uint32_t *q = w + 12 + 16 * h;
+#pragma unroll
+    for (int k = 0; k < 4; k++) grp[32 * (k + 3)] = make_uint4(q[4 * k], q[4 * k + 1], q[4 * k + 2], q[4 * k + 3]);
+}
+
 __device__ __forceinline__ void store_q6k_half(uint8_t *shard, int lb, const uint32_t ql[32], const uint32_t qh[16],
                                                const uint32_t sc[4], uint16_t d, int h) {
     uint8_t *gb = shard + (uint64_t)(lb >> 5) * FB_Q6K_HGROUP;
@@ -92,7 +102,8 @@ __global__ void k_gen_shards(uint8_t *dst0, uint64_t rec_stride, uint64_t seed, 
             if (lb < n_local) fsyn_q5k_block(key, full_block_index(g, lb), w);
             else
                 for (int i = 0; i < 44; i++) w[i] = 0;
-            store_q5k(shard, lb, w);
+            if (g.half >= 0) store_q5k_half(shard, lb, w, g.half);
+            else store_q5k(shard, lb, w);
         } else {
             uint32_t ql[32], qh[16], sc[4];
             uint16_t d = 0;
@@ -135,7 +146,8 @@ __global__ void k_repack(uint8_t *shard, const uint8_t *src, fb_shard_geom_t g) 
                 for (int i = 0; i < 44; i++) w[i] = s[i];
             } else
                 for (int i = 0; i < 44; i++) w[i] = 0;
-            store_q5k(shard, lb, w);
+            if (g.half >= 0) store_q5k_half(shard, lb, w, g.half);
+            else store_q5k(shard, lb, w);
         } else {
             uint32_t w[52];
             uint16_t d = 0;
@@ -207,6 +219,32 @@ __device__ __noinline__ void dequant_half_block(float *dst, const uint8_t *shard
                         const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xff;
                         y[64 * cc + 16 * kk + i] = __fsub_rn(__fmul_rn(d1, (float)(byte & 0xf)), m1);
                         y[64 * cc + 32 + 16 * kk + i] = __fsub_rn(__fmul_rn(d2, (float)(byte >> 4)), m2);
+                    }
+                }
+            }
+        } else if (type == FB_TYPE_Q5_K) { /* src/quant.c:216-247 restricted to chunks 2h, 2h+1 */
+            const uint4 *grp = reinterpret_cast<const uint4 *>(shard + (uint64_t)(lb >> 5) * FB_Q5K_HGROUP) + (lb & 31);
+            const uint4 hdr = grp[0];
+            const float d = fb_half_bits_to_float(hdr.x & 0xffff), mn = fb_half_bits_to_float(hdr.x >> 16);
+            const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+            const uint32_t scw = h ? ((u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4)) : (u0 & 0x3f3f3f3fu);
+            const uint32_t mw = h ? (((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4)) : (u1 & 0x3f3f3f3fu);
+            for (int cc = 0; cc < 2; cc++) {
+                const int c = 2 * h + cc; /* chunk of the whole block: its fifth bits are bits 2c and 2c+1 */
+                const float d1 = __fmul_rn(d, (float)((scw >> (16 * cc)) & 0xff));
+                const float d2 = __fmul_rn(d, (float)((scw >> (16 * cc + 8)) & 0xff));
+                const float m1 = __fmul_rn(mn, (float)((mw >> (16 * cc)) & 0xff));
+                const float m2 = __fmul_rn(mn, (float)((mw >> (16 * cc + 8)) & 0xff));
+                for (int kk = 0; kk < 2; kk++) {
+                    const uint4 v = grp[32 * (3 + 2 * cc + kk)], hv = grp[32 * (1 + kk)];
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w}, hw[4] = {hv.x, hv.y, hv.z, hv.w};
+                    for (int i = 0; i < 16; i++) {
+                        const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xff;
+                        const uint32_t hb = (hw[i >> 2] >> (8 * (i & 3))) & 0xff;
+                        const uint32_t q1 = (byte & 0xf) + (((hb >> (2 * c)) & 1u) << 4);
+                        const uint32_t q2 = (byte >> 4) + (((hb >> (2 * c + 1)) & 1u) << 4);
+                        y[64 * cc + 16 * kk + i] = __fsub_rn(__fmul_rn(d1, (float)q1), m1);
+                        y[64 * cc + 32 + 16 * kk + i] = __fsub_rn(__fmul_rn(d2, (float)q2), m2);
                     }
                 }
             }

@@ -116,7 +116,7 @@ typedef struct {
     int tp_rank, tp_size;    /* tensor parallelism over the intermediate dimension, tp_size <= 8.  With W = n_inter/256
                                 windows: tp_size dividing W gives every rank W/tp_size whole windows; tp_size == 2 W
                                 (8 ranks at n_inter 1024) gives ranks 2p and 2p+1 window p together: both compute its
-                                gate/up rows, each owns one 128-column half of the down projection (Q4_K / Q6_K only) */
+                                gate/up rows, each owns one 128-column half of the down projection */
     float rms_eps;
     float car_threshold;     /* CAR runs when 0 < threshold < 1 (reference src/car.c:68, gpu_kernels.hip:7170) */
     int car_dampen;          /* 1: substitute weight = original weight * ratio, no renormalise */
