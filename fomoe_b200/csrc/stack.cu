@@ -46,7 +46,7 @@
 #define SK_BAR_THREAD (SK_THREADS - 32) /* lane 0 of the last warp runs the grid barrier; it issues no copies */
 
 struct sk_smem_t {
-    fb_args_t A;                         /* this layer's arguments */
+    fb_args_t A2[2];                     /* this layer's arguments and, fetched during the down phase, the next layer's */
     fb_q8_entry_t q8h[16];               /* quantised hidden state */
     fb_q8_entry_t q8a[SK_MAX_Q8A];       /* quantised activations of every slot */
     float dots[SK_MAX_RG][SK_DN_SLOTS][32]; /* per-expert down outputs of this block's row groups */
@@ -298,18 +298,19 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
     bool alive = true;
     bool pending_join = false; /* a barrier has been arrived at but not yet waited for */
 
+    /* the first layer's arguments; every later layer's are fetched by an idle warp during the layer before it */
+    {
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(K.layers);
+        uint32_t *dst = reinterpret_cast<uint32_t *>(&S->A2[0]);
+        for (int i = tid; i < (int)(sizeof(fb_args_t) / 4); i += SK_THREADS) dst[i] = src[i];
+        __syncthreads();
+    }
+    int cur = 0; /* which of the two argument buffers holds the current layer */
     for (int tk = 0; tk < K.tok_count && alive; tk++) {
         const unsigned tok = tok_first + (unsigned)tk;
         float x[8];
-        for (int l = 0; l < K.n_layers && alive; l++) {
-            /* ---- this layer's arguments into shared memory */
-            {
-                const uint32_t *src = reinterpret_cast<const uint32_t *>(K.layers + l);
-                uint32_t *dst = reinterpret_cast<uint32_t *>(&S->A);
-                for (int i = tid; i < (int)(sizeof(fb_args_t) / 4); i += SK_THREADS) dst[i] = src[i];
-            }
-            __syncthreads();
-            const fb_args_t &A = S->A;
+        for (int l = 0; l < K.n_layers && alive; l++, cur ^= 1) {
+            const fb_args_t &A = S->A2[cur];
             const int n = A.n_embd, e0 = 8 * tid;
             const bool own = e0 < n;
 
@@ -616,6 +617,13 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     if (lane == 0) sk_give_up(B);
                     alive = false;
                 }
+            } else if (warp == SK_DOWN_WARPS) {
+                /* a warp without down tasks fetches the next layer's arguments (the next token's first layer after
+                 * the last one) into the other buffer; the block barriers below publish them */
+                const int ln = (l + 1 < K.n_layers) ? l + 1 : 0;
+                const uint32_t *src = reinterpret_cast<const uint32_t *>(K.layers + ln);
+                uint32_t *dst = reinterpret_cast<uint32_t *>(&S->A2[cur ^ 1]);
+                for (int i = lane; i < (int)(sizeof(fb_args_t) / 4); i += 32) dst[i] = src[i];
             } else if (warp < SK_DOWN_WARPS) {
                 int it = 0;
                 for (int j = warp; j < d1 - d0; j += SK_DOWN_WARPS, it++) {
@@ -797,7 +805,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
         /* ---- end of token: the last layer's block output, x += moe_out, publish */
         float mo[8];
         {
-            const fb_args_t &A = S->A;
+            const fb_args_t &A = S->A2[cur ^ 1]; /* the last layer's (cur has moved on) */
             const int e0 = 8 * tid;
             if (TP) {
                 bool got = true;
@@ -831,7 +839,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 xo[1] = o[1];
             }
         }
-        __syncthreads(); /* S->A is rewritten at the top of the next token */
+        __syncthreads(); /* the token is complete in this block before the next one starts */
     }
     if (leader && tid == 0 && alive) *K.tok_ctr = tok_first + (unsigned)K.tok_count;
 }
