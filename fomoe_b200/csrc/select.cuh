@@ -3,8 +3,8 @@
  *
  * Same result as route.cuh's single-warp routine, built for latency:
  *   1. every warp sorts its 32 (logit, expert) pairs with a shuffle bitonic network, best first;
- *   2. the best 16 of each warp (256 candidates) are merged by rank: every candidate counts, by binary search in
- *      the other 15 sorted lists, how many entries beat it; ranks 0..15 are the block's best 16;
+ *   2. the best 16 of each warp are merged pairwise (bitonic merges that keep the better half) down to the block's
+ *      best 16;
  *   3. near-ties among the best k+1 are recomputed in the CPU's summation order (src/tensor.c:104-113) and the
  *      ranking repeated, so the selected ids match the CPU's top_k (src/tensor.c:226-252) index for index;
  *   4. softmax over all experts (src/tensor.c:186-200), renormalised top-k weights (src/inference.c:496-502);
@@ -76,13 +76,35 @@ static __device__ __noinline__ float fb_exact_logit(const fb_args_t &A, const fl
     return exact;
 }
 
+/* One level of the merge tree: warp w < NL takes sorted lists 2w and 2w+1 (16 entries each, best first) from `sv/si`,
+ * lays them out as one bitonic run (the second list reversed into lanes 16..31), sorts it with the five
+ * compare-exchange steps of a bitonic merge and leaves its best 16 as list w of `dv/di`. */
+template <int NL>
+__device__ __forceinline__ void fb_merge_level(const float (*sv)[16], const int (*si)[16], float (*dv)[16],
+                                               int (*di)[16], int warp, int lane) {
+    if (warp < NL) {
+        const int src = 2 * warp + (lane >> 4), pos = (lane < 16) ? lane : 31 - lane;
+        float v = sv[src][pos];
+        int id = si[src][pos];
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) fb_cmpx(v, id, d, (lane & d) == 0);
+        if (lane < 16) {
+            dv[warp][lane] = v;
+            di[warp][lane] = id;
+        }
+    }
+    __syncthreads();
+}
+
 /* The block's best 16 of one (value, id) pair per thread, in order (value descending, lower id first), left in
- * W->lv[1][slot][*] / W->li[1][slot][*].  Every warp sorts its 32 pairs; the best 16 of each warp (256 candidates) are
- * merged by rank: candidate p of warp list w has p better entries in its own list, a 5-step binary search in each of
- * the other 15 sorted lists counts the rest; ranks below 16 are the block's best 16.  Called by all 512 threads.
- * Out of line and shared by the selection proper, its repeat after the near-tie arbiter and cache-aware routing: one
- * copy of this code stays in the instruction cache from layer to layer (inlined at each use the stack kernel's hot
- * path outgrew the cache, and every phase of every layer slowed down by a third). */
+ * W->lv[1][slot][*] / W->li[1][slot][*].  Every warp sorts its 32 pairs with a shuffle network; the sixteen lists of
+ * 16 are then halved four times (8, 4, 2, 1 warps), each step a 5-stage bitonic merge of two lists that keeps the
+ * better half, ping-ponging between W->lv[0] and rows 4..11 of W->lv[1].  (Ranking all 256 candidates at once by
+ * binary search in the other lists took one barrier instead of four but 900 instructions per thread: twice as
+ * long.)  Called by all 512 threads.  Out of line and shared by the selection proper, its repeat after the near-tie
+ * arbiter and cache-aware routing: one copy of this code stays in the instruction cache from layer to layer
+ * (inlined at each use the stack kernel's hot path outgrew the cache, and every phase of every layer slowed down
+ * by a third). */
 static __device__ __noinline__ void fb_block_best16(fb_sel_smem_t *W, float v, int id, int slot) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     fb_sort32(v, id, lane);
@@ -91,27 +113,10 @@ static __device__ __noinline__ void fb_block_best16(fb_sel_smem_t *W, float v, i
         W->li[0][warp][lane] = id;
     }
     __syncthreads();
-    if (tid < 256) {
-        const int w = tid >> 4, p = tid & 15;
-        const float mv = W->lv[0][w][p];
-        const int mi = W->li[0][w][p];
-        int rank = p;
-#pragma unroll /* fully unrolled on purpose: the fifteen searches overlap (unrolled by 3 or 5: no faster, by 1: slower) */
-        for (int o = 1; o < 16; o++) {
-            const int w2 = (w + o) & 15;
-            int pos = 0;
-#pragma unroll
-            for (int st = 8; st > 0; st >>= 1)
-                if (fb_better(W->lv[0][w2][pos + st - 1], W->li[0][w2][pos + st - 1], mv, mi)) pos += st;
-            if (fb_better(W->lv[0][w2][pos], W->li[0][w2][pos], mv, mi)) pos++;
-            rank += pos;
-        }
-        if (rank < 16) {
-            W->lv[1][slot][rank] = mv;
-            W->li[1][slot][rank] = mi;
-        }
-    }
-    __syncthreads();
+    fb_merge_level<8>(W->lv[0], W->li[0], W->lv[1] + 4, W->li[1] + 4, warp, lane);
+    fb_merge_level<4>(W->lv[1] + 4, W->li[1] + 4, W->lv[0], W->li[0], warp, lane);
+    fb_merge_level<2>(W->lv[0], W->li[0], W->lv[1] + 4, W->li[1] + 4, warp, lane);
+    fb_merge_level<1>(W->lv[1] + 4, W->li[1] + 4, W->lv[1] + slot, W->li[1] + slot, warp, lane);
 }
 
 /* Cache-aware routing over one residency tier (src/car.c:36-264; classify as src/gpu_kernels.hip:7097-7149) on the
@@ -188,11 +193,10 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
         fb_block_best16(W, lg, (tid < nE) ? tid : 0x7fffffff, 0);
         /* best 16 now in lv[1][0][*] */
         if (pass == 1) break;
-        uint32_t flag = 0;
-        for (int r = 0; r + 1 < kk; r++) {
-            const float a = W->lv[1][0][r], b = W->lv[1][0][r + 1];
-            if (a - b <= FB_TIE_TOL * fmaxf(1.0f, fabsf(a))) flag |= (1u << r) | (1u << (r + 1));
-        }
+        /* lane r compares candidates r and r+1 (every warp does the same, so the flags need no broadcast) */
+        const float ca = W->lv[1][0][lane & 15], cb = W->lv[1][0][(lane + 1) & 15];
+        const uint32_t close = __ballot_sync(FULL, lane + 1 < kk && ca - cb <= FB_TIE_TOL * fmaxf(1.0f, fabsf(ca)));
+        const uint32_t flag = close | (close << 1);
         if (!flag) break;
         bool mine = false;
         for (int r = 0; r < kk; r++)
