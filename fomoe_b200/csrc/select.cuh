@@ -177,10 +177,12 @@ __device__ __forceinline__ int fb_select_car(const fb_args_t &A, fb_sel_smem_t *
 /* Must be called by all 512 threads of the block.  Outputs (shared memory): ids[n_slots], scores[n_slots],
  * ids_orig[top_k], slot_rec[n_slots], all_scores[n_experts].  `leader` updates the global counters;
  * `shared_score` is the weight of the shared expert's slot; `rec` (leader only, may be NULL) receives the decision
- * for the routing trace. */
+ * for the routing trace; `early(const int *candidates)` is called by every thread as soon as the selected ids are
+ * known. */
+template <class Early>
 __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const float *h_smem, float *all_scores, int *ids,
-                                int *ids_orig, float *scores, const uint8_t **slot_rec, bool leader,
-                                float shared_score = 1.0f, fb_route_rec_t *rec = nullptr) {
+                                int *ids_orig, float *scores, const uint8_t **slot_rec, bool leader, float shared_score,
+                                fb_route_rec_t *rec, Early early) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nE = A.n_experts, k = A.top_k, kk = min(k + 1, nE);
     float lg = (tid < nE) ? __ldcg(A.logits + tid) : -INFINITY;
@@ -204,6 +206,10 @@ __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const floa
         if (mine) lg = fb_exact_logit(A, h_smem, tid);
         __syncthreads();
     }
+
+    /* The selected experts are known now, as W->li[1][0][0..k-1]; only their weights (and, rarely, their order or a
+     * cache-aware substitute) are still to come.  The caller may start fetching what it will read first. */
+    early(W->li[1][0]);
 
     /* softmax: the maximum is the best candidate's logit */
     const float mx = W->lv[1][0][0];

@@ -484,9 +484,31 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             SK_STAMP(4);
 
             /* ---- SEL: routing, redundantly in every block (results identical by construction) */
+            /* As soon as the ids are known, each warp asks L2 for the gate and up groups of its first two tasks of
+             * the next phase: the softmax, renormalisation and hand-over that follow (about 1 us) then overlap with
+             * HBM's start-up instead of preceding it.  A wrong guess (order changed by an exact tie, a cache-aware
+             * substitute) costs a wasted prefetch, nothing else; the shared expert's shards were requested at the
+             * top of the layer. */
+            auto early = [&](const int *cand) {
+                if (lane != 0) return;
+                const int total = A.n_slots * A.gate_groups;
+                const int t0 = (int)(((long long)cta * total) / G), t1 = (int)(((long long)(cta + 1) * total) / G);
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    const int t = t0 + warp + u * SK_WARPS;
+                    if (t >= t1) break;
+                    const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
+                    if (slot >= A.top_k) break;
+                    const int e = cand[slot];
+                    if (e < 0 || e >= A.n_experts) break;
+                    const uint8_t *src = A.table_layer + (uint64_t)e * A.rec_bytes + (uint64_t)g * FB_Q4K_GROUP;
+                    fb_prefetch_l2(src, FB_Q4K_GROUP);
+                    fb_prefetch_l2(src + A.up_off, FB_Q4K_GROUP);
+                }
+            };
             fb_block_select(A, &S->sel, h_sm, S->all_scores, S->ids, S->ids_orig, S->scores, S->slot_rec, leader,
                             S->shared_gate,
-                            (leader && A.route_log) ? A.route_log + (size_t)tok * A.route_stride : nullptr);
+                            (leader && A.route_log) ? A.route_log + (size_t)tok * A.route_stride : nullptr, early);
             if (leader) {
                 if (tid < A.n_slots) {
                     A.ids[tid] = S->ids[tid];
