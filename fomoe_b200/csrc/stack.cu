@@ -37,6 +37,12 @@
 #include "stream.cuh"
 
 #define SK_THREADS 512
+#ifndef SK_EARLY_ROUNDS
+#define SK_EARLY_ROUNDS 0
+#endif
+#ifndef SK_EARLY_COPY
+#define SK_EARLY_COPY 1
+#endif
 #define SK_WARPS 16
 #define SK_DOWN_WARPS 13                              /* warps that run down tasks: 38 tasks per block at the 397B shape = 3 rounds */
 #define SK_DN_SLOTS 12                                /* expert slots the down phase can serve */
@@ -484,27 +490,53 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             SK_STAMP(4);
 
             /* ---- SEL: routing, redundantly in every block (results identical by construction) */
-            /* As soon as the ids are known, each warp asks L2 for the gate and up groups of its first two tasks of
-             * the next phase: the softmax, renormalisation and hand-over that follow (about 1 us) then overlap with
-             * HBM's start-up instead of preceding it.  A wrong guess (order changed by an exact tie, a cache-aware
-             * substitute) costs a wasted prefetch, nothing else; the shared expert's shards were requested at the
-             * top of the layer. */
+            /* As soon as the ids are known, each warp starts the copies of its first gate/up task into its ring
+             * stages: the softmax, renormalisation and hand-over that follow (about 1 us, more with cache-aware
+             * routing) then overlap with HBM's start-up instead of preceding it.  The hidden state that shares the
+             * ring's first bytes is dead by then.  When the final list differs in that slot (order changed by an
+             * exact tie of probabilities, a cache-aware substitute) the stale copy is awaited and the right one
+             * requested, which costs what starting late costs. */
+            const int gu_total = A.n_slots * A.gate_groups;
+            const int t0 = (int)(((long long)cta * gu_total) / G), t1 = (int)(((long long)(cta + 1) * gu_total) / G);
+            const uint32_t ring_u = fb_smem_u32(ring) + warp * 2 * FB_Q4K_GROUP;
+            auto issue = [&](const uint8_t *recp, int g, int which) {
+                const uint8_t *src = recp + (which ? A.up_off : 0) + (uint64_t)g * FB_Q4K_GROUP;
+                fb_mbar_expect_tx(full_u + 8 * which, FB_Q4K_GROUP);
+                fb_bulk_g2s(ring_u + which * FB_Q4K_GROUP, src, FB_Q4K_GROUP, full_u + 8 * which);
+            };
+            int early_e = -1; /* the expert whose groups were requested early (the same in every lane) */
             auto early = [&](const int *cand) {
-                if (lane != 0) return;
-                const int total = A.n_slots * A.gate_groups;
-                const int t0 = (int)(((long long)cta * total) / G), t1 = (int)(((long long)(cta + 1) * total) / G);
-#pragma unroll
-                for (int u = 0; u < 2; u++) {
-                    const int t = t0 + warp + u * SK_WARPS;
-                    if (t >= t1) break;
-                    const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
-                    if (slot >= A.top_k) break;
-                    const int e = cand[slot];
-                    if (e < 0 || e >= A.n_experts) break;
+                const int t = t0 + warp;
+                if (t >= t1) return;
+                const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
+                const int e = slot < A.top_k ? cand[slot] : A.n_experts;
+                if (e < 0 || e > A.n_experts) return;
+#if SK_EARLY_COPY
+                early_e = e;
+                if (lane == 0) {
+                    const uint8_t *recp = A.table_layer + (uint64_t)e * A.rec_bytes;
+                    issue(recp, g, 0);
+                    issue(recp, g, 1);
+                }
+#else
+                if (lane == 0 && slot < A.top_k) {
                     const uint8_t *src = A.table_layer + (uint64_t)e * A.rec_bytes + (uint64_t)g * FB_Q4K_GROUP;
                     fb_prefetch_l2(src, FB_Q4K_GROUP);
                     fb_prefetch_l2(src + A.up_off, FB_Q4K_GROUP);
                 }
+#endif
+#if SK_EARLY_ROUNDS
+                const int tb = t + SK_WARPS;
+                if (lane == 0 && tb < t1) {
+                    const int sb = tb / A.gate_groups, gb = tb - sb * A.gate_groups;
+                    const int eb = sb < A.top_k ? cand[sb] : -1;
+                    if (eb >= 0 && eb < A.n_experts) {
+                        const uint8_t *src = A.table_layer + (uint64_t)eb * A.rec_bytes + (uint64_t)gb * FB_Q4K_GROUP;
+                        fb_prefetch_l2(src, FB_Q4K_GROUP);
+                        fb_prefetch_l2(src + A.up_off, FB_Q4K_GROUP);
+                    }
+                }
+#endif
             };
             fb_block_select(A, &S->sel, h_sm, S->all_scores, S->ids, S->ids_orig, S->scores, S->slot_rec, leader,
                             S->shared_gate,
@@ -524,18 +556,21 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
              *      its run round-robin to its 16 warps. */
             {
                 const int bpr = A.gate_bpr, rpg = 32 / bpr;
-                const int total = A.n_slots * A.gate_groups;
-                const int t0 = (int)(((long long)cta * total) / G), t1 = (int)(((long long)(cta + 1) * total) / G);
-                const uint32_t ring_u = fb_smem_u32(ring) + warp * 2 * FB_Q4K_GROUP;
-                auto issue = [&](int t, int which) {
-                    const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
-                    const uint8_t *src = S->slot_rec[slot] + (which ? A.up_off : 0) + (uint64_t)g * FB_Q4K_GROUP;
-                    fb_mbar_expect_tx(full_u + 8 * which, FB_Q4K_GROUP);
-                    fb_bulk_g2s(ring_u + which * FB_Q4K_GROUP, src, FB_Q4K_GROUP, full_u + 8 * which);
-                };
-                if (lane == 0 && t0 + warp < t1) {
-                    issue(t0 + warp, 0);
-                    issue(t0 + warp, 1);
+                if (t0 + warp < t1) {
+                    const int slot = (t0 + warp) / A.gate_groups, g = (t0 + warp) - slot * A.gate_groups;
+                    if (early_e != S->ids[slot]) {
+                        if (early_e >= 0) { /* a stale copy is on its way into the stages: take it off the barriers */
+                            if (!fb_mbar_wait(full_u, full_uses[0] & 1) || !fb_mbar_wait(full_u + 8, full_uses[1] & 1))
+                                alive = false;
+                            full_uses[0]++;
+                            full_uses[1]++;
+                            __syncwarp();
+                        }
+                        if (alive && lane == 0) {
+                            issue(S->slot_rec[slot], g, 0);
+                            issue(S->slot_rec[slot], g, 1);
+                        }
+                    }
                 }
                 const uint32_t a_u = fb_smem_u32(&S->q8h[lane % bpr]);
                 for (int t = t0 + warp; t < t1 && alive; t += SK_WARPS) {
@@ -550,8 +585,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     fb_dot2_q4k_sm(ring_u + 16 * lane, ring_u + FB_Q4K_GROUP + 16 * lane, a_u, f[0], f[1]);
                     __syncwarp();
                     if (lane == 0 && t + SK_WARPS < t1) {
-                        issue(t + SK_WARPS, 0);
-                        issue(t + SK_WARPS, 1);
+                        const int tn = t + SK_WARPS, sn = tn / A.gate_groups;
+                        issue(S->slot_rec[sn], tn - sn * A.gate_groups, 0);
+                        issue(S->slot_rec[sn], tn - sn * A.gate_groups, 1);
                     }
                     const float fg = fb_span_sum(f[0], bpr), fu = fb_span_sum(f[1], bpr);
                     const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
