@@ -511,6 +511,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
                 const int e = slot < A.top_k ? cand[slot] : A.n_experts;
                 if (e < 0 || e > A.n_experts) return;
+                /* under cache-aware routing an expert that is not resident may still be replaced: it is left for
+                 * the start of the phase proper (a resident one, and the shared expert, stay where they are) */
+                if (slot < A.top_k && A.resident && A.car_threshold > 0.0f && A.car_threshold < 1.0f &&
+                    !((__ldg(A.resident + (e >> 5)) >> (e & 31)) & 1u))
+                    return;
 #if SK_EARLY_COPY
                 early_e = e;
                 if (lane == 0) {
