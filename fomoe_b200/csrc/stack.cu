@@ -46,7 +46,7 @@
 #define SK_WARPS 16
 #define SK_DOWN_WARPS 13                              /* warps that run down tasks: 38 tasks per block at the 397B shape = 3 rounds */
 #define SK_DN_SLOTS 12                                /* expert slots the down phase can serve */
-#define SK_RING_BYTES (SK_DOWN_WARPS * 2 * FB_Q6K_GROUP) /* 174,720 B: 13 x 2 x 6720; gate/up uses 16 x 2 x 4608 of it */
+#define SK_RING_BYTES (SK_DOWN_WARPS * 3 * FB_Q4K_GROUP) /* 179,712 B: 13 warps x 3 stages x 4608 or x 2 stages x 6720 (174,720); gate/up uses 16 x 2 x 4608 of it */
 #define SK_MAX_Q8A 48                                 /* n_slots * down blocks per row */
 #define SK_MAX_RG 8                                   /* row groups one block's run of down tasks can touch */
 #define SK_BAR_THREAD (SK_THREADS - 32) /* lane 0 of the last warp runs the grid barrier; it issues no copies */
@@ -65,7 +65,7 @@ struct sk_smem_t {
     const uint8_t *slot_rec[FB_MAX_SLOTS];
     float scale;
     int ok;
-    uint64_t full[SK_WARPS][2];          /* ring stages */
+    uint64_t full[SK_WARPS][3];          /* ring stages */
 };
 
 struct sk_bar_t {
@@ -289,11 +289,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
     const uint32_t full_u = fb_smem_u32(&S->full[warp][0]);
     if (tid == 0) {
         for (int w = 0; w < SK_WARPS; w++)
-            for (int s = 0; s < 2; s++) fb_mbar_init(fb_smem_u32(&S->full[w][s]), 1);
+            for (int s = 0; s < 3; s++) fb_mbar_init(fb_smem_u32(&S->full[w][s]), 1);
         fb_mbar_init_fence();
     }
     __syncthreads();
-    uint32_t full_uses[2] = {0, 0}; /* completed phases of this warp's two stage barriers */
+    uint32_t full_par = 0; /* bit s: parity of the completed phases of this warp's stage barrier s */
 
     const unsigned tok_first = (unsigned)K.tok_first;
     int trace_n = 0;
@@ -565,10 +565,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     const int slot = (t0 + warp) / A.gate_groups, g = (t0 + warp) - slot * A.gate_groups;
                     if (early_e != S->ids[slot]) {
                         if (early_e >= 0) { /* a stale copy is on its way into the stages: take it off the barriers */
-                            if (!fb_mbar_wait(full_u, full_uses[0] & 1) || !fb_mbar_wait(full_u + 8, full_uses[1] & 1))
+                            if (!fb_mbar_wait(full_u, full_par & 1) || !fb_mbar_wait(full_u + 8, (full_par >> 1) & 1))
                                 alive = false;
-                            full_uses[0]++;
-                            full_uses[1]++;
+                            full_par ^= 3u;
                             __syncwarp();
                         }
                         if (alive && lane == 0) {
@@ -580,12 +579,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 const uint32_t a_u = fb_smem_u32(&S->q8h[lane % bpr]);
                 for (int t = t0 + warp; t < t1 && alive; t += SK_WARPS) {
                     float f[2];
-                    if (!fb_mbar_wait(full_u, full_uses[0] & 1) || !fb_mbar_wait(full_u + 8, full_uses[1] & 1)) {
+                    if (!fb_mbar_wait(full_u, full_par & 1) || !fb_mbar_wait(full_u + 8, (full_par >> 1) & 1)) {
                         alive = false;
                         break;
                     }
-                    full_uses[0]++;
-                    full_uses[1]++;
+                    full_par ^= 3u;
                     /* both groups are read where they lie, sharing every activation load between gate and up */
                     fb_dot2_q4k_sm(ring_u + 16 * lane, ring_u + FB_Q4K_GROUP + 16 * lane, a_u, f[0], f[1]);
                     __syncwarp();
@@ -627,11 +625,15 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             const int n_own_rg = (d1 > d0) ? (d1 / ns - rg_first) : 0;
             const uint32_t hand_gen = gen; /* tags this layer-token's hand-over words */
             auto dtask = [&](int j) { return j < n_tail ? d1 - n_tail + j : d0 + (j - n_tail); };
-            const uint32_t dring_u = fb_smem_u32(ring) + warp * 2 * FB_Q6K_GROUP;
+            /* groups of up to 4608 bytes (Q4_K, every half-block format) get three stages per warp, so that all
+             * three rounds of the 397B shape are requested up front; larger ones two */
+            const int nst = GB <= FB_Q4K_GROUP ? 3 : 2;
+            const uint32_t dstride = GB <= FB_Q4K_GROUP ? FB_Q4K_GROUP : FB_Q6K_GROUP;
+            const uint32_t dring_u = fb_smem_u32(ring) + warp * nst * dstride;
             auto dissue = [&](int t, int s) {
                 const int rg = t / ns, slot = t - rg * ns;
                 fb_mbar_expect_tx(full_u + 8 * s, GB);
-                fb_bulk_g2s(dring_u + s * FB_Q6K_GROUP, S->slot_rec[slot] + A.down_off + (uint64_t)rg * GB, GB, full_u + 8 * s);
+                fb_bulk_g2s(dring_u + s * dstride, S->slot_rec[slot] + A.down_off + (uint64_t)rg * GB, GB, full_u + 8 * s);
             };
             /* one group per warp now; the second follows the barrier and the (small, latency-critical) activation
              * loads, which would otherwise queue behind 175 KB of weights on their way into this SM */
@@ -656,7 +658,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         for (int i = 0; i < 8; i++) v[u][i] = 0.0f;
                     }
                 }
-                if (warp < SK_DOWN_WARPS && lane == 0 && warp + SK_DOWN_WARPS < d1 - d0) dissue(dtask(warp + SK_DOWN_WARPS), 1);
+                if (warp < SK_DOWN_WARPS && lane == 0) {
+                    if (warp + SK_DOWN_WARPS < d1 - d0) dissue(dtask(warp + SK_DOWN_WARPS), 1);
+                    if (nst == 3 && warp + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(warp + 2 * SK_DOWN_WARPS), 2);
+                }
                 /* the three windows' shuffle chains are independent: run them unconditionally so they interleave */
 #pragma unroll
                 for (int u = 0; u < 3; u++) {
@@ -688,17 +693,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 uint32_t *dst = reinterpret_cast<uint32_t *>(&S->A2[cur ^ 1]);
                 for (int i = lane; i < (int)(sizeof(fb_args_t) / 4); i += 32) dst[i] = src[i];
             } else if (warp < SK_DOWN_WARPS) {
-                int it = 0;
-                for (int j = warp; j < d1 - d0; j += SK_DOWN_WARPS, it++) {
-                    const int s = it & 1;
-                    if (!fb_mbar_wait(full_u + 8 * s, full_uses[s] & 1)) {
+                int s = 0;
+                for (int j = warp; j < d1 - d0; j += SK_DOWN_WARPS, s = (s + 1 == nst) ? 0 : s + 1) {
+                    if (!fb_mbar_wait(full_u + 8 * s, (full_par >> s) & 1u)) {
                         alive = false;
                         break;
                     }
-                    full_uses[s]++;
+                    full_par ^= 1u << s;
                     const int t = dtask(j);
                     const int rg = t / ns, slot = t - rg * ns;
-                    const uint32_t st = dring_u + s * FB_Q6K_GROUP + 16 * lane;
+                    const uint32_t st = dring_u + s * dstride + 16 * lane;
                     const uint32_t a_u = fb_smem_u32(&S->q8a[slot * dbpr + lane % dbpr]);
                     float f;
                     if (DM == SK_DM_HALF && A.down_type == FB_TYPE_Q4_K) { /* half super-blocks (layout.h) */
@@ -707,7 +711,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
 #pragma unroll
                         for (int k = 0; k < 4; k++) q[k] = fb_lds128(st + 512 * (k + 1));
                         __syncwarp();
-                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        if (lane == 0 && j + nst * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + nst * SK_DOWN_WARPS), s);
                         f = fb_dot_q4k_half_sm(hd, q, a_u, A.down_half);
                     } else if (DM == SK_DM_HALF && A.down_type == FB_TYPE_Q5_K) {
                         const uint4 hd = fb_lds128(st), h0 = fb_lds128(st + 512), h1 = fb_lds128(st + 1024);
@@ -715,7 +719,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
 #pragma unroll
                         for (int k = 0; k < 4; k++) q[k] = fb_lds128(st + 512 * (k + 3));
                         __syncwarp();
-                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        if (lane == 0 && j + nst * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + nst * SK_DOWN_WARPS), s);
                         f = fb_dot_q5k_half_sm(hd, h0, h1, q, a_u, A.down_half);
                     } else if (DM == SK_DM_HALF) {
                         uint4 ql[4], qh[2];
@@ -723,11 +727,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         for (int k = 0; k < 4; k++) ql[k] = fb_lds128(st + 512 * k);
 #pragma unroll
                         for (int k = 0; k < 2; k++) qh[k] = fb_lds128(st + 512 * (4 + k));
-                        const uint2 sc = fb_lds64_a(dring_u + s * FB_Q6K_GROUP + FB_Q6K_HOFF_SC + 8 * lane);
+                        const uint2 sc = fb_lds64_a(dring_u + s * dstride + FB_Q6K_HOFF_SC + 8 * lane);
                         uint32_t d16;
-                        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d16) : "r"(dring_u + s * FB_Q6K_GROUP + FB_Q6K_HOFF_D + 2 * lane));
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d16) : "r"(dring_u + s * dstride + FB_Q6K_HOFF_D + 2 * lane));
                         __syncwarp();
-                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        if (lane == 0 && j + nst * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + nst * SK_DOWN_WARPS), s);
                         f = fb_dot_q6k_half_sm(ql, qh, sc, d16, a_u, A.down_half);
                     } else if (A.down_type == FB_TYPE_Q4_K) {
                         const uint4 hd = fb_lds128(st);
@@ -735,7 +739,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
 #pragma unroll
                         for (int k = 0; k < 8; k++) q[k] = fb_lds128(st + 512 * (k + 1));
                         __syncwarp();
-                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        if (lane == 0 && j + nst * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + nst * SK_DOWN_WARPS), s);
                         f = fb_dot_q4k_sm(hd, q, a_u);
                     } else if (DM == SK_DM_WHOLE_Q5 && A.down_type == FB_TYPE_Q5_K) {
                         const uint4 hd = fb_lds128(st), h0 = fb_lds128(st + 512), h1 = fb_lds128(st + 1024);
@@ -743,7 +747,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
 #pragma unroll
                         for (int k = 0; k < 8; k++) q[k] = fb_lds128(st + 512 * (k + 3));
                         __syncwarp();
-                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        if (lane == 0 && j + nst * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + nst * SK_DOWN_WARPS), s);
                         f = fb_dot_q5k_sm(hd, h0, h1, q, a_u);
                     } else {
                         uint4 ql[8], qh[4];
@@ -753,9 +757,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                         for (int k = 0; k < 4; k++) qh[k] = fb_lds128(st + 512 * (8 + k));
                         const uint4 sc = fb_lds128(st + 512 * 12);
                         uint32_t d16;
-                        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d16) : "r"(dring_u + s * FB_Q6K_GROUP + FB_Q6K_OFF_D + 2 * lane));
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d16) : "r"(dring_u + s * dstride + FB_Q6K_OFF_D + 2 * lane));
                         __syncwarp();
-                        if (lane == 0 && j + 2 * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + 2 * SK_DOWN_WARPS), s);
+                        if (lane == 0 && j + nst * SK_DOWN_WARPS < d1 - d0) dissue(dtask(j + nst * SK_DOWN_WARPS), s);
                         f = fb_dot_q6k_sm(ql, qh, sc, d16, a_u);
                     }
                     f = fb_span_sum(f, dbpr);
