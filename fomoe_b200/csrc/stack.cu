@@ -47,6 +47,7 @@
 #define SK_DOWN_WARPS 13                              /* warps that run down tasks: 38 tasks per block at the 397B shape = 3 rounds */
 #define SK_DN_SLOTS 12                                /* expert slots the down phase can serve */
 #define SK_RING_BYTES (SK_DOWN_WARPS * 3 * FB_Q4K_GROUP) /* 179,712 B: 13 warps x 3 stages x 4608 or x 2 stages x 6720 (174,720); gate/up uses 16 x 2 x 4608 of it */
+#define SK_RING_BYTES_TP (SK_DOWN_WARPS * 2 * FB_Q6K_GROUP) /* tensor-parallel instances: two stages of up to 6720 bytes */
 #define SK_MAX_Q8A 48                                 /* n_slots * down blocks per row */
 #define SK_MAX_RG 8                                   /* row groups one block's run of down tasks can touch */
 #define SK_BAR_THREAD (SK_THREADS - 32) /* lane 0 of the last warp runs the grid barrier; it issues no copies */
@@ -277,7 +278,7 @@ template <bool TP, int DM, bool TRACE>
 __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
     extern __shared__ __align__(128) uint8_t dsm[];
     uint8_t *ring = dsm;
-    sk_smem_t *S = reinterpret_cast<sk_smem_t *>(dsm + SK_RING_BYTES);
+    sk_smem_t *S = reinterpret_cast<sk_smem_t *>(dsm + (TP ? SK_RING_BYTES_TP : SK_RING_BYTES));
     /* the normalised hidden state in fp32 (the near-tie arbiter re-sums router rows from it) lives in the first
      * 16 KB of the ring: it is written in P0 and last read in SEL, the ring is filled from P2 to the end of P3 */
     float *h_sm = reinterpret_cast<float *>(ring);
@@ -625,10 +626,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             const int n_own_rg = (d1 > d0) ? (d1 / ns - rg_first) : 0;
             const uint32_t hand_gen = gen; /* tags this layer-token's hand-over words */
             auto dtask = [&](int j) { return j < n_tail ? d1 - n_tail + j : d0 + (j - n_tail); };
-            /* groups of up to 4608 bytes (Q4_K, every half-block format) get three stages per warp, so that all
-             * three rounds of the 397B shape are requested up front; larger ones two */
-            const int nst = GB <= FB_Q4K_GROUP ? 3 : 2;
-            const uint32_t dstride = GB <= FB_Q4K_GROUP ? FB_Q4K_GROUP : FB_Q6K_GROUP;
+            /* on one GPU, groups of up to 4608 bytes (Q4_K) get three stages per warp, so that all three rounds of
+             * the 397B shape are requested up front; larger ones two.  A tensor-parallel rank has at most two rounds
+             * and keeps two stages (the third cost its instances registers, and with them 0.6 us per layer). */
+            const int nst = (!TP && GB <= FB_Q4K_GROUP) ? 3 : 2;
+            const uint32_t dstride = (!TP && GB <= FB_Q4K_GROUP) ? FB_Q4K_GROUP : FB_Q6K_GROUP;
             const uint32_t dring_u = fb_smem_u32(ring) + warp * nst * dstride;
             auto dissue = [&](int t, int s) {
                 const int rg = t / ns, slot = t - rg * ns;
@@ -693,8 +695,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 uint32_t *dst = reinterpret_cast<uint32_t *>(&S->A2[cur ^ 1]);
                 for (int i = lane; i < (int)(sizeof(fb_args_t) / 4); i += 32) dst[i] = src[i];
             } else if (warp < SK_DOWN_WARPS) {
-                int s = 0;
-                for (int j = warp; j < d1 - d0; j += SK_DOWN_WARPS, s = (s + 1 == nst) ? 0 : s + 1) {
+                int it = 0;
+                for (int j = warp; j < d1 - d0; j += SK_DOWN_WARPS, it++) {
+                    const int s = (nst == 2) ? (it & 1) : (it % 3);
                     if (!fb_mbar_wait(full_u + 8 * s, (full_par >> s) & 1u)) {
                         alive = false;
                         break;
