@@ -507,6 +507,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             };
             int early_e = -1; /* the expert whose groups were requested early (the same in every lane) */
             auto early = [&](const int *cand) {
+                SK_STAMP(5); /* the gate/up phase is timed from its first request */
                 const int t = t0 + warp;
                 if (t >= t1) return;
                 const int slot = t / A.gate_groups, g = t - slot * A.gate_groups;
@@ -556,7 +557,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 for (int e = tid; e < A.n_experts; e += SK_THREADS) A.all_scores[e] = S->all_scores[e];
             }
 
-            SK_STAMP(5);
             /* ---- P2: gate/up + SwiGLU.  Tasks = (expert slot, 32-block group) in slot-major order; every block owns
              *      a contiguous, equally long run of them (so all SMs stream the same number of bytes) and deals
              *      its run round-robin to its 16 warps. */
