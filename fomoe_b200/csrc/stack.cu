@@ -694,6 +694,15 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 const uint32_t *src = reinterpret_cast<const uint32_t *>(K.layers + ln);
                 uint32_t *dst = reinterpret_cast<uint32_t *>(&S->A2[cur ^ 1]);
                 for (int i = lane; i < (int)(sizeof(fb_args_t) / 4); i += 32) dst[i] = src[i];
+                /* its residency mask (64 bytes, long evicted by the expert stream) is asked back into L2: the
+                 * selection reads it right after barrier 1 and would otherwise wait for HBM there */
+                if (lane == 0) {
+                    const uint32_t *rp = K.layers[ln].resident;
+                    if (rp) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(rp));
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + (FB_MAX_EXPERTS / 32 - 1)));
+                    }
+                }
             } else if (warp < SK_DOWN_WARPS) {
                 int it = 0;
                 for (int j = warp; j < d1 - d0; j += SK_DOWN_WARPS, it++) {
