@@ -920,6 +920,13 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
         }
         __syncthreads(); /* the token is complete in this block before the next one starts */
     }
+    if (!alive) {
+        /* A block that gave up may still have bulk copies on their way into its ring (groups are requested ahead of
+         * the barriers and waits that can run out).  They land within microseconds; the block stays for a bounded
+         * grace period, far longer than that, before its shared memory is released. */
+        const unsigned long long t_end = sk_now() + 100000ull; /* 100 us of %globaltimer */
+        for (int i = 0; i < 4096 && sk_now() < t_end; i++) __nanosleep(256);
+    }
     if (leader && tid == 0 && alive) *K.tok_ctr = tok_first + (unsigned)K.tok_count;
 }
 
