@@ -57,14 +57,13 @@ struct sk_smem_t {
     fb_q8_entry_t q8h[16];               /* quantised hidden state */
     fb_q8_entry_t q8a[SK_MAX_Q8A];       /* quantised activations of every slot */
     float dots[SK_MAX_RG][SK_DN_SLOTS][32]; /* per-expert down outputs of this block's row groups */
-    float red[5][SK_WARPS];             /* four router rows and the shared expert's gate vector */
+    float red[6][SK_WARPS];             /* four router rows, the shared expert's gate vector, the sum of squares */
     float shared_gate;
     float all_scores[FB_MAX_EXPERTS];
     fb_sel_smem_t sel;
     int ids[FB_MAX_SLOTS], ids_orig[FB_MAX_SLOTS];
     float scores[FB_MAX_SLOTS];
     const uint8_t *slot_rec[FB_MAX_SLOTS];
-    float scale;
     int ok;
     uint64_t full[SK_WARPS][3];          /* ring stages */
 };
@@ -402,17 +401,15 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 for (int i = 0; i < 8; i++) ss = __fmaf_rn(x[i], x[i], ss);
             }
             for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(FULL, ss, o);
-            if (lane == 0) S->red[0][warp] = ss;
-            __syncthreads();
-            if (tid == 0) {
-                float t = 0.0f;
-                for (int w = 0; w < SK_WARPS; w++) t += S->red[0][w];
-                S->scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)n), A.rms_eps)));
-            }
+            if (lane == 0) S->red[5][warp] = ss;
             __syncthreads();
             float h[8];
             {
-                const float sc = S->scale;
+                /* every thread adds the sixteen partial sums itself, in the same order: no second barrier */
+                float t = 0.0f;
+#pragma unroll
+                for (int w = 0; w < SK_WARPS; w++) t += S->red[5][w];
+                const float sc = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)n), A.rms_eps)));
                 const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
                 for (int i = 0; i < 8; i++) h[i] = own ? __fmul_rn(__fmul_rn(x[i], sc), wv[i]) : 0.0f;
