@@ -12,7 +12,8 @@
  *   P1  router rows are dealt round-robin to the blocks; each thread multiplies its 8 columns of a
  *       row (prefetched into registers before the previous layer's barrier) and the block reduces
  *   --- grid barrier (logits) ---
- *   SEL every block, redundantly: softmax, ordered top-k, renormalise, CAR (route.cuh)
+ *   SEL every block, redundantly: ordered top-k, softmax, renormalise, CAR (select.cuh); as soon as
+ *       the ids are known every warp requests the weights of its first gate/up task
  *   P2  gate/up Q4_K dequant-matvec + SwiGLU: (expert, 32-block group) tasks dealt to 16 warps per
  *       block, weights streamed by bulk copies into per-warp shared-memory rings (stream.cuh)
  *   --- grid barrier (activations) --- the first down groups are already in flight
