@@ -422,11 +422,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 hp[1] = make_float4(h[4], h[5], h[6], h[7]);
                 /* these bytes are later overwritten by bulk copies (async proxy); block barriers follow before then */
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                if (leader) { /* kept in global memory as well, for inspection from the host */
-                    float4 *gp = reinterpret_cast<float4 *>(A.h + e0);
-                    gp[0] = hp[0];
-                    gp[1] = hp[1];
-                }
             }
 
             SK_STAMP(2);
@@ -489,6 +484,15 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
             SK_STAMP(4);
 
             /* ---- SEL: routing, redundantly in every block (results identical by construction) */
+            if (leader && own) {
+                /* the hidden state is kept in global memory as well, for inspection from the host.  Written here and
+                 * not where it is formed: 16 KB of stores ahead of barrier 1 made block 0's arrival (a release) the
+                 * last of every layer, by 0.45 us; ahead of barrier 2 they have the whole gate/up phase to drain */
+                const float4 *hp = reinterpret_cast<const float4 *>(h_sm + e0);
+                float4 *gp = reinterpret_cast<float4 *>(A.h + e0);
+                gp[0] = hp[0];
+                gp[1] = hp[1];
+            }
             /* As soon as the ids are known, each warp starts the copies of its first gate/up task into its ring
              * stages: the softmax, renormalisation and hand-over that follow (about 1 us, more with cache-aware
              * routing) then overlap with HBM's start-up instead of preceding it.  The hidden state that shares the
