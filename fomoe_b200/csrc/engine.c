@@ -86,7 +86,7 @@ struct fomoe_b200_ctx {
                     Environment override: FOMOE_B200_VARIANT */
     fb_args_t *d_layer_args; /* device copy of every layer's arguments for the stack kernel */
     int layer_args_valid;
-    unsigned long long *d_trace, *d_ll_dots;
+    unsigned long long *d_trace, *d_ll_dots, *d_ll_logits;
     /* tensor parallelism: this rank's receive buffer and every rank's buffer as mapped here */
     unsigned long long *tp_recv, *tp_peer[FB_MAX_TP], *tp_xsum;
     int tp_connected, tp_two_stage;
@@ -206,7 +206,7 @@ void fomoe_b200_destroy(fomoe_b200_ctx_t *c) {
         if (c->ev_free[i]) cudaEventDestroy(c->ev_free[i]);
     }
     if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
-    cudaFree(c->d_trace); cudaFree(c->stage); cudaFree(c->d_layer_args); cudaFree(c->d_bar); cudaFree(c->d_ll_dots); cudaFree(c->d_abort);
+    cudaFree(c->d_trace); cudaFree(c->stage); cudaFree(c->d_layer_args); cudaFree(c->d_bar); cudaFree(c->d_ll_dots); cudaFree(c->d_ll_logits); cudaFree(c->d_abort);
     if (c->pin) cudaFreeHost(c->pin);
     for (int i = 0; i < c->pev_cap; i++) cudaEventDestroy(c->pev[i]);
     free(c->pev);
@@ -343,7 +343,7 @@ fomoe_b200_ctx_t *fomoe_b200_create(const fomoe_b200_config_t *cfg) {
         dev_alloc(c, (void **)&c->shared_gate, sizeof(float)) ||
         dev_alloc(c, (void **)&c->d_layer_args, sizeof(fb_args_t) * (uint64_t)nl) ||
         dev_alloc(c, (void **)&c->d_bar, 32 * sizeof(unsigned long long)) ||
-        dev_alloc(c, (void **)&c->d_ll_dots, sizeof(unsigned long long) * FB_MAX_SLOTS * (uint64_t)ne) || dev_alloc(c, (void **)&c->d_abort, sizeof(int)) ||
+        dev_alloc(c, (void **)&c->d_ll_dots, sizeof(unsigned long long) * FB_MAX_SLOTS * (uint64_t)ne) || dev_alloc(c, (void **)&c->d_ll_logits, sizeof(unsigned long long) * FB_MAX_EXPERTS) || dev_alloc(c, (void **)&c->d_abort, sizeof(int)) ||
         dev_alloc(c, (void **)&c->tok_in, sizeof(float) * (uint64_t)(c->max_tokens + 1) * ne) ||
         dev_alloc(c, (void **)&c->tok_out, sizeof(float) * (uint64_t)(c->max_tokens + 1) * ne))
         goto fail;
@@ -1144,6 +1144,7 @@ static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int first, i
     k.bar = c->d_bar;
     k.bar_base = c->bar_count;
     k.ll_dots = c->d_ll_dots;
+    k.ll_logits = c->d_ll_logits;
     k.gen_base = c->gen_count;
     k.abort_flag = c->d_abort;
     k.spin_limit = c->spin_limit;

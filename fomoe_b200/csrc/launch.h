@@ -130,6 +130,7 @@ typedef struct {
     unsigned long long *bar; /* grid barrier: [0] arrival counter, [16] generation of the last completed barrier */
     unsigned long long bar_base; /* arrivals before this launch (the host keeps count) */
     unsigned long long *ll_dots; /* [FB_MAX_SLOTS][n_embd] {generation, value} words: row groups split between blocks */
+    unsigned long long *ll_logits; /* [FB_MAX_EXPERTS] {generation, value} words: the router logits of the layer-token in flight */
     unsigned gen_base;       /* layer-tokens run by earlier launches */
     unsigned spin_limit;     /* polls after which a wait on another block or rank is given up */
     int *abort_flag;         /* raised by a block that gave up a wait; cleared by the host before a launch */

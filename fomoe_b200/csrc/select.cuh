@@ -177,15 +177,15 @@ __device__ __forceinline__ int fb_select_car(const fb_args_t &A, fb_sel_smem_t *
 /* Must be called by all 512 threads of the block.  Outputs (shared memory): ids[n_slots], scores[n_slots],
  * ids_orig[top_k], slot_rec[n_slots], all_scores[n_experts].  `leader` updates the global counters;
  * `shared_score` is the weight of the shared expert's slot; `rec` (leader only, may be NULL) receives the decision
- * for the routing trace; `early(const int *candidates)` is called by every thread as soon as the selected ids are
- * known. */
-template <class Early>
+ * for the routing trace; `logit(expert)` fetches a router logit; `early(const int *candidates)` is called by every
+ * thread as soon as the selected ids are known. */
+template <class Logit, class Early>
 __device__ void fb_block_select(const fb_args_t &A, fb_sel_smem_t *W, const float *h_smem, float *all_scores, int *ids,
                                 int *ids_orig, float *scores, const uint8_t **slot_rec, bool leader, float shared_score,
-                                fb_route_rec_t *rec, Early early) {
+                                fb_route_rec_t *rec, Logit logit, Early early) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nE = A.n_experts, k = A.top_k, kk = min(k + 1, nE);
-    float lg = (tid < nE) ? __ldcg(A.logits + tid) : -INFINITY;
+    float lg = (tid < nE) ? logit(tid) : -INFINITY;
     /* cache-aware routing on for this layer?  (the same for every thread; its mask word is requested now) */
     const bool car_on = A.resident && A.car_threshold > 0.0f && A.car_threshold < 1.0f;
     const uint32_t res_word = car_on ? __ldg(A.resident + (tid >> 5)) : 0u;

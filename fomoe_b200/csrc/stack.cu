@@ -109,7 +109,7 @@ __device__ __forceinline__ void sk_give_up(const sk_bar_t &B) {
  * the data itself as {generation, value} words polled by their consumers (5 us for the 512 logits): on this chip
  * many pollers on few L2 lines delay the very stores they wait for.  Both words only ever grow; the host tells the
  * kernel where they stand when a launch starts. */
-__device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S) {
+__device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S, bool fenced = true) {
     __syncthreads();
     B.epoch++;
     if (threadIdx.x == SK_BAR_THREAD) {
@@ -125,7 +125,10 @@ __device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S) {
 #ifdef SK_FENCED_GENERATION
         asm volatile("atom.add.acq_rel.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
 #else
-        asm volatile("atom.add.release.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
+        if (fenced)
+            asm volatile("atom.add.release.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
+        else /* everything the block publishes at this barrier validates itself ({generation, value} words) */
+            asm volatile("atom.add.relaxed.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
 #endif
         const unsigned long long gen = B.base / B.grid + B.epoch;
         if (old + 1ULL == gen * B.grid) {
@@ -468,7 +471,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 if (row < A.n_experts) {
                     float t = 0.0f;
                     for (int w = 0; w < SK_WARPS; w++) t += S->red[tid][w];
-                    A.logits[row] = t;
+                    A.logits[row] = t; /* for inspection from the host */
+                    sk_put(K.ll_logits + row, t, gen);
                 }
             } else if (tid == 32) {
                 float t = 0.0f;
@@ -492,10 +496,13 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     float t = 0.0f;
                     for (int w = 0; w < SK_WARPS; w++) t += S->red[0][w];
                     A.logits[row] = t;
+                    sk_put(K.ll_logits + row, t, gen);
                 }
             }
             SK_STAMP(3);
-            sk_arrive(B, S);
+            /* The logits travel as {generation, value} words, which a reader can tell from stale ones, so this
+             * arrival needs no release: 0.5 us per layer less than a fence that waits for four stores. */
+            sk_arrive(B, S, false);
             alive = sk_wait(B, S);
             if (!alive) break;
             SK_STAMP(4);
@@ -564,9 +571,23 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 }
 #endif
             };
+            /* a logit word that the barrier has overtaken (it carries an older generation) is simply read again */
+            bool logits_ok = true;
+            auto logit = [&](int e) -> float {
+                sk_word_t w = sk_get1(K.ll_logits + e);
+                for (unsigned nsp = 0; (uint32_t)(w >> 32) != gen; nsp++) {
+                    if (nsp >= K.spin_limit || ((nsp & 255u) == 255u && ld_volatile_s32(K.abort_flag))) {
+                        logits_ok = false;
+                        break;
+                    }
+                    w = sk_get1(K.ll_logits + e);
+                }
+                return __uint_as_float((uint32_t)w);
+            };
             fb_block_select(A, &S->sel, h_sm, S->all_scores, S->ids, S->ids_orig, S->scores, S->slot_rec, leader,
                             S->shared_gate,
-                            (leader && A.route_log) ? A.route_log + (size_t)tok * A.route_stride : nullptr, early);
+                            (leader && A.route_log) ? A.route_log + (size_t)tok * A.route_stride : nullptr, logit, early);
+            if (!__all_sync(FULL, logits_ok)) alive = false; /* the block barrier that ends gate/up gives up */
             if (leader) {
                 if (tid < A.n_slots) {
                     A.ids[tid] = S->ids[tid];
