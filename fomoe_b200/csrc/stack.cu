@@ -11,7 +11,7 @@
  *       (x lives in registers, 8 elements per thread; src/tensor.c:175-184, src/quant.c:343-375)
  *   P1  router rows are dealt round-robin to the blocks; each thread multiplies its 8 columns of a
  *       row (prefetched into registers before the previous layer's barrier) and the block reduces
- *   --- grid barrier (logits) ---
+ *   --- logits exchanged as {generation, value} words, polled by the threads that rank them ---
  *   SEL every block, redundantly: ordered top-k, softmax, renormalise, CAR (select.cuh); as soon as
  *       the ids are known every warp requests the weights of its first gate/up task
  *   P2  gate/up Q4_K dequant-matvec + SwiGLU: (expert, 32-block group) tasks dealt to 16 warps per
@@ -109,7 +109,7 @@ __device__ __forceinline__ void sk_give_up(const sk_bar_t &B) {
  * the data itself as {generation, value} words polled by their consumers (5 us for the 512 logits): on this chip
  * many pollers on few L2 lines delay the very stores they wait for.  Both words only ever grow; the host tells the
  * kernel where they stand when a launch starts. */
-__device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S, bool fenced = true) {
+__device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S) {
     __syncthreads();
     B.epoch++;
     if (threadIdx.x == SK_BAR_THREAD) {
@@ -125,10 +125,7 @@ __device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S, bool fenced
 #ifdef SK_FENCED_GENERATION
         asm volatile("atom.add.acq_rel.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
 #else
-        if (fenced)
-            asm volatile("atom.add.release.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
-        else /* everything the block publishes at this barrier validates itself ({generation, value} words) */
-            asm volatile("atom.add.relaxed.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
+        asm volatile("atom.add.release.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
 #endif
         const unsigned long long gen = B.base / B.grid + B.epoch;
         if (old + 1ULL == gen * B.grid) {
@@ -500,12 +497,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 }
             }
             SK_STAMP(3);
-            /* The logits travel as {generation, value} words, which a reader can tell from stale ones, so this
-             * arrival needs no release: 0.5 us per layer less than a fence that waits for four stores. */
-            sk_arrive(B, S, false);
-            alive = sk_wait(B, S);
-            if (!alive) break;
-            SK_STAMP(4);
+            /* No grid barrier here: the logits travel as {generation, value} words, every thread of every block polls
+             * the one word it ranks, and a word of this layer-token cannot be mistaken for an older one.  (A block can
+             * only write the next layer-token's word after barrier 2 of this one, which every block reaches after it
+             * has read its logits.)  1.5 us per layer less than arrival, release and a load behind it. */
 
             /* ---- SEL: routing, redundantly in every block (results identical by construction) */
             if (leader && own) {
@@ -571,7 +566,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 }
 #endif
             };
-            /* a logit word that the barrier has overtaken (it carries an older generation) is simply read again */
+            /* the wait for the logits: a word is read again until it carries this layer-token's generation (bounded) */
             bool logits_ok = true;
             auto logit = [&](int e) -> float {
                 sk_word_t w = sk_get1(K.ll_logits + e);
@@ -582,12 +577,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                     }
                     w = sk_get1(K.ll_logits + e);
                 }
+                SK_STAMP(4); /* thread 0's word has arrived */
                 return __uint_as_float((uint32_t)w);
             };
             fb_block_select(A, &S->sel, h_sm, S->all_scores, S->ids, S->ids_orig, S->scores, S->slot_rec, leader,
                             S->shared_gate,
                             (leader && A.route_log) ? A.route_log + (size_t)tok * A.route_stride : nullptr, logit, early);
-            if (!__all_sync(FULL, logits_ok)) alive = false; /* the block barrier that ends gate/up gives up */
+            if (!__all_sync(FULL, logits_ok)) { /* the block barrier that ends gate/up gives up */
+                if (lane == 0) sk_give_up(B);
+                alive = false;
+            }
             if (leader) {
                 if (tid < A.n_slots) {
                     A.ids[tid] = S->ids[tid];
