@@ -1161,10 +1161,10 @@ static int launch_stack_kernel(fomoe_b200_ctx_t *c, int l0, int l1, int first, i
     k.trace_cta = c->trace_cta;
     /* the abort flag is zero unless an earlier launch gave up; stack_finish / fomoe_b200_status clear it again */
     CKL(c, fb_launch_stack(&k, c->n_sm, c->stream));
-    /* grid barriers per layer-token: activations and (one GPU only; tensor-parallel ranks exchange the block
-     * output through their receive buffers instead) the block output; every block arrives once at each.  (The
-     * logits cross as self-validating words, without a barrier.) */
-    c->bar_count += (c->cfg.tp_size > 1 ? 1ull : 2ull) * (unsigned long long)((l1 - l0) * count) * (unsigned long long)c->n_sm;
+    /* grid barriers per layer-token, every block arriving once at each: one GPU -- activations and block output (the
+     * logits cross as self-validating words without a barrier); a tensor-parallel rank -- logits and activations
+     * (the block output is exchanged through the ranks' receive buffers) */
+    c->bar_count += 2ull * (unsigned long long)((l1 - l0) * count) * (unsigned long long)c->n_sm;
     c->gen_count += (unsigned)((l1 - l0) * count);
     return 0;
 }

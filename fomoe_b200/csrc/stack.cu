@@ -109,7 +109,7 @@ __device__ __forceinline__ void sk_give_up(const sk_bar_t &B) {
  * the data itself as {generation, value} words polled by their consumers (5 us for the 512 logits): on this chip
  * many pollers on few L2 lines delay the very stores they wait for.  Both words only ever grow; the host tells the
  * kernel where they stand when a launch starts. */
-__device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S) {
+__device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S, bool fenced = true) {
     __syncthreads();
     B.epoch++;
     if (threadIdx.x == SK_BAR_THREAD) {
@@ -125,7 +125,10 @@ __device__ __forceinline__ void sk_arrive(sk_bar_t &B, sk_smem_t *S) {
 #ifdef SK_FENCED_GENERATION
         asm volatile("atom.add.acq_rel.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
 #else
-        asm volatile("atom.add.release.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
+        if (fenced)
+            asm volatile("atom.add.release.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
+        else /* everything the block publishes at this barrier validates itself ({generation, value} words) */
+            asm volatile("atom.add.relaxed.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(B.ctr), "l"(1ULL) : "memory");
 #endif
         const unsigned long long gen = B.base / B.grid + B.epoch;
         if (old + 1ULL == gen * B.grid) {
@@ -497,10 +500,18 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_stack(fb_stack_args_t K) {
                 }
             }
             SK_STAMP(3);
-            /* No grid barrier here: the logits travel as {generation, value} words, every thread of every block polls
-             * the one word it ranks, and a word of this layer-token cannot be mistaken for an older one.  (A block can
-             * only write the next layer-token's word after barrier 2 of this one, which every block reaches after it
-             * has read its logits.)  1.5 us per layer less than arrival, release and a load behind it. */
+            /* The logits travel as {generation, value} words; every thread polls the one word it ranks, and a word
+             * of this layer-token cannot be mistaken for an older one.  (A block can only write the next
+             * layer-token's word after barrier 2 of this one, which every block reaches after it has read its
+             * logits.)  On one GPU that is the whole exchange: no grid barrier, 1.5 us per layer less than arrival,
+             * release and a load behind it.  Tensor-parallel ranks keep a barrier (an arrival without a fence: the
+             * words validate themselves): their blocks come out of the join as the peers' words arrive, up to
+             * microseconds apart, and that many threads polling for that long slowed the whole layer by 1 - 4.5 us. */
+            if (TP) {
+                sk_arrive(B, S, false);
+                alive = sk_wait(B, S);
+                if (!alive) break;
+            }
 
             /* ---- SEL: routing, redundantly in every block (results identical by construction) */
             if (leader && own) {
