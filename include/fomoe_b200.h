@@ -265,7 +265,8 @@ int fomoe_b200_tp_connect(fomoe_b200_ctx_t *ctx, const void *handles /* tp_size 
  * phase boundaries during the following runs (cap 0 = off; cta < 0 = every block, `cap` stamps each, block-major);
  * trace_read copies the first n out.  Each word is
  * (index << 56) | nanoseconds; index 0 layer top, 1 previous barrier joined, 2 RMSNorm/Q8_K done, 3 router rows
- * done, 4 logits barrier passed, 5 routing done, 6 gate/up done, 7 activation barrier passed, 8 down done. */
+ * done, 4 logits received, 5 expert ids known (first gate/up weights requested), 6 gate/up done, 7 activation barrier
+ * passed, 8 down done. */
 int fomoe_b200_trace_enable(fomoe_b200_ctx_t *ctx, int cap, int cta);
 int fomoe_b200_trace_read(fomoe_b200_ctx_t *ctx, unsigned long long *out, int n);
 /* Execution variant: 2 (default) the persistent stack kernel runs whole tokens (stack_run, tokens_run,
